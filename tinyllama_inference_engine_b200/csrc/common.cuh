@@ -1,0 +1,71 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+//
+// Every kernel file exports plain C launchers (extern "C", returning a cudaError_t as
+// int) so that the host side can load the library without any binding generator.
+// Storage types are float (the true 32-bit path) and __nv_bfloat16 (the serving path);
+// arithmetic inside every kernel here is 32-bit.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TLIE_EXPORT extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the host wrappers
+#define TLIE_F32 0
+#define TLIE_BF16 1
+
+namespace tlie {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads.  The order of additions depends only on the
+// block size, so a row's result does not depend on what else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int warps = (blockDim.x + 31) >> 5;
+  float total = (lane < warps) ? scratch[lane] : 0.0f;
+  total = warp_sum(total);
+  return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int warps = (blockDim.x + 31) >> 5;
+  float total = (lane < warps) ? scratch[lane] : -INFINITY;
+  total = warp_max(total);
+  return total;
+}
+
+}  // namespace tlie

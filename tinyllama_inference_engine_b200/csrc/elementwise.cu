@@ -1,0 +1,161 @@
+// Row-wise kernels: embedding gather, residual add + RMSNorm, SiLU(gate) * up.
+//
+// Formulas follow the reference's operators (src/operators.cpp:22-45 RmsNorm,
+// :148-164 SiluMultiply) and its CUDA twins (src/cuda/kernels.cu:67-84, 198-215); the
+// fusion of the residual add into the norm and the 32-bit residual stream are this
+// engine's own.
+#include "common.cuh"
+
+namespace tlie {
+
+// residual[t, :] = float(table[ids[t], :])
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ residual, int hidden) {
+  const int row = blockIdx.x;
+  const T* src = table + (size_t)ids[row] * hidden;
+  float* dst = residual + (size_t)row * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+// Optional add, then RMSNorm.  For output row r the source row is rows ? rows[r] : r.
+//   if delta:  residual[src, :] += float(delta[src, :])        (32-bit sum, stored back)
+//   scale = 1 / sqrt(mean(residual[src]^2) + eps);  out[r, :] = (x * scale) * weight
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ weight,
+                                   float eps, T* __restrict__ out, int hidden) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* x = residual + (size_t)src * hidden;
+  float sum = 0.0f;
+  if (delta) {
+    const T* d = delta + (size_t)src * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = x[i] + to_float(d[i]);
+      x[i] = v;
+      sum += v * v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = x[i];
+      sum += v * v;
+    }
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = 1.0f / sqrtf(sum / (float)hidden + eps);
+  T* y = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) y[i] = from_float<T>((x[i] * scale) * weight[i]);
+}
+
+// residual[t, :] += float(delta[t, :]) without a norm (the last add when no norm follows).
+template <typename T>
+__global__ void add_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t count) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    residual[i] += to_float(delta[i]);
+}
+
+// out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i]
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / inter;
+    const int col = (int)(i - row * inter);
+    const float g = to_float(gate_up[row * 2 * inter + col]);
+    const float u = to_float(gate_up[row * 2 * inter + inter + col]);
+    out[i] = from_float<T>((g / (1.0f + expf(-g))) * u);
+  }
+}
+
+// out[r, :] = src[rows[r], :]
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows, T* __restrict__ out, int width) {
+  const int r = blockIdx.x;
+  const T* s = src + (size_t)rows[r] * width;
+  T* d = out + (size_t)r * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) d[i] = s[i];
+}
+
+// out (float) = float(in)
+template <typename T>
+__global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ out, size_t count) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = to_float(in[i]);
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+static inline int grid_for(size_t total, int block) {
+  size_t blocks = (total + block - 1) / block;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+TLIE_EXPORT int tlie_embedding(int dtype, const void* table, const int* ids, float* residual, int rows, int hidden,
+                               cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dtype == TLIE_F32)
+    embedding_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, residual, hidden);
+  else
+    embedding_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, residual, hidden);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_add_rmsnorm(int dtype, float* residual, const void* delta, const int* rows, const float* weight,
+                                 float eps, void* out, int out_rows, int hidden, cudaStream_t stream) {
+  if (out_rows <= 0) return 0;
+  const int block = hidden >= 1024 ? 256 : 128;
+  if (dtype == TLIE_F32)
+    add_rmsnorm_kernel<float><<<out_rows, block, 0, stream>>>(residual, (const float*)delta, rows, weight, eps,
+                                                              (float*)out, hidden);
+  else
+    add_rmsnorm_kernel<__nv_bfloat16><<<out_rows, block, 0, stream>>>(residual, (const __nv_bfloat16*)delta, rows,
+                                                                      weight, eps, (__nv_bfloat16*)out, hidden);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_add(int dtype, float* residual, const void* delta, long long count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (dtype == TLIE_F32)
+    add_kernel<float><<<grid_for(count, 256), 256, 0, stream>>>(residual, (const float*)delta, (size_t)count);
+  else
+    add_kernel<__nv_bfloat16><<<grid_for(count, 256), 256, 0, stream>>>(residual, (const __nv_bfloat16*)delta,
+                                                                        (size_t)count);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_silu_mul(int dtype, const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
+  const size_t total = (size_t)rows * inter;
+  if (total == 0) return 0;
+  if (dtype == TLIE_F32)
+    silu_mul_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+  else
+    silu_mul_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up,
+                                                                             (__nv_bfloat16*)out, inter, total);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_gather_rows(int dtype, const void* src, const int* rows, void* out, int out_rows, int width,
+                                 cudaStream_t stream) {
+  if (out_rows <= 0) return 0;
+  if (dtype == TLIE_F32)
+    gather_rows_kernel<float><<<out_rows, 256, 0, stream>>>((const float*)src, rows, (float*)out, width);
+  else
+    gather_rows_kernel<__nv_bfloat16><<<out_rows, 256, 0, stream>>>((const __nv_bfloat16*)src, rows,
+                                                                    (__nv_bfloat16*)out, width);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_to_float(int dtype, const void* in, float* out, long long count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (dtype == TLIE_F32)
+    to_float_kernel<float><<<grid_for(count, 256), 256, 0, stream>>>((const float*)in, out, (size_t)count);
+  else
+    to_float_kernel<__nv_bfloat16><<<grid_for(count, 256), 256, 0, stream>>>((const __nv_bfloat16*)in, out,
+                                                                             (size_t)count);
+  return (int)cudaGetLastError();
+}

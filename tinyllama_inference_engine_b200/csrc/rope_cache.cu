@@ -1,0 +1,99 @@
+// Rotary position encoding of q and k, fused with the write of k and v into cache pages.
+//
+// Rotation as in the reference (src/operators.cpp:47-78, src/cuda/kernels.cu:86-115):
+// "half-split" pairs (d, d + R/2) of the first R = rotary_dim elements of a head,
+// angle = float(position) * inv_freq[d], all in 32-bit.  inv_freq[d] = theta^(-2d/R) is
+// a table the host computes once, so host reference and kernel use the same frequencies.
+// The reference rotates one token per launch and copies k, v with a second kernel
+// (kernels.cu:137-145); here one launch handles every token of the step and stores
+// through the request's block table.
+//
+// qkv row layout: [q heads | k heads | v heads], each head head_dim wide.
+// Page layout (one layer): [page][2 (k, v)][kv head][slot in page][head_dim].
+#include "common.cuh"
+
+namespace tlie {
+
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                  const int* __restrict__ token_seq, const int* __restrict__ block_table,
+                                  int table_stride, const float* __restrict__ inv_freq, int rotary_dim,
+                                  T* __restrict__ pages, int q_heads, int kv_heads, int head_dim, int page_size,
+                                  int write_cache) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int row_width = (q_heads + 2 * kv_heads) * head_dim;
+  T* row = qkv + (size_t)t * row_width;
+  const int half = rotary_dim / 2;
+
+  T* k_dst = nullptr;
+  T* v_dst = nullptr;
+  if (write_cache) {
+    const int seq = token_seq[t];
+    const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+    const int slot = pos % page_size;
+    const size_t plane = (size_t)kv_heads * page_size * head_dim;
+    k_dst = pages + (size_t)page * 2 * plane + (size_t)slot * head_dim;
+    v_dst = k_dst + plane;
+  }
+  const size_t head_stride_in_page = (size_t)page_size * head_dim;
+
+  // q heads and k heads: rotate the first rotary_dim elements, pass the rest through.
+  const int rot_heads = q_heads + (write_cache ? kv_heads : 0);
+  const int per_head = head_dim - half;  // one work item per pair, one per unrotated element
+  for (int item = threadIdx.x; item < rot_heads * per_head; item += blockDim.x) {
+    const int head = item / per_head;
+    const int d = item - head * per_head;
+    T* x = row + (size_t)head * head_dim;
+    const bool is_k = head >= q_heads;
+    T* dst = is_k ? (k_dst + (size_t)(head - q_heads) * head_stride_in_page) : x;
+    if (d < half) {
+      float first = to_float(x[d]);
+      float second = to_float(x[d + half]);
+      if (inv_freq != nullptr) {
+        const float angle = (float)pos * inv_freq[d];
+        const float c = cosf(angle);
+        const float s = sinf(angle);
+        const float a = first * c - second * s;
+        const float b = second * c + first * s;
+        first = a;
+        second = b;
+      }
+      dst[d] = from_float<T>(first);
+      dst[d + half] = from_float<T>(second);
+    } else {
+      const int e = d + half;  // elements rotary_dim .. head_dim-1
+      if (is_k) dst[e] = x[e];
+    }
+  }
+  if (write_cache) {
+    const T* v = row + (size_t)(q_heads + kv_heads) * head_dim;
+    for (int item = threadIdx.x; item < kv_heads * head_dim; item += blockDim.x) {
+      const int head = item / head_dim;
+      const int d = item - head * head_dim;
+      v_dst[(size_t)head * head_stride_in_page + d] = v[item];
+    }
+  }
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+TLIE_EXPORT int tlie_rope_store(int dtype, void* qkv, const int* positions, const int* token_seq,
+                                const int* block_table, int table_stride, const float* inv_freq, int rotary_dim,
+                                void* pages, int tokens, int q_heads, int kv_heads, int head_dim, int page_size,
+                                int write_cache, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+  const int block = 256;
+  if (dtype == TLIE_F32)
+    rope_store_kernel<float><<<tokens, block, 0, stream>>>((float*)qkv, positions, token_seq, block_table,
+                                                           table_stride, inv_freq, rotary_dim, (float*)pages, q_heads,
+                                                           kv_heads, head_dim, page_size, write_cache);
+  else
+    rope_store_kernel<__nv_bfloat16><<<tokens, block, 0, stream>>>(
+        (__nv_bfloat16*)qkv, positions, token_seq, block_table, table_stride, inv_freq, rotary_dim,
+        (__nv_bfloat16*)pages, q_heads, kv_heads, head_dim, page_size, write_cache);
+  return (int)cudaGetLastError();
+}

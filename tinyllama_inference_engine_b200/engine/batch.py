@@ -1,0 +1,100 @@
+"""One step's batch: requests' next tokens, flattened, with everything a kernel needs to find the cache."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+
+    request_id: object
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)
+
+
+@dataclass
+class StepContext:
+    """Device-side description of a step (int32 tensors) plus the same numbers on the host.
+
+    Rows of the step are the tokens of all entries, entry after entry.
+      token_ids[T], positions[T]  each row's token and absolute position in its request
+      token_seq[T]                which entry (request of this step) a row belongs to
+      seq_starts[B + 1]           first row of every entry (cumulative lengths)
+      seq_lens[B]                 tokens the request holds after this step
+      first_positions[B]          position of the entry's first row
+      state_slots[B]              the request's slot in per-request state tensors
+      want_rows[W]                rows whose logits are returned, in entry and want order
+      block_tables[g][B, width]   page ids of every entry in page group g (-1: none)
+    """
+
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    token_seq: torch.Tensor
+    seq_starts: torch.Tensor
+    seq_lens: torch.Tensor
+    first_positions: torch.Tensor
+    state_slots: torch.Tensor
+    want_rows: torch.Tensor | None
+    block_tables: list[torch.Tensor]
+    # host copies (plain lists) for parts written in Python and for kernel launch shapes
+    request_ids: list
+    host_q_lens: list[int]
+    host_first_positions: list[int]
+    host_state_slots: list[int]
+    max_q_len: int
+    max_seq_len: int
+
+    @property
+    def decode_only(self) -> bool:
+        return self.max_q_len == 1
+
+
+def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[int], table_rows: list[list[list[int]]],
+              device: torch.device) -> StepContext:
+    """Flatten the entries into one int32 buffer, copy it once, and slice the views."""
+    q_lens = [len(e.tokens) for e in entries]
+    num_tokens, num_seqs = sum(q_lens), len(entries)
+    token_ids: list[int] = []
+    positions: list[int] = []
+    token_seq: list[int] = []
+    seq_starts = [0]
+    want_rows: list[int] = []
+    for index, (entry, first) in enumerate(zip(entries, first_positions)):
+        start = seq_starts[-1]
+        token_ids += entry.tokens
+        positions += range(first, first + len(entry.tokens))
+        token_seq += [index] * len(entry.tokens)
+        want_rows += [start + w for w in entry.want]
+        seq_starts.append(start + len(entry.tokens))
+    seq_lens = [f + n for f, n in zip(first_positions, q_lens)]
+    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows]
+    flat: list[int] = []
+    offsets = []
+    for section in sections:
+        offsets.append((len(flat), len(section)))
+        flat += section
+    table_offsets = []
+    for rows in table_rows:
+        width = len(rows[0]) if rows else 0
+        table_offsets.append((len(flat), num_seqs, width))
+        for row in rows:
+            flat += row
+    host = torch.tensor(flat, dtype=torch.int32)
+    if device.type == "cuda":
+        host = host.pin_memory()
+    buffer = host.to(device, non_blocking=True)
+    views = [buffer[o : o + n] for o, n in offsets]
+    tables = [buffer[o : o + b * w].view(b, w) for o, b, w in table_offsets]
+    return StepContext(
+        num_tokens=num_tokens, num_seqs=num_seqs,
+        token_ids=views[0], positions=views[1], token_seq=views[2], seq_starts=views[3], seq_lens=views[4],
+        first_positions=views[5], state_slots=views[6], want_rows=views[7] if want_rows else None,
+        block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=q_lens,
+        host_first_positions=list(first_positions), host_state_slots=list(slots),
+        max_q_len=max(q_lens), max_seq_len=max(seq_lens),
+    )

@@ -1,0 +1,111 @@
+"""The step function: run a batch of (request, its next tokens) from the cache, return wanted logits.
+
+``ModelRunner`` owns the model, the cache manager and nothing else.  ``step`` takes
+any mixture of prompt portions and single decoded tokens, cut anywhere; it runs only
+the tokens it is given, as one batch, and returns the logits at the wanted places.
+The reference's counterpart takes exactly one token per request and returns logits for
+every row (src/cuda/model.cu:531-725).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from ..cache import CacheManager
+from ..config import EngineConfig, load_model_config
+from ..errors import BatchError, KernelError
+from ..models import DecoderModel, expected_tensors
+from ..parts.base import Runtime, Workspace
+from ..weights import WeightStore
+from .batch import StepContext, StepEntry, pack_step
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str | Path, engine_config: EngineConfig | None = None):
+        self.engine_config = engine_config or EngineConfig()
+        self.device = torch.device(self.engine_config.device)
+        if self.device.type == "cuda" and not torch.cuda.is_available():
+            raise KernelError("no CUDA device is visible; this engine has no CPU path")
+        self.architecture, self.model_config = load_model_config(model_dir)
+        self.spec = self.architecture.build_spec(self.model_config)
+        self.dtype = _TORCH_DTYPES[self.engine_config.dtype]
+        weights = WeightStore.load(model_dir, expected_tensors(self.spec), self.device)
+        workspace = Workspace(self.device, self.engine_config.max_batch_tokens)
+        self.runtime = Runtime(self.dtype, self.device, workspace, {"engine": self.engine_config})
+        self.model = DecoderModel(self.spec, weights, self.runtime)
+        del weights
+        self.cache = CacheManager(
+            self.model.cache_needs, self.engine_config.page_size, self.engine_config.num_pages,
+            self.engine_config.max_requests, self.spec.max_positions, self.dtype, self.device,
+            poison_freed_pages=self.engine_config.poison_freed_pages,
+        )
+        self.steps = 0
+        self.tokens_run = 0
+
+    # --- the step --------------------------------------------------------------------------
+    def validate(self, entries: list[StepEntry]) -> list[int]:
+        """Check a batch without changing anything; returns each entry's first position."""
+        if not entries:
+            raise BatchError("a step needs at least one entry")
+        seen = set()
+        firsts = []
+        vocab = self.spec.vocab_size
+        new_requests = 0
+        for entry in entries:
+            if entry.request_id in seen:
+                raise BatchError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            if not entry.tokens:
+                raise BatchError(f"request {entry.request_id!r} brings no tokens")
+            for token in entry.tokens:
+                if not 0 <= token < vocab:
+                    raise BatchError(f"token {token} of request {entry.request_id!r} is outside the vocabulary of {vocab}")
+            for place in entry.want:
+                if not 0 <= place < len(entry.tokens):
+                    raise BatchError(f"request {entry.request_id!r} wants place {place} among {len(entry.tokens)} tokens")
+            first = self.cache.computed(entry.request_id) if self.cache.has(entry.request_id) else 0
+            new_requests += not self.cache.has(entry.request_id)
+            if first + len(entry.tokens) > self.spec.max_positions:
+                raise BatchError(
+                    f"request {entry.request_id!r} would reach {first + len(entry.tokens)} tokens; the model's context is {self.spec.max_positions}"
+                )
+            firsts.append(first)
+        if len(self.cache.records) + new_requests > self.cache.max_requests:
+            raise BatchError(f"more than {self.cache.max_requests} live requests")
+        return firsts
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run the entries as one batch; returns 32-bit logits [wanted, vocab] (None if nothing is wanted)."""
+        firsts = self.validate(entries)
+        wanted = [(e.request_id if self.cache.has(e.request_id) else None, f + len(e.tokens)) for e, f in zip(entries, firsts)]
+        if not self.cache.can_reserve(wanted):
+            from ..errors import OutOfPages
+
+            raise OutOfPages(f"the step needs more cache pages than are free ({self.cache.free_pages()} free)")
+        slots = []
+        for entry, first in zip(entries, firsts):
+            if not self.cache.has(entry.request_id):
+                self.cache.admit(entry.request_id)
+            self.cache.reserve(entry.request_id, first + len(entry.tokens))
+            slots.append(self.cache.records[entry.request_id].slot)
+        ids = [e.request_id for e in entries]
+        table_rows = [self.cache.block_table_rows(group, ids) for group in self.cache.page_groups]
+        ctx = pack_step(entries, firsts, slots, table_rows, self.device)
+        logits = self.run(ctx)
+        for entry, first in zip(entries, firsts):
+            self.cache.advance(entry.request_id, first + len(entry.tokens))
+        self.steps += 1
+        self.tokens_run += ctx.num_tokens
+        return logits
+
+    def run(self, ctx: StepContext) -> torch.Tensor | None:
+        caches = self.cache.layer_caches(ctx.block_tables)
+        return self.model.forward(ctx, caches)
+
+    def finish(self, request_id: object) -> None:
+        """The request has ended; what it holds is given back."""
+        if self.cache.has(request_id):
+            self.cache.release(request_id)

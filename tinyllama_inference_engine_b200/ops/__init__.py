@@ -1,0 +1,216 @@
+"""Host wrappers of the engine's CUDA kernels.
+
+Every function here launches a hand-written sm_100a kernel on the current CUDA
+stream.  There is no CPU fallback and no library model code behind them: tensors
+must live on a CUDA device, and a missing compiler or a failed build raises
+``KernelError``.  Matrix products of the bfloat16 path may go to the vendor library
+(as the reference's do, src/cuda/kernels.cu:342-368) until the engine's own
+tensor-core kernel covers the shape; the 32-bit path always uses the engine's own
+32-bit product.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..errors import KernelError
+from .build import build_library, load_library
+
+CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_fp32.cu", "sampling.cu"]
+_F32, _BF16 = 0, 1
+launch_count = 0  # kernels of this engine launched by this process (a claim the bench reports)
+
+
+def core():
+    lib = load_library("tlie_core", CORE_SOURCES)
+    if not getattr(lib, "_tlie_typed", False):
+        lib.tlie_uniform_from.restype = c_float
+        lib.tlie_uniform_from.argtypes = [c_longlong, c_longlong]
+        lib._tlie_typed = True
+    return lib
+
+
+def build_all() -> list:
+    """Compile every kernel set (used by the build check); returns the library paths."""
+    from . import fast
+
+    return [build_library("tlie_core", CORE_SOURCES)] + fast.build_all()
+
+
+def _code(tensor: torch.Tensor) -> int:
+    if tensor.dtype == torch.float32:
+        return _F32
+    if tensor.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {tensor.dtype}", code="invalid_dtype")
+
+
+def _ptr(tensor: torch.Tensor | None) -> c_void_p:
+    if tensor is None:
+        return c_void_p(0)
+    if not tensor.is_cuda:
+        raise KernelError("this engine has no CPU path: a kernel was given a tensor that is not on a CUDA device")
+    if not tensor.is_contiguous():
+        raise KernelError("kernels take contiguous tensors")
+    return c_void_p(tensor.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if status != 0:
+        raise KernelError(f"{what} failed to launch: CUDA error {status}")
+
+
+def _i32(tensor: torch.Tensor | None, what: str) -> c_void_p:
+    if tensor is not None and tensor.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, got {tensor.dtype}", code="invalid_dtype")
+    return _ptr(tensor)
+
+
+# --- rows --------------------------------------------------------------------------------
+def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[t] = float(table[ids[t]])."""
+    rows, hidden = residual.shape
+    _check(core().tlie_embedding(_code(table), _ptr(table), _i32(ids, "ids"), _ptr(residual), c_int(rows), c_int(hidden), _stream()), "embedding")
+
+
+def add_rmsnorm(residual, delta, weight, eps: float, out, rows=None) -> None:
+    """Optional ``residual += delta`` in 32-bit, then ``out = rmsnorm(residual) * weight``.
+
+    With ``rows`` (int32) only those rows are normalised (and ``delta`` must be None).
+    """
+    if residual.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise KernelError("the residual stream and norm weights are 32-bit", code="invalid_dtype")
+    if rows is not None and delta is not None:
+        raise KernelError("add_rmsnorm cannot add a delta while gathering rows")
+    out_rows, hidden = out.shape
+    if weight.numel() != hidden or residual.shape[1] != hidden:
+        raise KernelError("add_rmsnorm: widths differ", code="invalid_shape")
+    if delta is not None and (delta.shape != residual.shape or delta.dtype != out.dtype):
+        raise KernelError("add_rmsnorm: delta must match the residual's shape and the output's dtype", code="invalid_shape")
+    _check(
+        core().tlie_add_rmsnorm(_code(out), _ptr(residual), _ptr(delta), _i32(rows, "rows"), _ptr(weight), c_float(eps), _ptr(out), c_int(out_rows), c_int(hidden), _stream()),
+        "add_rmsnorm",
+    )
+
+
+def add_(residual, delta) -> None:
+    _check(core().tlie_add(_code(delta), _ptr(residual), _ptr(delta), c_longlong(residual.numel()), _stream()), "add")
+
+
+def silu_mul(gate_up, out) -> None:
+    rows, inter = out.shape
+    if gate_up.shape != (rows, 2 * inter) or gate_up.dtype != out.dtype:
+        raise KernelError("silu_mul: gate_up must be [rows, 2 * inter] of the output's dtype", code="invalid_shape")
+    _check(core().tlie_silu_mul(_code(out), _ptr(gate_up), _ptr(out), c_int(rows), c_int(inter), _stream()), "silu_mul")
+
+
+def gather_rows(src, rows, out) -> None:
+    _check(core().tlie_gather_rows(_code(src), _ptr(src), _i32(rows, "rows"), _ptr(out), c_int(out.shape[0]), c_int(out.shape[1]), _stream()), "gather_rows")
+
+
+def to_float(src, out) -> None:
+    _check(core().tlie_to_float(_code(src), _ptr(src), _ptr(out), c_longlong(src.numel()), _stream()), "to_float")
+
+
+# --- matrix products --------------------------------------------------------------------
+def linear(x, weight, out) -> None:
+    """out[M, N] = x[M, K] . weight[N, K]^T in the tensors' dtype (32-bit accumulation)."""
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)}^T -> {tuple(out.shape)} do not fit", code="invalid_shape")
+    if x.dtype == torch.float32:
+        if weight.dtype != torch.float32 or out.dtype != torch.float32:
+            raise KernelError("linear: the 32-bit path takes 32-bit weights and outputs", code="invalid_dtype")
+        _check(core().tlie_gemm_nt_f32(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), _stream()), "gemm_nt_f32")
+        return
+    from . import fast
+
+    fast.linear_bf16(x, weight, out)
+
+
+# --- position encoding and cache write ---------------------------------------------------
+def rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim: int, pages, q_heads: int, kv_heads: int, head_dim: int, page_size: int, write_cache: bool = True) -> None:
+    """Rotate q (in place) and k, and store k, v of every token into its request's pages."""
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (q_heads + 2 * kv_heads) * head_dim:
+        raise KernelError("rope_store: qkv width does not fit the head counts", code="invalid_shape")
+    if write_cache and pages.dtype != qkv.dtype:
+        raise KernelError("rope_store: pages and qkv differ in dtype", code="invalid_dtype")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("rope_store: inv_freq must hold rotary_dim / 2 32-bit frequencies", code="invalid_shape")
+    _check(
+        core().tlie_rope_store(
+            _code(qkv), _ptr(qkv), _i32(positions, "positions"), _i32(token_seq, "token_seq"), _i32(block_table, "block_table"),
+            c_int(block_table.shape[1]), _ptr(inv_freq), c_int(rotary_dim if inv_freq is not None else 0), _ptr(pages if write_cache else None),
+            c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(page_size), c_int(1 if write_cache else 0), _stream(),
+        ),
+        "rope_store",
+    )
+
+
+# --- attention -----------------------------------------------------------------------------
+def paged_attention(qkv, pages, positions, token_seq, block_table, out, q_heads: int, kv_heads: int, head_dim: int, page_size: int, window: int = 0, scale: float | None = None, batch=None) -> None:
+    """Attention of every query row over its request's cached keys up to its own position.
+
+    ``qkv`` rows start with the (already rotated) q heads; ``batch`` may carry the
+    step's shape so that a faster kernel can be chosen for bfloat16.
+    """
+    tokens = qkv.shape[0]
+    if head_dim % 16 != 0 or head_dim > 256:
+        raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to 256, got {head_dim}", code="invalid_shape")
+    if q_heads % kv_heads != 0:
+        raise KernelError("attention: query heads must be a multiple of key/value heads", code="invalid_shape")
+    if scale is None:
+        scale = head_dim ** -0.5
+    if qkv.dtype == torch.bfloat16:
+        from . import fast
+
+        if fast.paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, batch):
+            return
+    _check(
+        core().tlie_paged_attention_generic(
+            _code(qkv), _ptr(qkv), c_int(qkv.shape[1]), _ptr(pages), _i32(positions, "positions"), _i32(token_seq, "token_seq"),
+            _i32(block_table, "block_table"), c_int(block_table.shape[1]), _ptr(out), c_int(tokens), c_int(q_heads), c_int(kv_heads),
+            c_int(head_dim), c_int(page_size), c_int(window), c_float(scale), _stream(),
+        ),
+        "paged_attention_generic",
+    )
+
+
+# --- sampling ------------------------------------------------------------------------------
+def argmax(logits, out) -> None:
+    """out[r] = index of the largest logit of row r, the lowest index on ties."""
+    if logits.dtype != torch.float32:
+        raise KernelError("sampling takes 32-bit logits", code="invalid_dtype")
+    _check(core().tlie_argmax(_ptr(logits), c_int(logits.shape[0]), c_int(logits.shape[1]), _i32(out, "out"), _stream()), "argmax")
+
+
+def sample(logits, temperature, top_p, seeds, counters, out) -> None:
+    """Temperature / top-p sampling per row; rows with temperature <= 0 are greedy."""
+    if logits.dtype != torch.float32 or temperature.dtype != torch.float32 or top_p.dtype != torch.float32:
+        raise KernelError("sampling takes 32-bit logits, temperatures and top_p", code="invalid_dtype")
+    if seeds.dtype != torch.int64 or counters.dtype != torch.int64:
+        raise KernelError("sampling takes int64 seeds and counters", code="invalid_dtype")
+    _check(
+        core().tlie_sample(_ptr(logits), c_int(logits.shape[0]), c_int(logits.shape[1]), _ptr(temperature), _ptr(top_p), _ptr(seeds), _ptr(counters), _i32(out, "out"), _stream()),
+        "sample",
+    )
+
+
+def uniform_from(seed: int, counter: int) -> float:
+    """The uniform number in [0, 1) that draw ``counter`` of a request with ``seed`` uses."""
+    mask = (1 << 64) - 1
+    z = (seed * 0x9E3779B97F4A7C15 + (counter + 1) * 0xBF58476D1CE4E5B9) & mask
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+    z = z ^ (z >> 31)
+    return (z >> 40) / 16777216.0

@@ -1,0 +1,180 @@
+"""Interfaces of the parts a model is put together from.
+
+Five categories: ``mixer`` (token mixing: attention here), ``feed_forward``,
+``norm``, ``position`` (position encoding) and ``block`` (their arrangement in one
+layer); plus ``embedding`` and ``head`` at the ends of the model.  A part is built
+from a ``PartSpec`` (its sizes and constants), a tensor-name prefix, the weight
+store and the runtime.  No part knows which model it is in.
+
+What each category must offer:
+
+  every part   ``tensor_specs(spec, prefix)`` (classmethod): the tensors it reads.
+  norm         ``forward(residual, delta=None, rows=None) -> normed``: adds ``delta``
+               into the 32-bit ``residual`` first if given, normalises all rows or
+               the rows listed in ``rows``.
+  position     ``rotary_table()`` -> (inv_freq, rotary_dim) if the encoding is a
+               rotation the fused cache-write kernel can apply, else None, in which
+               case ``apply(qkv, ctx, q_heads, kv_heads, head_dim)`` edits q and k in place.
+  mixer        ``cache_need(spec)`` (classmethod) -> CacheNeed: pages of keys and
+               values, per-request state of fixed size, or nothing;
+               ``forward(x, ctx, cache) -> y`` for the step's tokens ``x [T, hidden]``.
+  feed_forward ``forward(x, ctx) -> y``.
+  block        ``forward(residual, delta, ctx, cache) -> (residual, delta)``: the
+               hidden state is the pair (32-bit residual, last output not yet added).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..errors import ConfigError
+from .spec import PartSpec, TensorSpec
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What a mixer keeps per request between steps.
+
+    kind "pages": keys and values of ``kv_heads`` heads of ``head_dim`` for every
+    cached token, or only the last ``window`` tokens if window > 0.
+    kind "state": one tensor of ``state_shape`` per request (always 32-bit).
+    kind "none": nothing.
+    """
+
+    kind: str = "none"
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: int = 0
+    state_shape: tuple[int, ...] = ()
+
+    def group_key(self) -> tuple:
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape)
+
+
+@dataclass
+class LayerCache:
+    """The cache of one run of a layer, as its mixer sees it during a step."""
+
+    need: CacheNeed
+    writes: bool = True
+    pages: torch.Tensor | None = None        # [num_pages, 2, kv_heads, page_size, head_dim]
+    block_table: torch.Tensor | None = None  # int32 [requests in step, width], -1 where no page
+    page_size: int = 0
+    state: torch.Tensor | None = None        # [slots, *state_shape] float32
+
+
+class Workspace:
+    """Named activation buffers of fixed address, sized once for the largest step."""
+
+    def __init__(self, device: torch.device, max_tokens: int):
+        self.device = device
+        self.max_tokens = max_tokens
+        self._buffers: dict[tuple, torch.Tensor] = {}
+
+    def get(self, name: str, rows: int, width: int, dtype: torch.dtype) -> torch.Tensor:
+        key = (name, width, dtype)
+        capacity = max(self.max_tokens, rows)
+        buffer = self._buffers.get(key)
+        if buffer is None or buffer.shape[0] < capacity:
+            buffer = torch.empty((capacity, width), dtype=dtype, device=self.device)
+            self._buffers[key] = buffer
+        return buffer[:rows]
+
+
+@dataclass
+class Runtime:
+    """Where and in which precision a model runs."""
+
+    dtype: torch.dtype
+    device: torch.device
+    workspace: Workspace
+    options: dict = field(default_factory=dict)
+
+
+class Part:
+    category = ""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        return []
+
+    def __init__(self, spec: PartSpec, prefix: str, weights, runtime: Runtime):
+        self.spec = spec
+        self.prefix = prefix
+        self.runtime = runtime
+
+
+class Norm(Part):
+    category = "norm"
+
+    def forward(self, residual, delta=None, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    category = "position"
+
+    def rotary_table(self):
+        return None
+
+    def apply(self, qkv, ctx, q_heads: int, kv_heads: int, head_dim: int) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    category = "mixer"
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec) -> CacheNeed:
+        return CacheNeed()
+
+    def forward(self, x, ctx, cache: LayerCache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    category = "feed_forward"
+
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Block(Part):
+    category = "block"
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec) -> CacheNeed:
+        return CacheNeed()
+
+    def forward(self, residual, delta, ctx, cache: LayerCache):
+        raise NotImplementedError
+
+
+# --- registry of part classes -------------------------------------------------------------
+_PARTS: dict[tuple[str, str], type] = {}
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+
+
+def register_part(category: str, kind: str, cls: type, *, replace: bool = False) -> None:
+    if category not in CATEGORIES:
+        raise ConfigError(f"unknown part category {category!r}")
+    if (category, kind) in _PARTS and not replace:
+        raise ConfigError(f"{category} part {kind!r} is already registered")
+    _PARTS[(category, kind)] = cls
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _PARTS.pop((category, kind), None)
+
+
+def part_class(category: str, spec: PartSpec) -> type:
+    try:
+        return _PARTS[(category, spec.kind)]
+    except KeyError:
+        known = sorted(kind for cat, kind in _PARTS if cat == category)
+        raise ConfigError(f"no {category} part of kind {spec.kind!r}; known: {known}") from None
+
+
+def build_part(category: str, spec: PartSpec, prefix: str, weights, runtime: Runtime):
+    return part_class(category, spec)(spec, prefix, weights, runtime)

@@ -1,0 +1,66 @@
+"""The two ends of a model: token embedding and output head."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, register_part
+from .spec import PartSpec, TensorSpec
+
+
+class TokenEmbedding(Part):
+    """hidden = table[token], a row copy without scaling (src/model.cpp:94-97).
+
+    params: ``vocab_size``, ``hidden_size``, ``name``.  The row is widened into the
+    32-bit residual stream by a gather kernel (the reference copies one row per token
+    with a device memcpy, src/cuda/model.cu:572-576).
+    """
+
+    category = "embedding"
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        return [TensorSpec(f"{spec['name']}.weight", (spec["vocab_size"], spec["hidden_size"]))]
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.table = weights.get(f"{spec['name']}.weight", runtime.dtype).contiguous()
+        self.hidden = int(spec["hidden_size"])
+
+    def forward(self, token_ids):
+        residual = self.runtime.workspace.get("residual", token_ids.shape[0], self.hidden, torch.float32)
+        ops.embedding(self.table, token_ids, residual)
+        return residual
+
+
+class LinearHead(Part):
+    """logits = W . normed, 32-bit out, for the wanted rows only (src/model.cpp:217-225).
+
+    params: ``vocab_size``, ``hidden_size``, ``name``, ``tied_to`` (name of the
+    embedding table, or None).  With ``tied_to`` and no tensor of its own the head
+    aliases the embedding table; the reference refuses tied checkpoints
+    (src/model_config.cpp:72).
+    """
+
+    category = "head"
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        if spec.get("tied_to"):
+            return []
+        return [TensorSpec(f"{spec['name']}.weight", (spec["vocab_size"], spec["hidden_size"]))]
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        source = spec.get("tied_to") or spec["name"]
+        self.weight = weights.get(f"{source}.weight", runtime.dtype).contiguous()
+        self.vocab = int(spec["vocab_size"])
+
+    def forward(self, normed_rows):
+        logits = torch.empty((normed_rows.shape[0], self.vocab), dtype=torch.float32, device=normed_rows.device)
+        ops.linear(normed_rows, self.weight, logits)
+        return logits
+
+
+register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("head", "linear_head", LinearHead)
