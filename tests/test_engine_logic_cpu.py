@@ -1,0 +1,79 @@
+"""The engine's host logic (cache manager, batch packing, step function, model assembly) on the CPU.
+
+The kernel wrappers are replaced by the plain per-kernel functions of tests/plain_ops.py,
+so these tests say nothing about the kernels; they show that pages, block tables,
+positions and wanted rows are right under every way of cutting the work.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_llama
+import plain_ops
+import trace_tools
+from tinyllama_inference_engine_b200 import EngineConfig
+from tinyllama_inference_engine_b200.engine.runner import ModelRunner
+from tinyllama_inference_engine_b200.errors import BatchError, KernelError, OutOfPages
+
+
+def _runner(folder, max_tokens=1024, page_size=16, dtype="float32"):
+    config = EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8, max_batch_tokens=64, device="cpu", poison_freed_pages=True)
+    return ModelRunner(folder, config)
+
+
+def _full_logits(folder, requests):
+    config, weights = plain_llama.load_model(folder)
+    return {rid: plain_llama.forward(config, weights, tokens) for rid, tokens in requests.items()}
+
+
+def test_without_kernels_the_engine_refuses_cpu_tensors(model_folders):
+    runner = _runner(model_folders["a"])
+    from tinyllama_inference_engine_b200.engine.batch import StepEntry
+
+    with pytest.raises(KernelError, match="no CPU path"):
+        runner.step([StepEntry("x", [1, 2, 3], [2])])
+
+
+@pytest.mark.parametrize("key", ["a", "b", "c"])
+def test_every_cut_gives_the_plain_logits(model_folders, monkeypatch, key):
+    plain_ops.install(monkeypatch)
+    folder = model_folders[key]
+    vocab = plain_llama.load_model(folder)[0]["vocab_size"]
+    requests = trace_tools.make_requests(vocab, [1, 7, 33, 70, 50, 41], seed=1)
+    full = _full_logits(folder, requests)
+    for steps in (trace_tools.whole(requests), trace_tools.tail_decode(requests), trace_tools.portions(requests)):
+        runner = _runner(folder)
+        worst = trace_tools.run_and_compare(runner, steps, full, atol=2e-5)
+        runner.cache.check()
+        assert not runner.cache.records and worst < 2e-5
+    steps, peak = trace_tools.mixed(requests, seed=3, page_size=16)
+    runner = _runner(folder, max_tokens=peak)
+    trace_tools.run_and_compare(runner, steps, full, atol=2e-5)
+    runner.cache.check()
+    stats = runner.cache.stats()["groups"][0]
+    assert stats["reuses"] > 0 and stats["free"] == stats["pages"]
+
+
+def test_step_refuses_bad_batches(model_folders, monkeypatch):
+    plain_ops.install(monkeypatch)
+    from tinyllama_inference_engine_b200.engine.batch import StepEntry
+
+    runner = _runner(model_folders["a"], max_tokens=32)
+    with pytest.raises(BatchError, match="outside the vocabulary"):
+        runner.step([StepEntry("x", [1, 9999], [])])
+    with pytest.raises(BatchError, match="twice"):
+        runner.step([StepEntry("x", [1], []), StepEntry("x", [2], [])])
+    with pytest.raises(BatchError, match="wants place"):
+        runner.step([StepEntry("x", [1, 2], [2])])
+    with pytest.raises(BatchError, match="context"):
+        runner.step([StepEntry("x", [1] * 129, [])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("x", [1] * 40, [])])
+    assert not runner.cache.records  # a refused step leaves nothing behind
+    runner.step([StepEntry("x", [1] * 30, [29])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("y", [1] * 10, [])])
+    assert list(runner.cache.records) == ["x"]
+    runner.finish("x")
+    runner.cache.check()

@@ -1,0 +1,203 @@
+"""Each kernel alone against its plain function (tests/plain_ops.py), at sizes other than the engine's."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype, scale=1.0):
+    return (2e-6 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tinyllama_inference_engine_b200 import ops as module
+
+    assert torch.cuda.is_available(), "these tests need the GPU"
+    module.core()
+    return module
+
+
+def _paged_case(rng, dtype, seq_lens, q_lens, kv_heads, head_dim, page_size, q_heads):
+    """Random cache pages for requests of ``seq_lens`` tokens, the last ``q_lens`` of which are this step's rows."""
+    num_pages = sum(-(-s // page_size) for s in seq_lens) + 3
+    order = rng.permutation(num_pages)
+    width = max(-(-s // page_size) for s in seq_lens) + 1
+    table = -np.ones((len(seq_lens), width), dtype=np.int32)
+    at = 0
+    for i, s in enumerate(seq_lens):
+        n = -(-s // page_size)
+        table[i, :n] = order[at : at + n]
+        at += n
+    pages = (torch.randn(num_pages, 2, kv_heads, page_size, head_dim) * 0.5).to(dtype)
+    positions, token_seq = [], []
+    for i, (s, q) in enumerate(zip(seq_lens, q_lens)):
+        positions += list(range(s - q, s))
+        token_seq += [i] * q
+    tokens = len(positions)
+    qkv = (torch.randn(tokens, (q_heads + 2 * kv_heads) * head_dim) * 0.5).to(dtype)
+    return qkv, pages, torch.tensor(positions, dtype=torch.int32), torch.tensor(token_seq, dtype=torch.int32), torch.from_numpy(table)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    torch.manual_seed(0)
+    table = torch.randn(131, 80).to(dtype)
+    ids = torch.tensor([0, 130, 5, 5, 77], dtype=torch.int32)
+    want = torch.empty(5, 80)
+    plain_ops.embedding(table, ids, want)
+    got = torch.empty(5, 80, device="cuda")
+    ops.embedding(table.cuda(), ids.cuda(), got)
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,eps", [(80, 1e-4), (2048, 1e-5), (1000, 1e-6)])
+def test_add_rmsnorm(ops, dtype, hidden, eps):
+    torch.manual_seed(1)
+    residual = torch.randn(7, hidden) * 3
+    delta = torch.randn(7, hidden).to(dtype)
+    weight = 1 + 0.1 * torch.randn(hidden)
+    for use_delta, rows in ((True, None), (False, None), (False, torch.tensor([6, 0, 3], dtype=torch.int32))):
+        r_plain, r_gpu = residual.clone(), residual.clone().cuda()
+        n = 7 if rows is None else 3
+        want = torch.empty(n, hidden, dtype=dtype)
+        plain_ops.add_rmsnorm(r_plain, delta if use_delta else None, weight, eps, want, rows)
+        got = torch.empty(n, hidden, dtype=dtype, device="cuda")
+        ops.add_rmsnorm(r_gpu, delta.cuda() if use_delta else None, weight.cuda(), eps, got, None if rows is None else rows.cuda())
+        assert torch.allclose(r_gpu.cpu(), r_plain, atol=1e-6)
+        assert torch.allclose(got.cpu().float(), want.float(), atol=_tol(dtype, 8), rtol=_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul_and_add(ops, dtype):
+    torch.manual_seed(2)
+    gate_up = (torch.randn(5, 2 * 176) * 2).to(dtype)
+    want = torch.empty(5, 176, dtype=dtype)
+    plain_ops.silu_mul(gate_up, want)
+    got = torch.empty(5, 176, dtype=dtype, device="cuda")
+    ops.silu_mul(gate_up.cuda(), got)
+    assert torch.allclose(got.cpu().float(), want.float(), atol=_tol(dtype, 4), rtol=_tol(dtype))
+    residual = torch.randn(5, 176)
+    delta = torch.randn(5, 176).to(dtype)
+    r = residual.clone().cuda()
+    ops.add_(r, delta.cuda())
+    assert torch.allclose(r.cpu(), residual + delta.float(), atol=1e-6)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (37, 131, 80), (130, 70, 513), (3, 1000, 17)])
+def test_gemm_fp32_is_true_32_bit(ops, M, N, K):
+    torch.manual_seed(3)
+    x, w = torch.randn(M, K), torch.randn(N, K)
+    want = (x.double() @ w.double().T).float()
+    got = torch.empty(M, N, device="cuda")
+    ops.linear(x.cuda(), w.cuda(), got)
+    # a reduced-precision (tf32 / bf16) product would be off by ~1e-3 * sqrt(K) here
+    assert torch.allclose(got.cpu(), want, atol=2e-6 * K ** 0.5 * 4, rtol=1e-6)
+    # one row alone gives bit-identical numbers: the order of a row's sum does not depend on the batch
+    alone = torch.empty(1, N, device="cuda")
+    ops.linear(x[M - 1 :].cuda(), w.cuda(), alone)
+    assert torch.equal(alone[0], got[M - 1])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (37, 136, 80), (130, 72, 520), (64, 2048, 2048)])
+def test_linear_bf16(ops, M, N, K):
+    torch.manual_seed(4)
+    x, w = torch.randn(M, K).bfloat16(), torch.randn(N, K).bfloat16()
+    want = x.float() @ w.float().T
+    got = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.linear(x.cuda(), w.cuda(), got)
+    assert torch.allclose(got.cpu().float(), want, atol=1e-2 * K ** 0.5, rtol=1e-2)
+    got32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.linear(x.cuda(), w.cuda(), got32)
+    assert torch.allclose(got32.cpu(), want, atol=2e-5 * K ** 0.5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,rotary_dim,theta", [(4, 2, 16, 16, 16, 1e4), (6, 2, 32, 32, 32, 5e5), (3, 3, 48, 16, 24, 777.0), (8, 1, 128, 64, 128, 1e4)])
+def test_rope_store(ops, dtype, q_heads, kv_heads, head_dim, page_size, rotary_dim, theta):
+    rng = np.random.default_rng(5)
+    torch.manual_seed(5)
+    seq_lens, q_lens = [4100, 17, page_size + 1, 1], [5, 17, 2, 1]
+    qkv, pages, positions, token_seq, table = _paged_case(rng, dtype, seq_lens, q_lens, kv_heads, head_dim, page_size, q_heads)
+    exponent = (np.float32(-2.0) * np.arange(rotary_dim // 2, dtype=np.float32)) / np.float32(rotary_dim)
+    inv_freq = torch.from_numpy(np.power(np.float32(theta), exponent, dtype=np.float32))
+    for write in (True, False):
+        qkv_plain, pages_plain = qkv.clone(), pages.clone()
+        plain_ops.rope_store(qkv_plain, positions, token_seq, table, inv_freq, rotary_dim, pages_plain, q_heads, kv_heads, head_dim, page_size, write)
+        qkv_gpu, pages_gpu = qkv.clone().cuda(), pages.clone().cuda()
+        ops.rope_store(qkv_gpu, positions.cuda(), token_seq.cuda(), table.cuda(), inv_freq.cuda(), rotary_dim, pages_gpu, q_heads, kv_heads, head_dim, page_size, write)
+        q_width = q_heads * head_dim
+        # position 4099 with 32-bit angles: sine and cosine of the two sides may differ in the last bits
+        assert torch.allclose(qkv_gpu.cpu().float()[:, :q_width], qkv_plain.float()[:, :q_width], atol=_tol(dtype, 4) + 2e-4)
+        assert torch.equal(qkv_gpu.cpu()[:, q_width:], qkv_plain[:, q_width:])
+        assert torch.allclose(pages_gpu.cpu().float(), pages_plain.float(), atol=_tol(dtype, 4) + 2e-4)
+        if not write:
+            assert torch.equal(pages_gpu.cpu(), pages)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window", [(4, 2, 16, 16, 0), (6, 2, 32, 32, 0), (3, 3, 48, 16, 0), (8, 1, 128, 64, 0), (4, 4, 80, 16, 0), (4, 2, 64, 16, 37), (32, 4, 64, 64, 0)])
+def test_paged_attention(ops, dtype, q_heads, kv_heads, head_dim, page_size, window):
+    rng = np.random.default_rng(6)
+    torch.manual_seed(6)
+    seq_lens = [300, page_size, page_size + 1, 1, 2 * page_size - 1, 131]
+    q_lens = [7, page_size, 2, 1, 1, 131]
+    qkv, pages, positions, token_seq, table = _paged_case(rng, dtype, seq_lens, q_lens, kv_heads, head_dim, page_size, q_heads)
+    # one far key among hundreds: make a single early key of request 0 match its last query strongly
+    q_row = sum(q_lens[:1]) - 1
+    page, slot = int(table[0, 3 // page_size]), 3 % page_size
+    for h in range(q_heads):
+        qv = qkv.view(qkv.shape[0], -1, head_dim)[q_row, h].float()
+        pages[page, 0, h // (q_heads // kv_heads), slot] = (qv * (6.0 / max(1e-3, float(qv.norm()) ** 2) * head_dim ** 0.5)).to(dtype)
+    tokens = qkv.shape[0]
+    want = torch.empty(tokens, q_heads * head_dim, dtype=dtype)
+    plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)
+    got = torch.empty(tokens, q_heads * head_dim, dtype=dtype, device="cuda")
+    ops.paged_attention(qkv.cuda(), pages.cuda(), positions.cuda(), token_seq.cuda(), table.cuda(), got, q_heads, kv_heads, head_dim, page_size, window)
+    assert torch.allclose(got.cpu().float(), want.float(), atol=_tol(dtype, 2) + (2e-6 if dtype == torch.float32 else 0)), float((got.cpu().float() - want.float()).abs().max())
+
+
+def test_argmax_and_sampling(ops):
+    torch.manual_seed(7)
+    logits = torch.randn(6, 1000)
+    logits[0, 10] = logits[0, 700] = 9.0     # a tie: the lowest id wins
+    logits[1, 999] = 12.0
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.argmax(logits.cuda(), out)
+    want = torch.empty(6, dtype=torch.int32)
+    plain_ops.argmax(logits, want)
+    assert torch.equal(out.cpu(), want) and int(want[0]) == 10 and int(want[1]) == 999
+    assert ops.uniform_from(11, 5) == plain_ops.uniform_from(11, 5) == pytest.approx(ops.core().tlie_uniform_from(11, 5))
+    rows = 64
+    logits = torch.randn(rows, 131) * 2
+    temperature = torch.tensor([0.0, 0.8, 1.0, 1.5] * (rows // 4))
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.5, 0.3, 1.0, 0.7, 0.95] * (rows // 8))
+    seeds = torch.arange(rows, dtype=torch.int64) * 7 + 1
+    counters = torch.arange(rows, dtype=torch.int64) % 5
+    got = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample(logits.cuda(), temperature.cuda(), top_p.cuda(), seeds.cuda(), counters.cuda(), got)
+    want = torch.empty(rows, dtype=torch.int32)
+    plain_ops.sample(logits, temperature, top_p, seeds, counters, want)
+    # the two sides sum probabilities in different orders: a draw that lands within rounding of a
+    # boundary may fall on the neighbouring kept token, so demand near-total agreement, and exact for greedy rows
+    agree = (got.cpu() == want)
+    assert bool(agree[temperature == 0].all())
+    assert int(agree.sum()) >= rows - 2, (got.cpu(), want)
+    # the distribution: many draws of one row follow softmax(l / T) restricted by top_p
+    row = torch.tensor([2.0, 1.0, 0.5, -1.0, -3.0] + [-20.0] * 45)
+    n = 4096
+    got = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample(row.repeat(n, 1).cuda(), torch.full((n,), 0.7).cuda(), torch.full((n,), 0.8).cuda(), torch.full((n,), 3, dtype=torch.int64).cuda(), torch.arange(n, dtype=torch.int64).cuda(), got)
+    p = torch.softmax(row / 0.7, 0)
+    keep = p >= p[1]  # 0.8 is reached by the two most probable tokens
+    expect = torch.where(keep, p, torch.zeros_like(p)) / p[keep].sum()
+    freq = torch.bincount(got.cpu().long(), minlength=50).float() / n
+    assert float((freq - expect).abs().max()) < 0.03

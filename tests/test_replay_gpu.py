@@ -1,0 +1,74 @@
+"""The engine on the GPU, in 32-bit and in bfloat16, under every way of cutting the work, against the plain implementation."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_llama
+import trace_tools
+from tinyllama_inference_engine_b200 import EngineConfig
+from tinyllama_inference_engine_b200.engine.runner import ModelRunner
+
+pytestmark = pytest.mark.gpu
+
+# largest |difference| allowed, as a fraction of the largest |logit| of the request set
+TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
+LENGTHS = {"a": [1, 7, 33, 100, 128, 65], "b": [3, 19, 64, 100, 255, 130], "c": [2, 40, 77, 300, 129, 64]}
+
+
+@pytest.fixture(scope="module")
+def cases(model_folders):
+    out = {}
+    for key, folder in model_folders.items():
+        config, weights = plain_llama.load_model(folder)
+        requests = trace_tools.make_requests(config["vocab_size"], LENGTHS[key], seed=11)
+        full = {rid: plain_llama.forward(config, weights, tokens) for rid, tokens in requests.items()}
+        scale = max(float(v.abs().max()) for v in full.values())
+        out[key] = (folder, requests, full, scale)
+    return out
+
+
+def _runner(folder, dtype, max_tokens=2048, page_size=64):
+    return ModelRunner(folder, EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8, max_batch_tokens=128, poison_freed_pages=True))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "b", "c"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_replay(cases, key, dtype, cut):
+    folder, requests, full, scale = cases[key]
+    atol = TOLERANCE[dtype] * scale
+    page_size = 16 if key == "c" else 64
+    if cut == "mixed":
+        steps, peak = trace_tools.mixed(requests, seed=5, page_size=page_size)
+        runner = _runner(folder, dtype, max_tokens=peak, page_size=page_size)
+    else:
+        steps = {"whole": trace_tools.whole, "tail": trace_tools.tail_decode, "portions": trace_tools.portions}[cut](requests)
+        runner = _runner(folder, dtype, page_size=page_size)
+    worst = trace_tools.run_and_compare(runner, steps, full, atol=atol)
+    runner.cache.check()
+    assert not runner.cache.records
+    if cut == "mixed":
+        assert runner.cache.stats()["groups"][0]["reuses"] > 0
+    print(f"{key} {dtype} {cut}: worst {worst:.3e} of scale {scale:.3f}")
+
+
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_float32_rows_do_not_depend_on_the_cut(cases, key):
+    """In 32-bit every kernel sums a row in an order of its own, so two cuts agree to the last bit."""
+    folder, requests, full, scale = cases[key]
+    from tinyllama_inference_engine_b200.engine.replay import replay_step
+
+    rid = "r3"
+    tokens = requests[rid]
+    a = _runner(folder, "float32")
+    whole = replay_step(a, {"step": 0, "entries": [{"id": rid, "tokens": tokens, "want": list(range(len(tokens)))}], "end": [rid]})
+    b = _runner(folder, "float32")
+    rows = []
+    other = requests["r4"]
+    for i, token in enumerate(tokens):
+        entries = [{"id": rid, "tokens": [token], "want": [0]}]
+        if i < len(other):
+            entries.insert(0, {"id": "o", "tokens": [other[i]], "want": []})
+        rows.append(replay_step(b, {"step": i, "entries": entries, "end": []})[0])
+    assert torch.equal(torch.stack(rows), whole)
