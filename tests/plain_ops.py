@@ -55,7 +55,7 @@ def linear(x, weight, out) -> None:
 def rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim, pages, q_heads, kv_heads, head_dim, page_size, write_cache=True) -> None:
     tokens = qkv.shape[0]
     view = qkv.view(tokens, q_heads + 2 * kv_heads, head_dim)
-    rotated = view[:, : q_heads + kv_heads].float()
+    rotated = view[:, : q_heads + kv_heads].float().clone()
     if inv_freq is not None and rotary_dim > 0:
         half = rotary_dim // 2
         angle = positions.float()[:, None] * inv_freq[None, :]
