@@ -1,0 +1,146 @@
+"""Generality of the parts: a toy mixer with per-request state of its own, defined here, is registered,
+built into a model beside attention layers, and stepped, without touching the framework's files.
+
+The toy is no model of anyone's: s_t = decay * s_{t-1} + W_in x_t, y_t = W_out s_t, one state vector per request.
+"""
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_ops
+from tinyllama_inference_engine_b200 import EngineConfig
+from tinyllama_inference_engine_b200.config import Architecture, register_architecture, unregister_architecture
+from tinyllama_inference_engine_b200.engine.batch import StepEntry
+from tinyllama_inference_engine_b200.engine.runner import ModelRunner
+from tinyllama_inference_engine_b200.parts import CacheNeed, LayerSpec, Mixer, ModelSpec, OrderEntry, PartSpec, TensorSpec, register_part, unregister_part
+from tinyllama_inference_engine_b200.weights import write_random_model
+
+
+class DecayMixer(Mixer):
+    @classmethod
+    def tensor_specs(cls, spec, prefix):
+        h, s = spec["hidden_size"], spec["state_size"]
+        return [TensorSpec(f"{prefix}.in.weight", (s, h), std=0.1), TensorSpec(f"{prefix}.out.weight", (h, s), std=0.1)]
+
+    @classmethod
+    def cache_need(cls, spec):
+        return CacheNeed("state", state_shape=(spec["state_size"],))
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.w_in = weights.get(f"{prefix}.in.weight", torch.float32)
+        self.w_out = weights.get(f"{prefix}.out.weight", torch.float32)
+        self.decay = float(spec["decay"])
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty_like(x)
+        drive = x.float() @ self.w_in.T
+        start = 0
+        for slot, count in zip(ctx.host_state_slots, ctx.host_q_lens):  # every request's portion, in order
+            state = cache.state[slot]
+            for row in range(start, start + count):
+                state = self.decay * state + drive[row]
+                out[row] = (self.w_out @ state).to(x.dtype)
+            cache.state[slot] = state
+            start += count
+        return out
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    hidden_size: int = 48
+    state_size: int = 24
+    vocab_size: int = 97
+    intermediate_size: int = 80
+    decay: float = 0.9
+    max_position_embeddings: int = 160
+    architectures: tuple = ("ToyDecayForCausalLM",)
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: (tuple(v) if k == "architectures" else v) for k, v in data.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return {**asdict(self), "architectures": list(self.architectures)}
+
+
+def build_toy_spec(c: ToyConfig) -> ModelSpec:
+    norm = PartSpec("rmsnorm", {"size": c.hidden_size, "eps": 1e-5})
+    ff = PartSpec("gated_mlp", {"hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size, "activation": "silu"})
+    attention = PartSpec("attention", {"hidden_size": c.hidden_size, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16, "window": 0, "scale": None,
+                                       "position": PartSpec("rotary", {"rotary_dim": 16, "theta": 100.0})})
+    windowed = PartSpec("attention", {**attention.params, "window": 20})
+    decay = PartSpec("toy_decay", {"hidden_size": c.hidden_size, "state_size": c.state_size, "decay": c.decay})
+
+    def block(mixer):
+        return PartSpec("pre_norm_residual", {"mixer_norm": norm, "mixer_norm_name": "n1", "mixer": mixer, "mixer_name": "mix",
+                                              "feed_forward_norm": norm, "feed_forward_norm_name": "n2", "feed_forward": ff, "feed_forward_name": "ff"})
+
+    layers = (LayerSpec("toy.l0", block(attention)), LayerSpec("toy.l1", block(decay)), LayerSpec("toy.l2", block(windowed)))
+    # layer 1 runs twice (two cache streams of its own); the last run of layer 0 reads the keys its first run cached
+    order = (OrderEntry(0, cache=0), OrderEntry(1, cache=1), OrderEntry(2, cache=2), OrderEntry(1, cache=3), OrderEntry(0, cache=0, writes_cache=False))
+    return ModelSpec("ToyDecayForCausalLM", c.hidden_size, c.vocab_size, c.max_position_embeddings,
+                     PartSpec("token_embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size, "name": "toy.embed"}),
+                     layers, order, PartSpec("rmsnorm", {"size": c.hidden_size, "eps": 1e-5, "name": "toy.norm"}),
+                     PartSpec("linear_head", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size, "name": "toy.head", "tied_to": "toy.embed"}))
+
+
+@pytest.fixture()
+def toy_folder(tmp_path):
+    register_part("mixer", "toy_decay", DecayMixer, replace=True)
+    register_architecture(Architecture("ToyDecayForCausalLM", ToyConfig, build_toy_spec), replace=True)
+    yield write_random_model(tmp_path / "toy", ToyConfig(), seed=8, storage_dtype="bfloat16")
+    unregister_architecture("ToyDecayForCausalLM")
+    unregister_part("mixer", "toy_decay")
+
+
+def _check_toy(folder, device, dtype, fraction):
+    config = EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=320, max_requests=4, max_batch_tokens=64, device=device)
+    rng = np.random.default_rng(2)
+    requests = {name: [int(t) for t in rng.integers(0, 97, size=n)] for name, n in (("p", 61), ("q", 45), ("r", 30))}
+    whole = ModelRunner(folder, config)
+    groups = whole.cache.page_groups
+    assert [(g.need.window, g.streams) for g in groups] == [(0, [0]), (20, [2])] and [g.streams for g in whole.cache.state_groups] == [[1, 3]]
+    full = {}
+    for name, tokens in requests.items():
+        full[name] = whole.step([StepEntry(name, tokens, list(range(len(tokens))))]).cpu()
+        whole.finish(name)
+    atol = fraction * max(float(v.abs().max()) for v in full.values())  # a fraction of the largest |logit|
+    cut = ModelRunner(folder, config)
+    at = {name: 0 for name in requests}
+    sizes = iter([5, 2, 1, 9, 3, 1, 1, 16, 2, 7] * 20)
+    worst = 0.0
+    while any(at[n] < len(t) for n, t in requests.items()):
+        entries, rows = [], []
+        for name, tokens in requests.items():
+            if at[name] < len(tokens):
+                n = min(next(sizes), len(tokens) - at[name])
+                entries.append(StepEntry(name, tokens[at[name] : at[name] + n], [n - 1]))
+                rows.append(full[name][at[name] + n - 1])
+                at[name] += n
+        got = cut.step(entries).cpu()
+        worst = max(worst, float((got - torch.stack(rows)).abs().max()))
+        cut.cache.check()
+    assert worst <= atol, worst
+    # the windowed group gave pages back while the requests were still live
+    assert cut.cache.page_groups[1].pool.free_count > cut.cache.page_groups[0].pool.free_count
+    for name in requests:
+        cut.finish(name)
+    # a slot used again starts from a zero state: run r again after the others dirtied every slot
+    again = cut.step([StepEntry("again", requests["r"], [len(requests["r"]) - 1])]).cpu()
+    assert float((again[0] - full["r"][-1]).abs().max()) <= atol
+
+
+def test_toy_mixer_with_state_steps_on_cpu(toy_folder, monkeypatch):
+    plain_ops.install(monkeypatch)
+    _check_toy(toy_folder, "cpu", "float32", 2e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,fraction", [("float32", 2e-5), ("bfloat16", 2.5e-2)])
+def test_toy_mixer_with_state_steps_on_gpu(toy_folder, dtype, fraction):
+    _check_toy(toy_folder, "cuda:0", dtype, fraction)

@@ -232,6 +232,23 @@ class CacheManager:
     def free_pages(self) -> list[int]:
         return [group.pool.free_count for group in self.page_groups]
 
+    def max_total(self, request_id: object | None, free: list[int]) -> int:
+        """The most tokens the request could hold if it got ``free[g]`` more pages in every group g."""
+        record = self.records.get(request_id) if request_id is not None else None
+        best = 1 << 60
+        for group in self.page_groups:
+            held = len(record.tables.get(group.index, [])) if record is not None else 0
+            best = min(best, (held + free[group.index]) * self.page_size)
+        return best
+
+    def total_pages(self) -> list[int]:
+        return [group.pool.num_pages for group in self.page_groups]
+
+    def release_request(self, request_id: object) -> None:
+        """``release`` that tolerates a request which never ran (nothing to give back)."""
+        if request_id in self.records:
+            self.release(request_id)
+
     def stats(self) -> dict:
         return {
             "live_requests": len(self.records),

@@ -1,0 +1,221 @@
+"""Command line in the manner of the reference's binaries.
+
+    tinyllama_b200 generate  MODEL_DIR PROMPT MAX_TOKENS [GOLDEN_JSON]
+    tinyllama_b200 logits    MODEL_DIR PROMPT
+    tinyllama_b200 benchmark MODEL_DIR CONTEXT OUTPUT_TOKENS WARMUP SAMPLES
+    tinyllama_b200 reference MODEL_DIR PROMPT MAX_TOKENS [EXPECTED_FIRST_TOKEN]
+    tinyllama_b200 random-model OUT_DIR CONFIG_JSON SEED
+
+The first three are the subcommands of ``tinyllama_cuda`` (app/cuda_reference.cu:476-521)
+with the same positional arguments and JSON on standard output; ``reference`` prints
+``token_ids:`` / ``text:`` like ``tinyllama_reference`` (app/reference_cli.cpp:40-125).
+Errors are one JSON object ``{"error": {"code", "message"}}`` on standard error and
+exit status 1 (app/reference_cli.cpp:20-25).  PROMPT is text when MODEL_DIR holds a
+``tokenizer.model`` (SentencePiece, BOS prepended as src/tokenizer.cpp:103-105 does),
+otherwise a list of token ids separated by commas or spaces.  Options, before or
+after the positionals: ``--dtype bfloat16|float32``, ``--temperature``, ``--top-p``,
+``--seed``, ``--batch``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from pathlib import Path
+
+from .errors import EngineError
+
+USAGE = __doc__.split("\n\n")[1]
+
+
+def _positive(text: str, name: str, minimum: int = 1) -> int:
+    try:
+        value = int(text)
+    except ValueError:
+        value = None
+    if value is None or value < minimum:
+        raise EngineError(f"{name} must be an integer >= {minimum}", code="invalid_argument")
+    return value
+
+
+class _Tokens:
+    """Text <-> ids with the folder's SentencePiece model if there is one, else ids as text."""
+
+    def __init__(self, model_dir: Path, bos_id):
+        self.processor = None
+        self.bos_id = bos_id
+        path = model_dir / "tokenizer.model"
+        if path.exists():
+            try:
+                import sentencepiece
+
+                self.processor = sentencepiece.SentencePieceProcessor(model_file=str(path))
+            except Exception as exc:  # noqa: BLE001
+                raise EngineError(f"unable to load tokenizer: {exc}", code="tokenizer") from exc
+
+    def encode(self, prompt: str) -> list[int]:
+        if self.processor is not None:
+            ids = list(self.processor.encode(prompt))
+            return ([self.bos_id] if self.bos_id is not None else []) + ids
+        try:
+            ids = [int(piece) for piece in prompt.replace(",", " ").split()]
+        except ValueError:
+            raise EngineError("PROMPT must be token ids (no tokenizer.model in MODEL_DIR)", code="tokenizer") from None
+        if not ids:
+            raise EngineError("PROMPT holds no token", code="invalid_argument")
+        return ids
+
+    def decode(self, ids: list[int]) -> str:
+        if self.processor is not None:
+            return self.processor.decode(ids)
+        return " ".join(str(i) for i in ids)
+
+
+def _engine(args, max_cache_tokens: int, max_requests: int = 1):
+    from . import EngineConfig
+    from .engine.api import Engine
+
+    config = EngineConfig(dtype=args.dtype, max_cache_tokens=max(64, -(-max_cache_tokens // 64) * 64), max_requests=max(1, max_requests),
+                          max_batch_tokens=args.max_batch_tokens)
+    return Engine(args.model_dir, config)
+
+
+def _generate(args) -> int:
+    from .config import load_model_config
+    from .engine.request import SamplingParams
+
+    max_tokens = _positive(args.rest[1], "MAX_TOKENS")
+    _, model_config = load_model_config(args.model_dir)
+    tokens = _Tokens(Path(args.model_dir), getattr(model_config, "bos_token_id", None))
+    prompt = tokens.encode(args.rest[0])
+    engine = _engine(args, len(prompt) + max_tokens)
+    started = time.perf_counter()
+    request_id = engine.add_request(prompt, SamplingParams(max_tokens=max_tokens, temperature=args.temperature, top_p=args.top_p, seed=args.seed))
+    engine.step()
+    prefill_ms = (time.perf_counter() - started) * 1e3
+    while engine.has_unfinished():
+        engine.step()
+    total_ms = (time.perf_counter() - started) * 1e3
+    generated = engine.requests[request_id].generated
+    if args.command == "reference":
+        if len(args.rest) > 2 and generated[0] != _positive(args.rest[2], "EXPECTED_FIRST_TOKEN", 0):
+            print("first generated token did not match expectation", file=sys.stderr)
+            return 1
+        print("token_ids:" + "".join(f" {t}" for t in generated))
+        print("text: " + tokens.decode(generated))
+        return 0
+    result = {"prompt_tokens": len(prompt), "generated_tokens": generated, "text": tokens.decode(generated),
+              "prefill_ms": prefill_ms, "decode_ms": total_ms - prefill_ms, "dtype": args.dtype}
+    if len(args.rest) > 2:
+        golden = json.loads(Path(args.rest[2]).read_text())
+        expected = golden.get("generated_tokens", golden.get("greedy_token_ids"))
+        result["golden_match"] = expected is not None and list(expected)[: len(generated)] == generated
+        if not result["golden_match"]:
+            print(json.dumps(result))
+            raise EngineError("generated tokens differ from the golden file", code="numerical")
+    print(json.dumps(result))
+    return 0
+
+
+def _logits(args) -> int:
+    from .config import load_model_config
+    from .engine.batch import StepEntry
+
+    _, model_config = load_model_config(args.model_dir)
+    prompt = _Tokens(Path(args.model_dir), getattr(model_config, "bos_token_id", None)).encode(args.rest[0])
+    engine = _engine(args, len(prompt))
+    logits = engine.runner.step([StepEntry("logits", prompt, [len(prompt) - 1])])
+    print(json.dumps({"prompt_tokens": len(prompt), "logits": logits[0].cpu().tolist()}))
+    return 0
+
+
+def _benchmark(args) -> int:
+    """CONTEXT prompt tokens (seeded random ids), OUTPUT_TOKENS greedy tokens, per-sample TTFT / TPOT / tokens per second."""
+    import numpy as np
+    import torch
+
+    from .engine.request import SamplingParams
+
+    context, output_tokens = _positive(args.rest[0], "CONTEXT"), _positive(args.rest[1], "OUTPUT_TOKENS")
+    warmup, samples = _positive(args.rest[2], "WARMUP", 0), _positive(args.rest[3], "SAMPLES")
+    engine = _engine(args, args.batch * (context + output_tokens + 64), args.batch)
+    vocab = engine.runner.spec.vocab_size
+    rng = np.random.default_rng(0)
+    prompts = [[int(t) for t in rng.integers(0, vocab, size=context)] for _ in range(args.batch)]
+    records = []
+    for index in range(warmup + samples):
+        ids = [engine.add_request(p, SamplingParams(max_tokens=output_tokens)) for p in prompts]
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        first = None
+        while engine.has_unfinished():
+            engine.step()
+            if first is None and all(engine.requests[i].generated for i in ids):
+                torch.cuda.synchronize()
+                first = time.perf_counter()
+        torch.cuda.synchronize()
+        ended = time.perf_counter()
+        generated = [engine.requests.pop(i).generated for i in ids]
+        if index >= warmup:
+            decode_tokens = args.batch * (output_tokens - 1)
+            records.append({
+                "ttft_ms": (first - started) * 1e3,
+                "tpot_ms": (ended - first) * 1e3 / max(1, output_tokens - 1),
+                "decode_tokens_per_second": decode_tokens / (ended - first) if decode_tokens else 0.0,
+                "total_tokens_per_second": args.batch * output_tokens / (ended - started),
+                "tokens": generated[0][:8],
+            })
+    deterministic = all(r["tokens"] == records[0]["tokens"] for r in records)
+    median = lambda key: float(np.median([r[key] for r in records]))  # noqa: E731
+    print(json.dumps({
+        "context": context, "output_tokens": output_tokens, "batch": args.batch, "warmup": warmup, "samples": samples, "dtype": args.dtype,
+        "median_ttft_ms": median("ttft_ms"), "median_tpot_ms": median("tpot_ms"),
+        "median_decode_tokens_per_second": median("decode_tokens_per_second"), "median_total_tokens_per_second": median("total_tokens_per_second"),
+        "deterministic": deterministic, "device": torch.cuda.get_device_name(0), "samples_detail": records,
+    }))
+    return 0
+
+
+def _random_model(args) -> int:
+    from .config import architecture_for
+    from .weights import write_random_model
+
+    data = json.loads(Path(args.rest[0]).read_text())
+    config = architecture_for(data).config_class.from_dict(data)
+    folder = write_random_model(args.model_dir, config, _positive(args.rest[1], "SEED", 0))
+    print(json.dumps({"model_dir": str(folder)}))
+    return 0
+
+
+_COMMANDS = {"generate": (_generate, (2, 3)), "reference": (_generate, (2, 3)), "logits": (_logits, (1, 1)),
+             "benchmark": (_benchmark, (4, 4)), "random-model": (_random_model, (2, 2))}
+
+
+def main(argv: list[str] | None = None) -> int:
+    parser = argparse.ArgumentParser(prog="tinyllama_b200", usage=USAGE, add_help=True)
+    parser.add_argument("command", choices=sorted(_COMMANDS))
+    parser.add_argument("model_dir")
+    parser.add_argument("rest", nargs="*")
+    parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    parser.add_argument("--temperature", type=float, default=0.0)
+    parser.add_argument("--top-p", type=float, default=1.0)
+    parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--batch", type=int, default=1)
+    parser.add_argument("--max-batch-tokens", type=int, default=2048)
+    try:
+        args = parser.parse_intermixed_args(argv)
+    except SystemExit as exc:
+        return int(exc.code or 0) and 1
+    handler, (low, high) = _COMMANDS[args.command]
+    try:
+        if not low <= len(args.rest) <= high:
+            raise EngineError("invalid tinyllama_b200 command or arguments\n" + USAGE, code="invalid_argument")
+        return handler(args)
+    except EngineError as exc:
+        print(json.dumps(exc.to_json()), file=sys.stderr)
+        return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
