@@ -1,0 +1,113 @@
+"""Generation through the entry point on the GPU: greedy ids, long decoding, first tokens, tight caches, graphs."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+import trace_tools
+from tinyllama_inference_engine_b200 import EngineConfig
+from tinyllama_inference_engine_b200.engine.api import Engine
+from tinyllama_inference_engine_b200.engine.request import SamplingParams
+from tinyllama_inference_engine_b200.engine.runner import ModelRunner
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompts(vocab, lengths, seed=1):
+    rng = np.random.default_rng(seed)
+    return [[int(t) for t in rng.integers(0, vocab, size=n)] for n in lengths]
+
+
+def _engine(folder, **options):
+    base = dict(dtype="float32", page_size=16, max_cache_tokens=1024, max_requests=8, max_batch_tokens=48)
+    base.update(options)
+    return Engine(folder, EngineConfig(**base))
+
+
+def _agrees_up_to_near_ties(config, weights, prompt, got, want, fraction):
+    """Equal ids, or at the first difference the chosen token's plain logit is within ``fraction`` of the scale of the top."""
+    tokens = list(prompt)
+    for a, b in zip(got, want):
+        if a != b:
+            logits = plain_llama.forward(config, weights, tokens)[-1]
+            return float(logits.max() - logits[a]) <= fraction * float(logits.abs().max())
+        tokens.append(a)
+    return True
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("key", ["a", "b", "c"])
+def test_greedy_generation_through_the_entry_point(model_folders, key, graphs):
+    config, weights = plain_llama.load_model(model_folders[key])
+    prompts = _prompts(config["vocab_size"], [1, 2, 7, 33])
+    want = [plain_llama.generate_greedy(config, weights, p, 16) for p in prompts]
+    engine = _engine(model_folders[key], use_cuda_graphs=graphs)
+    got = [r.generated_tokens for r in engine.generate(prompts, SamplingParams(max_tokens=16))]
+    assert got == want
+    engine.runner.cache.check()
+    bf16 = _engine(model_folders[key], dtype="bfloat16", use_cuda_graphs=graphs)
+    got = [r.generated_tokens for r in bf16.generate(prompts, SamplingParams(max_tokens=16))]
+    for prompt, g, w in zip(prompts, got, want):
+        assert _agrees_up_to_near_ties(config, weights, prompt, g, w, 0.03)
+
+
+def test_graph_and_eager_decoding_agree_and_sampling_is_seeded(model_folders):
+    config, _ = plain_llama.load_model(model_folders["b"])
+    prompts = _prompts(config["vocab_size"], [5, 40, 17, 64, 9], seed=4)
+    params = [SamplingParams(max_tokens=20 + 7 * i, temperature=0.9, top_p=0.9, seed=i) for i in range(5)]
+    eager = [r.generated_tokens for r in _engine(model_folders["b"], use_cuda_graphs=False).generate(prompts, params)]
+    graph_engine = _engine(model_folders["b"], use_cuda_graphs=True)
+    graphed = [r.generated_tokens for r in graph_engine.generate(prompts, params)]
+    assert graphed == eager
+    assert graph_engine._sessions, "decode steps should have gone through a graph session"
+    alone = [_engine(model_folders["b"]).generate([p], [q])[0].generated_tokens for p, q in zip(prompts, params)]
+    assert alone == eager  # a request's draws do not depend on the batch
+    assert all(len(g) == p.max_tokens for g, p in zip(eager, params))
+
+
+def test_long_decoding_stays_right(model_folders):
+    """One token of prompt, then 250 decoded one by one: every step's logits against the plain implementation."""
+    folder = model_folders["b"]
+    config, weights = plain_llama.load_model(folder)
+    requests = trace_tools.make_requests(config["vocab_size"], [251], seed=21)
+    full = {rid: plain_llama.forward(config, weights, tokens) for rid, tokens in requests.items()}
+    scale = max(float(v.abs().max()) for v in full.values())
+    for dtype, fraction in (("float32", 2e-5), ("bfloat16", 2.5e-2)):
+        runner = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=256, max_requests=2, max_batch_tokens=16))
+        trace_tools.run_and_compare(runner, trace_tools.tail_decode(requests, tail=250), full, atol=fraction * scale)
+
+
+def test_tight_cache_preempts_and_still_gives_the_same_tokens(model_folders):
+    config, _ = plain_llama.load_model(model_folders["a"])
+    prompts = _prompts(config["vocab_size"], [30, 30, 19, 25], seed=3)
+    params = [SamplingParams(max_tokens=40, temperature=0.7, top_p=0.95, seed=50 + i) for i in range(4)]
+    roomy = [r.generated_tokens for r in _engine(model_folders["a"]).generate(prompts, params)]
+    tight_engine = _engine(model_folders["a"], max_cache_tokens=144)
+    tight = [r.generated_tokens for r in tight_engine.generate(prompts, params)]
+    assert tight_engine.metrics()["preemptions"] > 0 and tight == roomy
+    tight_engine.runner.cache.check()
+    assert tight_engine.runner.cache.free_pages() == tight_engine.runner.cache.total_pages()
+
+
+def test_command_line_generates_on_the_gpu(model_folders, capsys):
+    import json
+
+    from tinyllama_inference_engine_b200.cli import main
+
+    config, weights = plain_llama.load_model(model_folders["a"])
+    prompt = _prompts(config["vocab_size"], [6], seed=2)[0]
+    text = ",".join(map(str, prompt))
+    assert main(["generate", str(model_folders["a"]), text, "8", "--dtype", "float32"]) == 0
+    result = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    want = plain_llama.generate_greedy(config, weights, prompt, 8)
+    assert result["generated_tokens"] == want and result["prompt_tokens"] == 6
+    assert main(["reference", str(model_folders["a"]), text, "8", str(want[0]), "--dtype", "float32"]) == 0
+    assert capsys.readouterr().out.splitlines()[0] == "token_ids:" + "".join(f" {t}" for t in want)
+    assert main(["logits", str(model_folders["a"]), text, "--dtype", "float32"]) == 0
+    logits = torch.tensor(json.loads(capsys.readouterr().out)["logits"])
+    assert torch.allclose(logits, plain_llama.forward(config, weights, prompt)[-1], atol=1e-5)
+    assert main(["benchmark", str(model_folders["a"]), "20", "6", "1", "2", "--batch", "2"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report["deterministic"] and report["median_decode_tokens_per_second"] > 0

@@ -196,3 +196,25 @@ TLIE_EXPORT int tlie_sample(const float* logits, int rows, int vocab, const floa
 TLIE_EXPORT float tlie_uniform_from(long long seed, long long counter) {
   return uniform_from((unsigned long long)seed, (unsigned long long)counter);
 }
+
+// After a decode step: the sampled tokens become the next step's inputs and every request
+// moves one position on.  Lets a run of decode steps stay on the device.
+__global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
+                                      int* __restrict__ positions, int* __restrict__ seq_lens,
+                                      int* __restrict__ first_positions, long long* __restrict__ counters, int count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  token_ids[i] = sampled[i];
+  positions[i] += 1;
+  seq_lens[i] += 1;
+  first_positions[i] += 1;
+  counters[i] += 1;
+}
+
+TLIE_EXPORT int tlie_decode_advance(int* token_ids, const int* sampled, int* positions, int* seq_lens,
+                                    int* first_positions, long long* counters, int count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  decode_advance_kernel<<<(count + 127) / 128, 128, 0, stream>>>(token_ids, sampled, positions, seq_lens,
+                                                                  first_positions, counters, count);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,159 @@
+"""A set of requests decoding one token per step, replayed as one CUDA graph.
+
+A decode step of this model is some hundred small kernels; launched one by one the
+host cannot keep up with a B200 (the reference issues ~332 launches per token,
+src/cuda/model.cu:406-475).  A session keeps the step's metadata (tokens, positions,
+block tables, sampling options) in device buffers of fixed address, captures
+forward + sampling + "move on by one position" once, and replays it.  Between
+replays the host only reserves a page when a request crosses a page edge and copies
+the changed block-table rows.  The graph's launch shapes depend on the number of
+requests and on static limits only, never on the current lengths.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..errors import BatchError
+from .batch import StepContext
+
+
+class DecodeSession:
+    def __init__(self, runner, count: int, use_graph: bool = True):
+        self.runner = runner
+        self.cache = runner.cache
+        self.request_ids: list = []
+        self.count = count
+        device = runner.device
+        width = self.cache.table_width
+        groups = len(self.cache.page_groups)
+        # one int32 buffer: [tokens | positions | token_seq | seq_starts | seq_lens | first_positions | slots | want | tables...]
+        sizes = [count, count, count, count + 1, count, count, count, count] + [count * width] * groups
+        self._host = torch.zeros(sum(sizes), dtype=torch.int32).pin_memory()
+        self._device = torch.zeros(sum(sizes), dtype=torch.int32, device=device)
+        offsets = [0]
+        for size in sizes:
+            offsets.append(offsets[-1] + size)
+        self._offsets = offsets
+        view = lambda buffer, i: buffer[offsets[i] : offsets[i + 1]]  # noqa: E731
+        self.h_tokens, self.h_positions = view(self._host, 0), view(self._host, 1)
+        self.h_tables = [view(self._host, 8 + g).view(count, width) for g in range(groups)]
+        view(self._host, 2).copy_(torch.arange(count))
+        view(self._host, 3).copy_(torch.arange(count + 1))
+        view(self._host, 7).copy_(torch.arange(count))
+        d = [view(self._device, i) for i in range(8)]
+        self.d_tables = [view(self._device, 8 + g).view(count, width) for g in range(groups)]
+        self.sampled = torch.zeros(count, dtype=torch.int32, device=device)
+        self.temperature = torch.zeros(count, dtype=torch.float32, device=device)
+        self.top_p = torch.ones(count, dtype=torch.float32, device=device)
+        self.seeds = torch.zeros(count, dtype=torch.int64, device=device)
+        self.counters = torch.zeros(count, dtype=torch.int64, device=device)
+        self.ctx = StepContext(
+            num_tokens=count, num_seqs=count, token_ids=d[0], positions=d[1], token_seq=d[2], seq_starts=d[3], seq_lens=d[4],
+            first_positions=d[5], state_slots=d[6], want_rows=d[7], block_tables=self.d_tables, request_ids=self.request_ids,
+            host_q_lens=[1] * count, host_first_positions=[0] * count, host_state_slots=[0] * count, max_q_len=1,
+            max_seq_len=runner.spec.max_positions,
+        )
+        self.positions = [0] * count      # host mirror: position of the token each request runs next
+        self.use_graph = use_graph
+        self._fresh = True
+        self._loaded = False
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.kernels_per_step = 0
+
+    # --- loading -----------------------------------------------------------------------------
+    def load(self, request_ids: list, tokens: list[int], params: list | None = None, draw_indices: list[int] | None = None) -> None:
+        """Bind ``count`` live requests: each one's next token (at the position its cache has reached) and sampling options."""
+        if len(request_ids) != self.count or len(set(request_ids)) != self.count:
+            raise BatchError(f"this decode session holds exactly {self.count} different requests")
+        self.request_ids = list(request_ids)
+        self.ctx.request_ids = self.request_ids
+        self._fresh = True
+        slots = []
+        for i, request_id in enumerate(self.request_ids):
+            if not self.cache.has(request_id):
+                raise BatchError(f"request {request_id!r} is not live; a decode session continues requests that were prefilled")
+            self.positions[i] = self.cache.computed(request_id)
+            slots.append(self.cache.records[request_id].slot)
+        self.h_tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
+        self.h_positions.copy_(torch.tensor(self.positions, dtype=torch.int32))
+        o = self._offsets
+        self._host[o[4] : o[5]].copy_(self.h_positions + 1)   # seq_lens
+        self._host[o[5] : o[6]].copy_(self.h_positions)       # first_positions
+        self._host[o[6] : o[7]].copy_(torch.tensor(slots, dtype=torch.int32))
+        self.ctx.host_state_slots = slots
+        self._reserve_and_fill_tables()
+        self._fresh = False
+        self._loaded = True
+        self._device.copy_(self._host, non_blocking=True)
+        if params is not None:
+            self.temperature.copy_(torch.tensor([p.temperature for p in params], dtype=torch.float32))
+            self.top_p.copy_(torch.tensor([p.top_p for p in params], dtype=torch.float32))
+            self.seeds.copy_(torch.tensor([p.seed for p in params], dtype=torch.int64))
+            self.counters.copy_(torch.tensor(draw_indices or [0] * self.count, dtype=torch.int64))
+
+    def _reserve_and_fill_tables(self) -> bool:
+        """Pages for this step's positions; returns whether any block-table row changed."""
+        changed = False
+        for i, request_id in enumerate(self.request_ids):
+            before = [len(self.cache.records[request_id].tables.get(g.index, [])) for g in self.cache.page_groups]
+            self.cache.reserve(request_id, self.positions[i] + 1)
+            for g, group in enumerate(self.cache.page_groups):
+                table = self.cache.records[request_id].tables.get(group.index, [])
+                if len(table) != before[g] or self._fresh:
+                    row = self.h_tables[g][i]
+                    row.fill_(-1)
+                    row[: len(table)] = torch.tensor(table, dtype=torch.int32)
+                    changed = True
+        return changed
+
+    # --- stepping ----------------------------------------------------------------------------
+    def _body(self) -> None:
+        caches = self.cache.layer_caches(self.d_tables)
+        self.logits = self.runner.model.forward(self.ctx, caches)
+        ops.sample(self.logits, self.temperature, self.top_p, self.seeds, self.counters, self.sampled)
+        c = self.ctx
+        ops.decode_advance(c.token_ids, self.sampled, c.positions, c.seq_lens, c.first_positions, self.counters)
+
+    def set_tokens(self, tokens: list[int]) -> None:
+        """Host tokens in: the step's input ids come from pinned host memory."""
+        self.h_tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
+        self._device[: self.count].copy_(self.h_tokens, non_blocking=True)
+
+    def step(self) -> torch.Tensor:
+        """One decode step for every request; returns the sampled tokens (device, int32).
+
+        The tokens run are those on the device: the ones loaded, or the previous step's samples.
+        """
+        if not self._loaded:  # load() already reserved and copied the tables of its first step
+            if self._reserve_and_fill_tables():
+                o = self._offsets
+                self._device[o[8] :].copy_(self._host[o[8] :], non_blocking=True)
+        self._loaded = False
+        if not self.use_graph:
+            self._body()
+        elif self.graph is None:
+            before = ops.launch_count
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                self._body()  # warm-up outside capture: workspaces, library handles
+                # the warm-up ran the step; put the metadata back before capturing the same step
+                self._device.copy_(self._host, non_blocking=True)
+                self.counters -= 1
+            torch.cuda.current_stream().wait_stream(stream)
+            self.kernels_per_step = ops.launch_count - before
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._body()
+            # capture does not run anything: the step itself is the first replay
+            self.graph.replay()
+        else:
+            self.graph.replay()
+        for i, request_id in enumerate(self.request_ids):
+            self.positions[i] += 1
+            self.cache.advance(request_id, self.positions[i])
+        self.runner.steps += 1
+        self.runner.tokens_run += self.count
+        return self.sampled

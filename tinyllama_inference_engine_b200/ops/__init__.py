@@ -206,6 +206,15 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
     )
 
 
+def decode_advance(token_ids, sampled, positions, seq_lens, first_positions, counters) -> None:
+    """token_ids = sampled; positions, seq_lens, first_positions and counters move on by one."""
+    _check(
+        core().tlie_decode_advance(_i32(token_ids, "token_ids"), _i32(sampled, "sampled"), _i32(positions, "positions"), _i32(seq_lens, "seq_lens"),
+                                   _i32(first_positions, "first_positions"), _ptr(counters), c_int(token_ids.shape[0]), _stream()),
+        "decode_advance",
+    )
+
+
 def uniform_from(seed: int, counter: int) -> float:
     """The uniform number in [0, 1) that draw ``counter`` of a request with ``seed`` uses."""
     mask = (1 << 64) - 1
