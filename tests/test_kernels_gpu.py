@@ -201,3 +201,75 @@ def test_argmax_and_sampling(ops):
     expect = torch.where(keep, p, torch.zeros_like(p)) / p[keep].sum()
     freq = torch.bincount(got.cpu().long(), minlength=50).float() / n
     assert float((freq - expect).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window", [
+    (32, 4, 64, 64, 0), (8, 8, 128, 64, 0), (32, 8, 128, 16, 0), (4, 2, 16, 16, 0), (6, 2, 32, 32, 0), (3, 3, 48, 16, 0),
+    (16, 1, 64, 64, 0), (8, 2, 64, 32, 100), (10, 2, 80, 16, 33),
+])
+@pytest.mark.parametrize("splits", [1, 3, 16])
+def test_decode_attention_split_kv(ops, q_heads, kv_heads, head_dim, page_size, window, splits):
+    """The tensor-core decode kernel against the plain function: lengths at page and tile edges, one far key that dominates."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    rng = np.random.default_rng(8)
+    torch.manual_seed(8)
+    seq_lens = [1, 31, 32, 33, 64, 65, 127, 129, 700, 1153, 2 * page_size, 2 * page_size + 1]
+    qkv, pages, positions, token_seq, table = _paged_case(rng, torch.bfloat16, seq_lens, [1] * len(seq_lens), kv_heads, head_dim, page_size, q_heads)
+    for row in (8, 9):  # key 3 of the long requests matches every head's query strongly (only visible without a window)
+        page, slot = int(table[row, 3 // page_size]), 3 % page_size
+        for h in range(q_heads):
+            qv = qkv.view(qkv.shape[0], -1, head_dim)[row, h].float()
+            pages[page, 0, h // (q_heads // kv_heads), slot] = (qv * (6.0 * head_dim ** 0.5 / float(qv.norm()) ** 2)).bfloat16()
+    want = torch.empty(len(seq_lens), q_heads * head_dim, dtype=torch.bfloat16)
+    plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)
+    got = torch.empty(len(seq_lens), q_heads * head_dim, dtype=torch.bfloat16, device="cuda")
+    pages_gpu = pages.cuda()
+    held = set(int(p) for p in table.flatten() if p >= 0)
+    for page in range(pages.shape[0]):   # pages no request holds, and slots past a request's end: reading them would show
+        if page not in held:
+            pages_gpu[page] = float("nan")
+    for i, n in enumerate(seq_lens):
+        if n % page_size:
+            pages_gpu[int(table[i, n // page_size]), :, :, n % page_size :] = float("nan")
+    fast.decode_attention(qkv.cuda(), pages_gpu, positions.cuda(), table.cuda(), got, q_heads, kv_heads, head_dim, page_size, window, head_dim ** -0.5, splits)
+    error = (got.cpu().float() - want.float()).abs().max(1).values
+    assert float(error.max()) <= 1.6e-2 * 2, error
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window", [
+    (32, 4, 64, 64, 0), (8, 8, 128, 64, 0), (4, 2, 16, 16, 0), (6, 2, 32, 32, 0), (3, 3, 48, 16, 0), (8, 2, 64, 32, 100), (10, 2, 80, 16, 33), (4, 1, 96, 16, 70),
+])
+def test_prefill_attention_flash(ops, q_heads, kv_heads, head_dim, page_size, window):
+    """The tensor-core prompt kernel against the plain function: portions that start anywhere, tile and page edges, single rows."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    rng = np.random.default_rng(9)
+    torch.manual_seed(9)
+    seq_lens = [300, 64, 65, 1, 127, 131, 700, 2, 129]
+    q_lens = [300, 64, 2, 1, 1, 131, 70, 2, 65]
+    qkv, pages, positions, token_seq, table = _paged_case(rng, torch.bfloat16, seq_lens, q_lens, kv_heads, head_dim, page_size, q_heads)
+    row = sum(q_lens[:6]) + 69  # the last row of the request of 700: key 5 far behind it dominates (if no window hides it)
+    page, slot = int(table[6, 5 // page_size]), 5 % page_size
+    for h in range(q_heads):
+        qv = qkv.view(qkv.shape[0], -1, head_dim)[row, h].float()
+        pages[page, 0, h // (q_heads // kv_heads), slot] = (qv * (6.0 * head_dim ** 0.5 / float(qv.norm()) ** 2)).bfloat16()
+    tokens = qkv.shape[0]
+    want = torch.empty(tokens, q_heads * head_dim, dtype=torch.bfloat16)
+    plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)
+    starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    firsts = np.array([s - q for s, q in zip(seq_lens, q_lens)], dtype=np.int32)
+    tiles = [[i, int(starts[i]) + off] for i, q in enumerate(q_lens) for off in range(0, q, 64)]
+    pages_gpu = pages.cuda()
+    held = set(int(p) for p in table.flatten() if p >= 0)
+    for page in range(pages.shape[0]):
+        if page not in held:
+            pages_gpu[page] = float("nan")
+    for i, n in enumerate(seq_lens):
+        if n % page_size:
+            pages_gpu[int(table[i, n // page_size]), :, :, n % page_size :] = float("nan")
+    got = torch.full((tokens, q_heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    fast.prefill_attention(qkv.cuda(), pages_gpu, torch.tensor(tiles, dtype=torch.int32).cuda(), torch.from_numpy(starts).cuda(), torch.from_numpy(firsts).cuda(),
+                           table.cuda(), got, q_heads, kv_heads, head_dim, page_size, window, head_dim ** -0.5)
+    error = (got.cpu().float() - want.float()).abs().max(1).values
+    assert float(error.max()) <= 1.6e-2 * 2, (int(error.argmax()), error.max())

@@ -6,6 +6,9 @@ from dataclasses import dataclass, field
 import torch
 
 
+ATTENTION_TILE_ROWS = 64
+
+
 @dataclass
 class StepEntry:
     """The next tokens of one request and the places among them whose logits are wanted."""
@@ -28,6 +31,8 @@ class StepContext:
       state_slots[B]              the request's slot in per-request state tensors
       want_rows[W]                rows whose logits are returned, in entry and want order
       block_tables[g][B, width]   page ids of every entry in page group g (-1: none)
+      attn_tiles[N, 2]            (entry, first row) of every run of up to 64 consecutive rows of one entry:
+                                  the work list of the prompt-attention kernel
     """
 
     num_tokens: int
@@ -48,6 +53,7 @@ class StepContext:
     host_state_slots: list[int]
     max_q_len: int
     max_seq_len: int
+    attn_tiles: torch.Tensor | None = None
 
     @property
     def decode_only(self) -> bool:
@@ -72,7 +78,11 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         want_rows += [start + w for w in entry.want]
         seq_starts.append(start + len(entry.tokens))
     seq_lens = [f + n for f, n in zip(first_positions, q_lens)]
-    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows]
+    tiles: list[int] = []
+    for index, count in enumerate(q_lens):
+        for offset in range(0, count, ATTENTION_TILE_ROWS):
+            tiles += [index, seq_starts[index] + offset]
+    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows, tiles]
     flat: list[int] = []
     offsets = []
     for section in sections:
@@ -96,5 +106,5 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         first_positions=views[5], state_slots=views[6], want_rows=views[7] if want_rows else None,
         block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=q_lens,
         host_first_positions=list(first_positions), host_state_slots=list(slots),
-        max_q_len=max(q_lens), max_seq_len=max(seq_lens),
+        max_q_len=max(q_lens), max_seq_len=max(seq_lens), attn_tiles=views[8].view(-1, 2),
     )

@@ -5,15 +5,29 @@ and compiled only for what a model needs.
 """
 from __future__ import annotations
 
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
 import torch
 
 from ..errors import KernelError
+from .build import build_library, load_library
 
 library_gemm_calls = 0  # vendor-library matrix products issued (not this engine's kernels)
+SM_COUNT = 148
+DEFAULT_HEAD_DIMS = (64, 128)
+_scratch: dict[torch.device, list[torch.Tensor]] = {}
 
 
 def build_all() -> list:
-    return []
+    built = [build_library(f"tlie_attn_decode_d{d}", ["attention_decode.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
+    built += [build_library(f"tlie_attn_prefill_d{d}", ["attention_prefill.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
+    return built
+
+
+def _ops():
+    from .. import ops
+
+    return ops
 
 
 def linear_bf16(x, weight, out) -> None:
@@ -27,6 +41,76 @@ def linear_bf16(x, weight, out) -> None:
         torch.mm(x, weight.t(), out=out)
 
 
+# --- decode attention -------------------------------------------------------------------------
+def decode_attention_library(head_dim: int):
+    lib = load_library(f"tlie_attn_decode_d{head_dim}", ["attention_decode.cu"], {"HEAD_DIM": head_dim})
+    if not getattr(lib, "_tlie_typed", False):
+        lib.tlie_decode_attention_scratch_floats.restype = c_longlong
+        lib._tlie_typed = True
+    return lib
+
+
+def decode_splits(requests: int, kv_heads: int, max_context: int) -> int:
+    """Parts the key range is cut into so that about two CTAs per SM exist; at least 128 keys per part."""
+    by_occupancy = -(-2 * SM_COUNT // max(1, requests * kv_heads))
+    by_length = max(1, -(-max_context // 128))
+    return max(1, min(by_occupancy, by_length))
+
+
+def scratch(device: torch.device, floats: int) -> torch.Tensor:
+    """Scratch memory of stable address (captured graphs keep pointing at it): grown, never freed."""
+    held = _scratch.setdefault(device, [])
+    if not held or held[-1].numel() < floats:
+        held.append(torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device))
+    return held[-1]
+
+
+def decode_attention(qkv, pages, positions, block_table, out, q_heads: int, kv_heads: int, head_dim: int, page_size: int,
+                     window: int, scale: float, splits: int) -> None:
+    """One query token per request (row i of qkv belongs to request i) over its cached keys; bfloat16."""
+    ops = _ops()
+    requests = qkv.shape[0]
+    lib = decode_attention_library(head_dim)
+    floats = lib.tlie_decode_attention_scratch_floats(c_int(requests), c_int(q_heads), c_int(splits))
+    buffer = scratch(qkv.device, floats) if floats else None
+    ops._check(
+        lib.tlie_decode_attention(
+            ops._ptr(qkv), c_int(qkv.shape[1]), ops._ptr(pages), ops._i32(positions, "positions"), ops._i32(block_table, "block_table"),
+            c_int(block_table.shape[1]), ops._ptr(out), ops._ptr(buffer), c_int(requests), c_int(q_heads), c_int(kv_heads), c_int(page_size),
+            c_int(window), c_float(scale), c_int(splits), ops._stream(),
+        ),
+        "decode_attention",
+    )
+    if splits > 1:
+        ops.launch_count += 1  # the merge kernel
+
+
+# --- prompt (and mixed) attention -----------------------------------------------------------------
+def prefill_attention(qkv, pages, tiles, seq_starts, first_positions, block_table, out, q_heads: int, kv_heads: int, head_dim: int,
+                      page_size: int, window: int, scale: float) -> None:
+    """Flash attention of every 64-row tile in ``tiles`` (int32 [n, 2]: request, first row) over the paged cache; bfloat16."""
+    ops = _ops()
+    lib = load_library(f"tlie_attn_prefill_d{head_dim}", ["attention_prefill.cu"], {"HEAD_DIM": head_dim})
+    ops._check(
+        lib.tlie_prefill_attention(
+            ops._ptr(qkv), c_int(qkv.shape[1]), ops._ptr(pages), ops._i32(tiles, "tiles"), c_int(tiles.shape[0]), ops._i32(seq_starts, "seq_starts"),
+            ops._i32(first_positions, "first_positions"), ops._i32(block_table, "block_table"), c_int(block_table.shape[1]), ops._ptr(out),
+            c_int(q_heads), c_int(kv_heads), c_int(page_size), c_int(window), c_float(scale), ops._stream(),
+        ),
+        "prefill_attention",
+    )
+
+
 def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, batch) -> bool:
     """Run a specialised kernel if one covers this shape; False sends the caller to the general one."""
+    if batch is None or pages.dtype != torch.bfloat16:
+        return False
+    if batch.decode_only and qkv.shape[0] == batch.num_seqs and head_dim <= 128 and q_heads // kv_heads <= 16:
+        splits = decode_splits(batch.num_seqs, kv_heads, batch.max_seq_len)
+        decode_attention(qkv, pages, positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, splits)
+        return True
+    if batch.attn_tiles is not None and head_dim <= 128:
+        prefill_attention(qkv, pages, batch.attn_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads,
+                          head_dim, page_size, window, scale)
+        return True
     return False
