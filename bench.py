@@ -189,7 +189,8 @@ def run_engine(args) -> dict:
             runner.finish(rid)
         return batch * steps / (ms / 1e3), ms / steps, session.kernels_per_step, clocks.summary()
 
-    value, ms_per_step, kernels_per_step, clocks = device_decode(args.batch)
+    sections = set(args.sections.split(","))
+    value, ms_per_step, kernels_per_step, clocks = device_decode(args.batch) if "decode" in sections else (0.0, 1.0, 0, {})
     first_context = PROMPT_TOKENS + max(warmup, 3)
     mean_context = first_context + (steps + 1) / 2.0
     step_bytes = decode_bytes(layers, args.batch, mean_context)
@@ -197,35 +198,41 @@ def run_engine(args) -> dict:
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
 
     # the same through the Python entry point: host token ids in, sampled ids out, every step
-    ids = [engine.add_request(p, SamplingParams(max_tokens=generated)) for p in prompts(args.batch, PROMPT_TOKENS)]
-    while any(not engine.requests[i].generated for i in ids):
-        engine.step()
-    for _ in range(max(warmup, 3)):
-        engine.step()
-    torch.cuda.synchronize()
-    started = time.perf_counter()
-    for _ in range(steps):
-        engine.step()
-    torch.cuda.synchronize()
-    e2e_seconds = time.perf_counter() - started
-    for i in ids:
-        engine.cancel(i)
-    e2e = {"value": args.batch * steps / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": args.batch * 4, "d2h_bytes_per_step": args.batch * 4}
+    e2e = None
+    if "e2e" in sections:
+        ids = [engine.add_request(p, SamplingParams(max_tokens=generated)) for p in prompts(args.batch, PROMPT_TOKENS)]
+        while any(not engine.requests[i].generated for i in ids):
+            engine.step()
+        for _ in range(max(warmup, 3)):
+            engine.step()
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        for _ in range(steps):
+            engine.step()
+        torch.cuda.synchronize()
+        e2e_seconds = time.perf_counter() - started
+        for i in ids:
+            engine.cancel(i)
+        e2e = {"value": args.batch * steps / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": args.batch * 4, "d2h_bytes_per_step": args.batch * 4}
 
     # prefill of one 2,048-token prompt
-    prefill_ms = []
-    for index, prompt in enumerate(prompts(5, PREFILL_TOKENS)):
-        rid = f"p{index}"
-        prefill_ms.append(event_ms(lambda: runner.step([StepEntry(rid, prompt, [PREFILL_TOKENS - 1])])))
-        runner.finish(rid)
-    best = sorted(prefill_ms[2:])[len(prefill_ms[2:]) // 2]
-    flops = prefill_flops(layers, PREFILL_TOKENS)
-    prefill = {"value": PREFILL_TOKENS / (best / 1e3), "tokens": PREFILL_TOKENS, "ms": best,
-               "frac": flops / (best / 1e3) / (peak["bf16_tflops"] * 1e12), "tflops": flops / (best / 1e3) / 1e12}
+    prefill = None
+    if "prefill" in sections:
+        prefill_ms = []
+        for index, prompt in enumerate(prompts(3 + args.prefill_samples, PREFILL_TOKENS)):
+            rid = f"p{index}"
+            prefill_ms.append(event_ms(lambda: runner.step([StepEntry(rid, prompt, [PREFILL_TOKENS - 1])])))
+            runner.finish(rid)
+        timed = sorted(prefill_ms[3:])
+        best = timed[len(timed) // 2]
+        flops = prefill_flops(layers, PREFILL_TOKENS)
+        prefill = {"value": PREFILL_TOKENS / (best / 1e3), "tokens": PREFILL_TOKENS, "ms": best,
+                   "frac": flops / (best / 1e3) / (peak["bf16_tflops"] * 1e12), "tflops": flops / (best / 1e3) / 1e12}
 
     points = {}
-    for batch in (1, 64):
-        points[f"decode_b{batch}"] = value if batch == args.batch else device_decode(batch)[0]
+    if "points" in sections:
+        for batch in (1, 64):
+            points[f"decode_b{batch}"] = value if batch == args.batch else device_decode(batch)[0]
 
     full_layers = SHAPES["num_hidden_layers"]
     return {
@@ -255,7 +262,9 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=SHAPES["num_hidden_layers"])
+    parser.add_argument("--prefill-samples", type=int, default=5)
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    parser.add_argument("--sections", default="decode,e2e,prefill,points", help="which measurements to take (all by default; fewer for profiling runs)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine is single-GPU by design (asked for {args.gpus})")

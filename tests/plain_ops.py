@@ -52,6 +52,15 @@ def linear(x, weight, out) -> None:
     _store(out, x.float() @ weight.float().T)
 
 
+def gated_linear(gate_up, weight, out, activated) -> None:
+    silu_mul(gate_up, activated)
+    linear(activated, weight, out)
+
+
+def fused_rows_limit(dtype, device) -> int:
+    return 0
+
+
 def rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim, pages, q_heads, kv_heads, head_dim, page_size, write_cache=True) -> None:
     tokens = qkv.shape[0]
     view = qkv.view(tokens, q_heads + 2 * kv_heads, head_dim)
@@ -119,7 +128,7 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
         out[r] = plain_llama.sample_top_p(logits[r].float(), float(temperature[r]), float(top_p[r]), u)
 
 
-_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "gather_rows", "to_float", "linear", "rope_store", "paged_attention", "argmax", "sample"]
+_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "gather_rows", "to_float", "linear", "gated_linear", "fused_rows_limit", "rope_store", "paged_attention", "argmax", "sample"]
 
 
 def install(monkeypatch) -> None:

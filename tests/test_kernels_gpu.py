@@ -273,3 +273,68 @@ def test_prefill_attention_flash(ops, q_heads, kv_heads, head_dim, page_size, wi
                            table.cuda(), got, q_heads, kv_heads, head_dim, page_size, window, head_dim ** -0.5)
     error = (got.cpu().float() - want.float()).abs().max(1).values
     assert float(error.max()) <= 1.6e-2 * 2, (int(error.argmax()), error.max())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(131, 80), (2560, 2048), (2048, 5632), (1000, 200), (16, 4096)])
+def test_gemm_skinny(ops, M, N, K):
+    """The weight-streaming product against a 32-bit product of the same bfloat16 values, plain and with the fused gate."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    torch.manual_seed(10)
+    x = torch.randn(M, K).bfloat16()
+    w = (torch.randn(N, K) * 0.05).bfloat16()
+    want = x.float() @ w.float().T
+    for out_dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 1.6e-2)):
+        got = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
+        fast.gemm_skinny(x.cuda(), w.cuda(), got)
+        assert torch.allclose(got.cpu().float(), want, atol=tol * float(want.abs().max()), rtol=0), float((got.cpu().float() - want).abs().max())
+    padded = torch.randn(M, K + 24).bfloat16().cuda()  # rows with a stride larger than K
+    got = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    fast.gemm_skinny(padded[:, :K], w.cuda(), got)
+    assert torch.allclose(got.cpu(), padded[:, :K].cpu().float() @ w.float().T, atol=1e-4 * float(want.abs().max()) + 1e-5)
+    gate_up = (torch.randn(M, 2 * K) * 1.5).bfloat16()
+    act = torch.empty(M, K, dtype=torch.bfloat16)
+    plain_ops.silu_mul(gate_up, act)
+    want = act.float() @ w.float().T
+    got = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    fast.gemm_skinny(gate_up.cuda(), w.cuda(), got, gated=True)
+    assert torch.allclose(got.cpu(), want, atol=1e-3 * float(want.abs().max()) + 1e-5), float((got.cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(130, 80), (2560, 2048), (2048, 5632), (1000, 200), (352, 176)])
+def test_gemv_fused(ops, M, N, K):
+    """The fused decode products: plain, with the norm in front, accumulating into the residual, and gated."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    torch.manual_seed(11)
+    x = torch.randn(M, K).bfloat16()
+    w = (torch.randn(N, K) * 0.05).bfloat16()
+    want = x.float() @ w.float().T
+    scale = float(want.abs().max())
+    for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 1.6e-2)):
+        got = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+        fast.gemv_fused(x.cuda(), w.cuda(), got)
+        assert torch.allclose(got.cpu().float(), want, atol=tol * scale, rtol=0)
+    residual = torch.randn(M, N)
+    got = residual.clone().cuda()
+    fast.gemv_fused(x.cuda(), w.cuda(), got, epilogue="accumulate")
+    assert torch.allclose(got.cpu(), residual + want, atol=1e-4 * scale + 1e-5)
+    # gated: silu of the first half of the rows times the second half, both rounded to bfloat16 first
+    half = N // 2
+    g, u = want[:, :half].bfloat16().float(), want[:, half:].bfloat16().float()
+    gated = torch.empty(M, half, dtype=torch.bfloat16, device="cuda")
+    fast.gemv_fused(x.cuda(), w.cuda(), gated, epilogue="gated")
+    expect = (g / (1 + torch.exp(-g))) * u
+    assert torch.allclose(gated.cpu().float(), expect, atol=1.6e-2 * float(expect.abs().max()) + 2e-3 * scale)
+    # norm in front, with and without a gather of rows
+    stream = torch.randn(M + 3, K) * 2
+    norm_weight = 1 + 0.1 * torch.randn(K)
+    for rows in (None, torch.randperm(M + 3)[:M].to(torch.int32)):
+        normed = torch.empty(M, K, dtype=torch.bfloat16)
+        plain_ops.add_rmsnorm(stream.clone(), None, norm_weight, 1e-5, normed, rows if rows is not None else torch.arange(M, dtype=torch.int32))
+        want_n = normed.float() @ w.float().T
+        got = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        fast.gemv_fused(stream.cuda(), w.cuda(), got, norm=(norm_weight.cuda(), 1e-5, None if rows is None else rows.cuda()))
+        assert torch.allclose(got.cpu(), want_n, atol=4e-3 * float(want_n.abs().max())), float((got.cpu() - want_n).abs().max())

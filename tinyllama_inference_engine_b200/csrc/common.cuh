@@ -69,3 +69,40 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 }  // namespace tlie
+
+// --- programmatic dependent launch -----------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its
+// predecessor in the stream still runs.  It must call grid_dependency_wait() before it reads
+// anything the predecessor wrote (weights and other constants may be fetched earlier), and it
+// lets its own successor start early with grid_launch_dependents().  Without the attribute both
+// are no-ops.
+namespace tlie {
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+}  // namespace tlie
+
+#ifdef __CUDACC__
+#include <cstdlib>
+namespace tlie {
+// Launch with programmatic dependent launch unless TLIE_PDL=0 is set in the environment.
+template <typename... KernelArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  static const bool enabled = [] {
+    const char* v = std::getenv("TLIE_PDL");
+    return !(v && v[0] == '0');
+  }();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+}  // namespace tlie
+#endif

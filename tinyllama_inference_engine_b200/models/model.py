@@ -60,5 +60,8 @@ class DecoderModel:
     def logits(self, residual, want_rows):
         if want_rows is None or want_rows.shape[0] == 0:
             return None
-        normed = self.final_norm.forward(residual, None, rows=want_rows)
-        return self.head.forward(normed)
+        from .. import ops
+
+        if self.final_norm.supports_lazy and want_rows.shape[0] <= ops.fused_rows_limit(self.runtime.dtype, residual.device):
+            return self.head.forward(self.final_norm.forward(residual, None, rows=want_rows, lazy=True))
+        return self.head.forward(self.final_norm.forward(residual, None, rows=want_rows))

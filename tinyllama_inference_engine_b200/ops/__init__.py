@@ -137,6 +137,64 @@ def linear(x, weight, out) -> None:
     fast.linear_bf16(x, weight, out)
 
 
+def fused_rows_limit(dtype: torch.dtype, device: torch.device) -> int:
+    """Up to how many rows a step may use the fused decode kernels (0: never, as in the 32-bit path)."""
+    if dtype != torch.bfloat16 or device.type != "cuda":
+        return 0
+    from . import fast
+
+    return fast.FUSED_MAX_ROWS
+
+
+class LazyNorm:
+    """A normalised activation that is not computed yet: rmsnorm(residual[rows]) * weight.
+
+    A product that can apply the norm while it loads its operand takes this in the place of a tensor
+    (``norm_linear``); anything else calls ``tensor()``.
+    """
+
+    def __init__(self, residual, weight, eps: float, rows, materialize):
+        self.residual, self.weight, self.eps, self.rows = residual, weight, eps, rows
+        self._materialize = materialize
+        self.shape = (residual.shape[0] if rows is None else rows.shape[0], residual.shape[1])
+
+    def tensor(self):
+        return self._materialize()
+
+
+def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
+    """out = rmsnorm(residual) * norm_weight . weight^T in one kernel (``gated``: silu(gate) * up of the two halves)."""
+    from . import fast
+
+    fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), epilogue="gated" if gated else "store")
+
+
+def linear_accumulate(x, weight, residual) -> None:
+    """residual += x . weight^T, the sum in 32-bit, in one kernel (bfloat16 x, up to the fused row limit)."""
+    from . import fast
+
+    fast.gemv_fused(x, weight, residual, epilogue="accumulate")
+
+
+def linear_gated(x, weight, out) -> None:
+    """out = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel."""
+    from . import fast
+
+    fast.gemv_fused(x, weight, out, epilogue="gated")
+
+
+def gated_linear(gate_up, weight, out, activated) -> None:
+    """out = (silu(gate) * up) . weight^T for rows [gate | up]; ``activated`` is scratch for the unfused route."""
+    if gate_up.dtype == torch.bfloat16:
+        from . import fast
+
+        if gate_up.shape[0] <= fast.SKINNY_MAX_ROWS and weight.shape[1] % 8 == 0:
+            fast.gemm_skinny(gate_up, weight, out, gated=True)
+            return
+    silu_mul(gate_up, activated)
+    linear(activated, weight, out)
+
+
 # --- position encoding and cache write ---------------------------------------------------
 def rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim: int, pages, q_heads: int, kv_heads: int, head_dim: int, page_size: int, write_cache: bool = True) -> None:
     """Rotate q (in place) and k, and store k, v of every token into its request's pages."""

@@ -21,6 +21,8 @@ _scratch: dict[torch.device, list[torch.Tensor]] = {}
 def build_all() -> list:
     built = [build_library(f"tlie_attn_decode_d{d}", ["attention_decode.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
     built += [build_library(f"tlie_attn_prefill_d{d}", ["attention_prefill.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
+    built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
+    built.append(build_library("tlie_gemv_fused", ["gemv_fused.cu"]))
     return built
 
 
@@ -30,10 +32,77 @@ def _ops():
     return ops
 
 
+SKINNY_MAX_ROWS = 16   # up to this many rows the weight-streaming kernel beats the library's product
+
+
+def skinny_library():
+    return load_library("tlie_gemm_skinny", ["gemm_skinny.cu"])
+
+
+def gemm_skinny(x, weight, out, gated: bool = False) -> None:
+    """out[M, N] = x . weight^T for M <= 64 rows; with ``gated`` x is [gate | up] and the operand is silu(gate) * up."""
+    ops = _ops()
+    M, N, K = x.shape[0], weight.shape[0], weight.shape[1]
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or K % 8 != 0 or M > 64 or x.shape[1] != (2 * K if gated else K):
+        raise KernelError(f"gemm_skinny cannot take x {tuple(x.shape)} (strides {x.stride()}) with weight {tuple(weight.shape)}", code="invalid_shape")
+    if not x.is_cuda:
+        raise KernelError("this engine has no CPU path: a kernel was given a tensor that is not on a CUDA device")
+    ops._check(
+        skinny_library().tlie_gemm_skinny(c_void_p(x.data_ptr()), c_int(x.stride(0)), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K),
+                                          c_int(1 if gated else 0), c_int(1 if out.dtype == torch.float32 else 0), ops._stream()),
+        "gemm_skinny",
+    )
+
+
+FUSED_MAX_ROWS = 16     # the fused decode kernels (norm + product, product + residual add, gate) take up to this many rows
+_EPILOGUES = {"store": None, "accumulate": 2, "gated": 3}
+
+
+def gemv_library():
+    return load_library("tlie_gemv_fused", ["gemv_fused.cu"])
+
+
+def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store") -> None:
+    """out (+)= f(x) . weight^T for up to 16 rows, one kernel.
+
+    norm      None: ``x`` is bfloat16 [M, K].  (norm_weight, eps, rows): ``x`` is the 32-bit residual stream and
+              the operand is rmsnorm(x[rows]) * norm_weight (rows None: the first M rows).
+    epilogue  "store": out [M, N] bfloat16 or 32-bit;  "accumulate": out is the 32-bit residual, out += result;
+              "gated": weight is [gate rows | up rows], out [M, N / 2] = silu(gate) * up.
+    """
+    ops = _ops()
+    N, K = weight.shape
+    M = out.shape[0]
+    if weight.dtype != torch.bfloat16 or M > FUSED_MAX_ROWS or K % 8 != 0:
+        raise KernelError(f"gemv_fused takes bfloat16 weights with K % 8 == 0 and at most {FUSED_MAX_ROWS} rows", code="invalid_shape")
+    code = _EPILOGUES[epilogue]
+    if epilogue == "store":
+        code = 1 if out.dtype == torch.float32 else 0
+    elif epilogue == "accumulate" and out.dtype != torch.float32:
+        raise KernelError("gemv_fused accumulates into the 32-bit residual only", code="invalid_dtype")
+    if out.shape[1] != (N // 2 if epilogue == "gated" else N):
+        raise KernelError("gemv_fused: the output's width does not fit the weight", code="invalid_shape")
+    if norm is None:
+        if x.dtype != torch.bfloat16 or x.shape != (M, K) or x.stride(1) != 1 or x.stride(0) % 8 != 0:
+            raise KernelError("gemv_fused: x must be bfloat16 [M, K] with rows 16-byte aligned", code="invalid_shape")
+        args = (c_int(0), c_void_p(x.data_ptr()), c_int(x.stride(0)), c_void_p(0), c_void_p(0), c_float(0.0))
+    else:
+        norm_weight, eps, rows = norm
+        if x.dtype != torch.float32 or x.shape[1] != K or norm_weight.dtype != torch.float32 or norm_weight.numel() != K:
+            raise KernelError("gemv_fused: the residual and the norm weight must be 32-bit and K wide", code="invalid_shape")
+        args = (c_int(1), ops._ptr(x), c_int(K), ops._i32(rows, "rows"), ops._ptr(norm_weight), c_float(eps))
+    if not out.is_cuda:
+        raise KernelError("this engine has no CPU path: a kernel was given a tensor that is not on a CUDA device")
+    ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), ops._stream()), "gemv_fused")
+
+
 def linear_bf16(x, weight, out) -> None:
     global library_gemm_calls
     if weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("linear: the bfloat16 path takes bfloat16 weights", code="invalid_dtype")
+    if x.shape[0] <= FUSED_MAX_ROWS and weight.shape[1] % 8 == 0 and x.stride(0) % 8 == 0:
+        gemv_fused(x, weight, out)
+        return
     library_gemm_calls += 1
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)

@@ -22,6 +22,9 @@ class Attention(Mixer):
     weights are stacked once at load time and one product yields ``[q | k | v]``.
     """
 
+    accepts_lazy_norm = True
+    fuses_residual_add = True
+
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
         hidden, d = spec["hidden_size"], spec["head_dim"]
@@ -52,10 +55,13 @@ class Attention(Mixer):
         self.position = build_part("position", spec["position"], prefix, weights, runtime)
         self.qkv_width = (self.q_heads + 2 * self.kv_heads) * self.head_dim
 
-    def forward(self, x, ctx, cache: LayerCache):
+    def forward(self, x, ctx, cache: LayerCache, accumulate_into=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         qkv = ws.get("qkv", tokens, self.qkv_width, dtype)
-        ops.linear(x, self.w_qkv, qkv)
+        if isinstance(x, ops.LazyNorm):
+            ops.norm_linear(x, self.w_qkv, qkv)
+        else:
+            ops.linear(x, self.w_qkv, qkv)
         table = self.position.rotary_table()
         if table is None:
             self.position.apply(qkv, ctx, self.q_heads, self.kv_heads, self.head_dim)
@@ -67,6 +73,9 @@ class Attention(Mixer):
         mixed = ws.get("attention", tokens, self.q_heads * self.head_dim, dtype)
         ops.paged_attention(qkv, cache.pages, ctx.positions, ctx.token_seq, cache.block_table, mixed,
                             self.q_heads, self.kv_heads, self.head_dim, cache.page_size, self.window, self.scale, batch=ctx)
+        if accumulate_into is not None:
+            ops.linear_accumulate(mixed, self.w_o, accumulate_into)
+            return None
         out = ws.get("mixer_out", tokens, self.hidden, dtype)
         ops.linear(mixed, self.w_o, out)
         return out

@@ -19,6 +19,8 @@ What each category must offer:
                values, per-request state of fixed size, or nothing;
                ``forward(x, ctx, cache) -> y`` for the step's tokens ``x [T, hidden]``.
   feed_forward ``forward(x, ctx) -> y``.
+               (A mixer or feed-forward may set ``accepts_lazy_norm`` / ``fuses_residual_add``
+               to take the norm before it and the residual add after it into its own kernels.)
   block        ``forward(residual, delta, ctx, cache) -> (residual, delta)``: the
                hidden state is the pair (32-bit residual, last output not yet added).
 """
@@ -107,6 +109,7 @@ class Part:
 
 class Norm(Part):
     category = "norm"
+    supports_lazy = False   # True: forward(..., lazy=True) may return an ops.LazyNorm for a product to apply
 
     def forward(self, residual, delta=None, rows=None):
         raise NotImplementedError
@@ -124,6 +127,9 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     category = "mixer"
+    # A mixer (or feed-forward) that sets these takes more work into its own kernels when the block offers it:
+    accepts_lazy_norm = False      # forward may receive an ops.LazyNorm in the place of the normalised tensor
+    fuses_residual_add = False     # forward(..., accumulate_into=residual) adds its output there and returns None
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
@@ -135,6 +141,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     category = "feed_forward"
+    accepts_lazy_norm = False
+    fuses_residual_add = False
 
     def forward(self, x, ctx):
         raise NotImplementedError

@@ -36,11 +36,23 @@ class PreNormResidualBlock(Block):
             setattr(self, slot, build_part(category, spec[slot], f"{prefix}.{spec[slot + '_name']}", weights, runtime))
 
     def forward(self, residual, delta, ctx, cache: LayerCache):
-        normed = self.mixer_norm.forward(residual, delta)
-        delta = self.mixer.forward(normed, ctx, cache)
-        normed = self.feed_forward_norm.forward(residual, delta)
-        delta = self.feed_forward.forward(normed, ctx)
+        from .. import ops
+
+        fused = residual.shape[0] <= ops.fused_rows_limit(self.runtime.dtype, residual.device)
+        delta = self._run(self.mixer_norm, self.mixer, residual, delta, fused, ctx, cache)
+        delta = self._run(self.feed_forward_norm, self.feed_forward, residual, delta, fused, ctx)
         return residual, delta
+
+    @staticmethod
+    def _run(norm, part, residual, delta, fused, *args):
+        """norm -> part, letting the part take the norm and the residual add into its kernels where it can (few rows)."""
+        if fused and part.accepts_lazy_norm and norm.supports_lazy:
+            x = norm.forward(residual, delta, lazy=True)
+        else:
+            x = norm.forward(residual, delta)
+        if fused and part.fuses_residual_add:
+            return part.forward(x, *args, accumulate_into=residual)
+        return part.forward(x, *args)
 
 
 register_part("block", "pre_norm_residual", PreNormResidualBlock)

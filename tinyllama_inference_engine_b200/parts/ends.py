@@ -57,8 +57,13 @@ class LinearHead(Part):
         self.vocab = int(spec["vocab_size"])
 
     def forward(self, normed_rows):
-        logits = torch.empty((normed_rows.shape[0], self.vocab), dtype=torch.float32, device=normed_rows.device)
-        ops.linear(normed_rows, self.weight, logits)
+        """``normed_rows`` is the normalised hidden state of the wanted rows, or an ops.LazyNorm of it."""
+        rows = normed_rows.shape[0]
+        logits = torch.empty((rows, self.vocab), dtype=torch.float32, device=self.weight.device)
+        if isinstance(normed_rows, ops.LazyNorm):
+            ops.norm_linear(normed_rows, self.weight, logits)
+        else:
+            ops.linear(normed_rows, self.weight, logits)
         return logits
 
 

@@ -19,6 +19,9 @@ class GatedMLP(FeedForward):
     ``up`` are computed in 32-bit.
     """
 
+    accepts_lazy_norm = True
+    fuses_residual_add = True
+
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
         hidden, inter = spec["hidden_size"], spec["intermediate_size"]
@@ -38,12 +41,24 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat([weights.get(f"{prefix}.gate_proj.weight", dtype), weights.get(f"{prefix}.up_proj.weight", dtype)], dim=0).contiguous()
         self.w_down = weights.get(f"{prefix}.down_proj.weight", dtype).contiguous()
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, accumulate_into=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
-        gate_up = ws.get("gate_up", tokens, 2 * self.inter, dtype)
-        ops.linear(x, self.w_gate_up, gate_up)
         act = ws.get("activated", tokens, self.inter, dtype)
-        ops.silu_mul(gate_up, act)
+        if tokens <= ops.fused_rows_limit(dtype, act.device):
+            # few rows: the gate is applied in the first product's epilogue, the residual add in the second's
+            if isinstance(x, ops.LazyNorm):
+                ops.norm_linear(x, self.w_gate_up, act, gated=True)
+            else:
+                ops.linear_gated(x, self.w_gate_up, act)
+        else:
+            if isinstance(x, ops.LazyNorm):
+                x = x.tensor()
+            gate_up = ws.get("gate_up", tokens, 2 * self.inter, dtype)
+            ops.linear(x, self.w_gate_up, gate_up)
+            ops.silu_mul(gate_up, act)
+        if accumulate_into is not None:
+            ops.linear_accumulate(act, self.w_down, accumulate_into)
+            return None
         out = ws.get("ff_out", tokens, self.hidden, dtype)
         ops.linear(act, self.w_down, out)
         return out

@@ -16,6 +16,8 @@ class RMSNorm(Norm):
     the weight is held in 32-bit (exact for a bfloat16 checkpoint).
     """
 
+    supports_lazy = True
+
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
         return [TensorSpec(f"{prefix}.weight", (spec["size"],), init="norm", std=0.1)]
@@ -26,7 +28,10 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.weight = weights.get(f"{prefix}.weight", torch.float32).contiguous()
 
-    def forward(self, residual, delta=None, rows=None):
+    def forward(self, residual, delta=None, rows=None, lazy: bool = False):
+        """``lazy`` (and nothing to add): hand the norm on to the product that consumes it (ops.LazyNorm)."""
+        if lazy and delta is None:
+            return ops.LazyNorm(residual, self.weight, self.eps, rows, lambda: self.forward(residual, None, rows))
         count = residual.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.workspace.get("normed" if rows is None else "normed_rows", count, self.size, self.runtime.dtype)
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
