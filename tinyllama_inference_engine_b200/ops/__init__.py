@@ -166,21 +166,36 @@ def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
     """out = rmsnorm(residual) * norm_weight . weight^T in one kernel (``gated``: silu(gate) * up of the two halves)."""
     from . import fast
 
-    fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), epilogue="gated" if gated else "store")
+    if fast.gemv_fits(out.shape[0], weight.shape[1], norm=True, gated=gated):
+        fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), epilogue="gated" if gated else "store")
+    elif gated:
+        linear_gated(x.tensor(), weight, out)
+    else:
+        linear(x.tensor(), weight, out)
 
 
 def linear_accumulate(x, weight, residual) -> None:
     """residual += x . weight^T, the sum in 32-bit, in one kernel (bfloat16 x, up to the fused row limit)."""
     from . import fast
 
-    fast.gemv_fused(x, weight, residual, epilogue="accumulate")
+    if fast.gemv_fits(x.shape[0], weight.shape[1], norm=False):
+        fast.gemv_fused(x, weight, residual, epilogue="accumulate")
+    else:
+        delta = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        linear(x, weight, delta)
+        add_(residual, delta)
 
 
 def linear_gated(x, weight, out) -> None:
     """out = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel."""
     from . import fast
 
-    fast.gemv_fused(x, weight, out, epilogue="gated")
+    if fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True):
+        fast.gemv_fused(x, weight, out, epilogue="gated")
+    else:
+        gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        linear(x, weight, gate_up)
+        silu_mul(gate_up, out)
 
 
 def gated_linear(gate_up, weight, out, activated) -> None:

@@ -62,6 +62,17 @@ def gemv_library():
     return load_library("tlie_gemv_fused", ["gemv_fused.cu"])
 
 
+def gemv_fits(rows: int, K: int, norm: bool, gated: bool = False) -> bool:
+    """Whether the fused kernel's shared memory (x as bfloat16 and the warps' partial tiles) fits."""
+    if rows > FUSED_MAX_ROWS or K % 8 != 0:
+        return False
+    padded_rows = 8 if rows <= 8 else 16
+    stride = K + ((32 - K % 64) + 64) % 64
+    stride += 64 if stride == K else 0
+    need = padded_rows * stride * 2 + 8 * (2 if gated else 1) * 16 * (padded_rows + 1) * 4
+    return need <= 200 * 1024
+
+
 def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store") -> None:
     """out (+)= f(x) . weight^T for up to 16 rows, one kernel.
 
@@ -100,7 +111,7 @@ def linear_bf16(x, weight, out) -> None:
     global library_gemm_calls
     if weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("linear: the bfloat16 path takes bfloat16 weights", code="invalid_dtype")
-    if x.shape[0] <= FUSED_MAX_ROWS and weight.shape[1] % 8 == 0 and x.stride(0) % 8 == 0:
+    if x.stride(0) % 8 == 0 and gemv_fits(x.shape[0], weight.shape[1], norm=False):
         gemv_fused(x, weight, out)
         return
     library_gemm_calls += 1
