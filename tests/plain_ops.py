@@ -106,6 +106,12 @@ def paged_attention(qkv, pages, positions, token_seq, block_table, out, q_heads,
     _store(out, result.view(tokens, q_heads * head_dim))
 
 
+def attention_step(qkv, positions, token_seq, block_table, inv_freq, rotary_dim, pages, out, q_heads, kv_heads, head_dim, page_size,
+                   window=0, scale=None, write_cache=True, batch=None) -> None:
+    rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim, pages, q_heads, kv_heads, head_dim, page_size, write_cache)
+    paged_attention(qkv, pages, positions, token_seq, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, batch)
+
+
 def argmax(logits, out) -> None:
     for r in range(logits.shape[0]):
         out[r] = int(torch.nonzero(logits[r] == logits[r].max())[0])
@@ -128,7 +134,7 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
         out[r] = plain_llama.sample_top_p(logits[r].float(), float(temperature[r]), float(top_p[r]), u)
 
 
-_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "gather_rows", "to_float", "linear", "gated_linear", "fused_rows_limit", "rope_store", "paged_attention", "argmax", "sample"]
+_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "gather_rows", "to_float", "linear", "gated_linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample"]
 
 
 def install(monkeypatch) -> None:

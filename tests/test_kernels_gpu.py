@@ -339,3 +339,33 @@ def test_gemv_fused(ops, M, N, K):
         fast.gemv_fused(stream.cuda(), w.cuda(), got, norm=(norm_weight.cuda(), 1e-5, None if rows is None else rows.cuda()))
         # the kernel rounds residual * weight to bfloat16 and scales the 32-bit sum: the same product, rounded elsewhere
         assert torch.allclose(got.cpu(), want_n, atol=6e-3 * float(want_n.abs().max())), float((got.cpu() - want_n).abs().max())
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window,rotate", [
+    (32, 4, 64, 64, 0, True), (8, 8, 128, 64, 0, True), (6, 2, 32, 32, 0, True), (8, 2, 64, 16, 100, True), (4, 2, 64, 16, 0, False), (12, 3, 96, 16, 0, True),
+])
+@pytest.mark.parametrize("splits", [1, 5])
+def test_decode_attention_with_rotation_and_cache_write(ops, q_heads, kv_heads, head_dim, page_size, window, rotate, splits):
+    """The decode kernel doing rope_store's work itself: same output, same pages, as rope_store followed by attention."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    rng = np.random.default_rng(12)
+    torch.manual_seed(12)
+    seq_lens = [1, 32, 33, 64, 65, 700, 1153, 4097, 2 * page_size + 1]
+    qkv, pages, positions, token_seq, table = _paged_case(rng, torch.bfloat16, seq_lens, [1] * len(seq_lens), kv_heads, head_dim, page_size, q_heads)
+    inv_freq = None
+    if rotate:
+        exponent = (np.float32(-2.0) * np.arange(head_dim // 2, dtype=np.float32)) / np.float32(head_dim)
+        inv_freq = torch.from_numpy(np.power(np.float32(10000.0), exponent, dtype=np.float32))
+    for write in (True, False):
+        qkv_plain, pages_plain = qkv.clone(), pages.clone()
+        want = torch.empty(len(seq_lens), q_heads * head_dim, dtype=torch.bfloat16)
+        plain_ops.attention_step(qkv_plain, positions, token_seq, table, inv_freq, head_dim if rotate else 0, pages_plain, want, q_heads, kv_heads, head_dim, page_size, window, None, write)
+        pages_gpu = pages.clone().cuda()
+        got = torch.empty(len(seq_lens), q_heads * head_dim, dtype=torch.bfloat16, device="cuda")
+        fast.decode_attention(qkv.cuda(), pages_gpu, positions.cuda(), table.cuda(), got, q_heads, kv_heads, head_dim, page_size, window, head_dim ** -0.5, splits,
+                              fuse_rope=True, inv_freq=None if inv_freq is None else inv_freq.cuda(), write_cache=write)
+        assert float((got.cpu().float() - want.float()).abs().max()) <= 3.2e-2
+        assert torch.allclose(pages_gpu.cpu().float(), pages_plain.float(), atol=1.6e-2 * 4 + 2e-4)
+        if not write:
+            assert torch.equal(pages_gpu.cpu(), pages)

@@ -100,6 +100,7 @@ class CacheManager:
             for position, stream in enumerate(streams):
                 self.stream_group[stream] = (need.kind, group.index, position)
         self.needs = dict(needs)
+        self._has_windows = any(group.need.window > 0 for group in self.page_groups)
         self.records: dict[object, RequestRecord] = {}
         self._free_slots = list(range(max_requests - 1, -1, -1))
         if self.device is not None:
@@ -148,9 +149,11 @@ class CacheManager:
     def pages_needed(self, request_id: object | None, new_total: int) -> list[int]:
         """New pages per page group for the request to hold positions < new_total."""
         record = self.records.get(request_id) if request_id is not None else None
+        pages = -(-new_total // self.page_size)
         if record is None:
-            return [-(-new_total // self.page_size) for _ in self.page_groups]
-        return [group.pages_for(record, new_total) for group in self.page_groups]
+            return [pages] * len(self.page_groups)
+        tables = record.tables
+        return [max(0, pages - len(tables.get(group.index, ()))) for group in self.page_groups]
 
     def can_reserve(self, wanted: list[tuple[object | None, int]]) -> bool:
         """Whether all (request, new_total) pairs can get their pages at once."""
@@ -179,6 +182,8 @@ class CacheManager:
         if new_total < record.computed:
             raise BatchError(f"request {request_id!r} cannot go back from {record.computed} to {new_total}")
         record.computed = new_total
+        if not self._has_windows:
+            return
         for group in self.page_groups:
             table = record.tables.get(group.index, [])
             passed = [i for i in range(min(group.first_needed_page(new_total), len(table))) if table[i] >= 0]

@@ -16,6 +16,13 @@
 //   * q.K^T and P.V run on the tensor cores (mma.sync m16n8k16, bf16 in, 32-bit accumulate):
 //     with at most 16 rows per tile the 128-row tcgen05 shapes would be idle weight, and the
 //     CUDA cores alone cannot keep up with 8 flop per cache byte at HBM speed.
+//   * the rotation of q and of the new key (src/operators.cpp:47-78) and the write of the new key and
+//     value into the request's page happen here too when the caller asks for it: q is rotated in the
+//     registers of its tensor-core fragments, and the CTA whose key range holds the new position
+//     stores k and v before it starts reading, so a decode step needs no separate rotation / cache
+//     write kernel (src/cuda/kernels.cu:86-145 in the reference);
+//   * the parts are merged by whichever CTA of a (request, kv head) finishes last (a counter in
+//     scratch memory, reset by that CTA), not by a second kernel; nobody waits for anybody.
 // The grid depends only on (requests, kv heads, SPLITS); lengths are read on the device, so one
 // captured graph serves every later step.
 //
@@ -31,8 +38,14 @@ namespace tlie {
 
 constexpr int kD = HEAD_DIM;
 constexpr int kTileKeys = 32;
-constexpr int kWarps = 4;
-constexpr int kStages = (kD <= 64) ? 3 : 2;
+#ifndef DECODE_WARPS
+#define DECODE_WARPS ((HEAD_DIM <= 64) ? 8 : 4)
+#endif
+#ifndef DECODE_STAGES
+#define DECODE_STAGES 2
+#endif
+constexpr int kWarps = DECODE_WARPS;
+constexpr int kStages = DECODE_STAGES;
 constexpr int kRow = kD + 8;                       // padded row, in elements (16 bytes of padding)
 constexpr int kTileElems = kTileKeys * kRow;       // one K or V tile
 constexpr int kChunks = kD / 8;                    // 16-byte chunks per row
@@ -40,37 +53,52 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 // Loads one 32-key tile of K and V of kv head `kvh` into a warp's stage buffer.  Rows whose key is
 // outside [lo, n_keys) are zero-filled (their pages may not exist, and 0 * garbage must stay 0).
+// A page holds a multiple of 16 keys, so each 16-key half of the tile lies in one page: two table
+// lookups per tile, no division per row.
 __device__ __forceinline__ void load_tile(__nv_bfloat16* k_smem, __nv_bfloat16* v_smem, const __nv_bfloat16* pages,
                                           const int* table, int key0, int lo, int n_keys, int kvh, int kv_heads,
                                           int page_size, int lane) {
   const size_t plane = (size_t)kv_heads * page_size * kD;
+  const __nv_bfloat16* half_base[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int k = key0 + 16 * h;
+    const bool any = k < n_keys && k + 16 > lo;
+    const int page = any ? table[k / page_size] : 0;
+    half_base[h] = pages + (size_t)page * 2 * plane + ((size_t)kvh * page_size + (k % page_size)) * kD;
+  }
 #pragma unroll
   for (int idx = lane; idx < kTileKeys * kChunks; idx += 32) {
     const int row = idx / kChunks;
     const int chunk = idx - row * kChunks;
     const int key = key0 + row;
     const bool valid = key >= lo && key < n_keys;
-    const __nv_bfloat16* src = pages;
-    if (valid) {
-      const int page = table[key / page_size];
-      src = pages + (size_t)page * 2 * plane + ((size_t)kvh * page_size + (key % page_size)) * kD + chunk * 8;
-    }
-    cp_async_16(k_smem + row * kRow + chunk * 8, src, valid);
-    cp_async_16(v_smem + row * kRow + chunk * 8, valid ? src + plane : src, valid);
+    const __nv_bfloat16* src = (row < 16 ? half_base[0] : half_base[1]) + (row & 15) * kD + chunk * 8;
+    cp_async_16(k_smem + row * kRow + chunk * 8, valid ? src : pages, valid);
+    cp_async_16(v_smem + row * kRow + chunk * 8, valid ? src + plane : pages, valid);
   }
 }
 
 // partial_o: [request, q head, split, D] 32-bit, unnormalised; partial_ml: [request, q head, split, 2] = (max in log2 units, sum).
+// fuse_rope: 0 = q is rotated and the cache is written already; 1 = rotate q (and the new key) here with inv_freq
+// (full-head rotation, kD % 32 == 0) or not at all if inv_freq is null, and, if write_cache, store the new key and value.
 __global__ void __launch_bounds__(kWarps * 32)
-    decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ pages,
+    decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ pages,
                             const int* __restrict__ positions, const int* __restrict__ block_table, int table_stride,
                             __nv_bfloat16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
-                            int q_heads, int kv_heads, int page_size, int window, float scale, int splits) {
+                            int* __restrict__ tickets, int q_heads, int kv_heads, int page_size, int window, float scale,
+                            int splits, int fuse_rope, const float* __restrict__ inv_freq, int write_cache) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int last_arrival;
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int group = q_heads / kv_heads;
+  grid_launch_dependents();
+  // With fuse_rope nothing this kernel reads before its q comes from the kernel just before it: positions and block
+  // tables were set before the step began, and every cached key but the new one is from earlier steps.  So the cache
+  // tiles are fetched first and the wait for the previous kernel (which produces q, k, v of the new token) comes after.
+  if (!fuse_rope) grid_dependency_wait();
   const int pos = positions[seq];
   const int n_keys = pos + 1;
   const int lo = (window > 0 && n_keys > window) ? n_keys - window : 0;
@@ -84,6 +112,26 @@ __global__ void __launch_bounds__(kWarps * 32)
   const int tile_end = min(first_tile + all_tiles, tile_begin + per_split);
 
   __nv_bfloat16* stage_base = reinterpret_cast<__nv_bfloat16*>(smem_raw) + (size_t)warp * kStages * 2 * kTileElems;
+
+  // The new token's key (rotated) and value are not in the cache yet.  The warp that owns the tile holding the
+  // new position computes them, stores them in the page for later steps, and patches them into its own copy of
+  // the tile in shared memory, so nothing has to travel through global memory first.  (A run that only reads a
+  // cache another run wrote finds the key in the page already.)
+  const bool patch_new = fuse_rope && write_cache && pos / kTileKeys >= tile_begin && pos / kTileKeys < tile_end &&
+                         ((pos / kTileKeys - tile_begin) % kWarps) == warp;
+
+  // prologue: this warp's tiles are tile_begin + warp, + kWarps, ...
+  int next_load = tile_begin + warp;
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (next_load < tile_end) {
+      __nv_bfloat16* ks = stage_base + (size_t)s * 2 * kTileElems;
+      load_tile(ks, ks + kTileElems, pages, table, next_load * kTileKeys, lo, n_keys, kvh, kv_heads, page_size, lane);
+    }
+    cp_async_commit();
+    next_load += kWarps;
+  }
+  if (fuse_rope) grid_dependency_wait();
 
   // Q fragments: rows = query heads of the group (row r valid if r < group), k = head dims
   unsigned qa[kD / 16][4];
@@ -100,6 +148,31 @@ __global__ void __launch_bounds__(kWarps * 32)
     }
   }
 
+  if (fuse_rope && inv_freq != nullptr) {
+    // pair (d, d + kD/2): k-steps ks and ks + kD/32 hold them in the same register slot of the same thread
+    if constexpr (kD % 32 == 0) {
+#pragma unroll
+      for (int ks = 0; ks < kD / 32; ++ks) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int d = ks * 16 + 2 * t + half * 8;
+          const float a0 = (float)pos * inv_freq[d], a1 = (float)pos * inv_freq[d + 1];
+          const float c0 = cosf(a0), s0 = sinf(a0), c1 = cosf(a1), s1 = sinf(a1);
+#pragma unroll
+          for (int row = 0; row < 2; ++row) {
+            const int r = half * 2 + row;
+            const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks][r]);
+            const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks + kD / 32][r]);
+            const float f0 = __bfloat162float(lo.x), f1 = __bfloat162float(lo.y);
+            const float g0 = __bfloat162float(hi.x), g1 = __bfloat162float(hi.y);
+            qa[ks][r] = pack_bf16(f0 * c0 - g0 * s0, f1 * c1 - g1 * s1);
+            qa[ks + kD / 32][r] = pack_bf16(g0 * c0 + f0 * s0, g1 * c1 + f1 * s1);
+          }
+        }
+      }
+    }
+  }
+
   float o[kD / 8][4];
 #pragma unroll
   for (int i = 0; i < kD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -107,17 +180,6 @@ __global__ void __launch_bounds__(kWarps * 32)
   float row_sum[2] = {0.0f, 0.0f};
   const float sl2 = scale * kLog2e;
 
-  // prologue: this warp's tiles are tile_begin + warp, + kWarps, ...
-  int next_load = tile_begin + warp;
-#pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (next_load < tile_end) {
-      __nv_bfloat16* ks = stage_base + (size_t)s * 2 * kTileElems;
-      load_tile(ks, ks + kTileElems, pages, table, next_load * kTileKeys, lo, n_keys, kvh, kv_heads, page_size, lane);
-    }
-    cp_async_commit();
-    next_load += kWarps;
-  }
   int stage = 0;
   for (int tile = tile_begin + warp; tile < tile_end; tile += kWarps) {
     // prefetch the tile kStages-1 ahead into the stage consumed last iteration
@@ -132,8 +194,36 @@ __global__ void __launch_bounds__(kWarps * 32)
     }
     cp_async_wait<kStages - 1>();
     __syncwarp();
-    const __nv_bfloat16* k_smem = stage_base + (size_t)stage * 2 * kTileElems;
-    const __nv_bfloat16* v_smem = k_smem + kTileElems;
+    __nv_bfloat16* k_smem = stage_base + (size_t)stage * 2 * kTileElems;
+    __nv_bfloat16* v_smem = k_smem + kTileElems;
+    if (patch_new && tile == pos / kTileKeys) {
+      const __nv_bfloat16* k_new = q + (size_t)seq * q_row_stride + (size_t)(q_heads + kvh) * kD;
+      const __nv_bfloat16* v_new = k_new + (size_t)kv_heads * kD;
+      const size_t plane = (size_t)kv_heads * page_size * kD;
+      __nv_bfloat16* k_dst = pages + (size_t)table[pos / page_size] * 2 * plane + ((size_t)kvh * page_size + (pos % page_size)) * kD;
+      const int row = pos % kTileKeys;
+      for (int d = lane; d < kD / 2; d += 32) {
+        float first = __bfloat162float(k_new[d]), second = __bfloat162float(k_new[d + kD / 2]);
+        if (inv_freq != nullptr) {
+          const float angle = (float)pos * inv_freq[d];
+          const float c = cosf(angle), sn = sinf(angle);
+          const float a = first * c - second * sn, b = second * c + first * sn;
+          first = a;
+          second = b;
+        }
+        const __nv_bfloat16 kf = __float2bfloat16_rn(first), ks2 = __float2bfloat16_rn(second);
+        k_smem[row * kRow + d] = kf;
+        k_smem[row * kRow + d + kD / 2] = ks2;
+        k_dst[d] = kf;
+        k_dst[d + kD / 2] = ks2;
+      }
+      for (int d = lane; d < kD; d += 32) {
+        const __nv_bfloat16 v = v_new[d];
+        v_smem[row * kRow + d] = v;
+        k_dst[plane + d] = v;
+      }
+      __syncwarp();
+    }
 
     // S = Q . K^T  (16 rows x 32 keys)
     float s_frag[kTileKeys / 8][4];
@@ -262,24 +352,41 @@ __global__ void __launch_bounds__(kWarps * 32)
       }
     }
   }
-}
-
-__global__ void decode_attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                              __nv_bfloat16* __restrict__ out, int splits) {
-  const size_t pair = blockIdx.x;  // request * q_heads + head
-  const float* ml = partial_ml + pair * splits * 2;
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[s * 2]);
-  for (int d = threadIdx.x; d < kD; d += blockDim.x) {
-    float acc = 0.0f, sum = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-      const float sm = ml[s * 2];
-      const float f = (sm == -INFINITY) ? 0.0f : exp2f(sm - m);
-      acc += f * partial_o[(pair * splits + s) * kD + d];
-      sum += f * ml[s * 2 + 1];
-    }
-    out[pair * kD + d] = __float2bfloat16_rn(acc / sum);
+  if (splits == 1) return;
+  // The CTA of this (request, kv head) that arrives last merges all parts.  No CTA waits for another.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&tickets[seq * kv_heads + kvh], 1);
+    last_arrival = (ticket == splits - 1);
   }
+  __syncthreads();
+  if (!last_arrival) return;
+  __threadfence();
+  // one warp per query head; lane sp holds part sp's maximum and sum (splits <= 32), so every load is issued at once
+  for (int r = warp; r < group; r += kWarps) {
+    const size_t pair = (size_t)seq * q_heads + kvh * group + r;
+    const float* ml = partial_ml + pair * splits * 2;
+    float part_max = -INFINITY, part_sum = 0.0f;
+    if (lane < splits) {
+      part_max = __ldcg(ml + lane * 2);
+      part_sum = __ldcg(ml + lane * 2 + 1);
+    }
+    const float m = warp_max(part_max);
+    const float f = (part_max == -INFINITY) ? 0.0f : exp2f(part_max - m);
+    const float sum = warp_sum(f * part_sum);
+    for (int d0 = 0; d0 < kD; d0 += 32) {
+      const int d = d0 + lane;
+      float acc = 0.0f;
+#pragma unroll 8
+      for (int sp = 0; sp < splits; ++sp) {
+        const float fs = __shfl_sync(0xffffffffu, f, sp);
+        if (d < kD) acc += fs * __ldcg(partial_o + (pair * splits + sp) * kD + d);
+      }
+      if (d < kD) out[pair * kD + d] = __float2bfloat16_rn(acc / sum);
+    }
+  }
+  if (threadIdx.x == 0) tickets[seq * kv_heads + kvh] = 0;   // ready for the next launch
 }
 
 constexpr size_t kPipelineBytes = (size_t)kWarps * kStages * 2 * kTileElems * sizeof(__nv_bfloat16);
@@ -292,17 +399,22 @@ using namespace tlie;
 
 TLIE_EXPORT int tlie_decode_attention_head_dim() { return kD; }
 
-// Scratch needed for `splits` > 1: floats for partial_o and partial_ml.
+constexpr int kMaxTickets = 16384;   // requests * kv_heads a launch may have
+
+// Scratch: kMaxTickets counters (zero when first used; every launch leaves them zero), then for splits > 1 the parts.
 TLIE_EXPORT long long tlie_decode_attention_scratch_floats(int requests, int q_heads, int splits) {
-  return splits <= 1 ? 0 : (long long)requests * q_heads * splits * (kD + 2);
+  return kMaxTickets + (splits <= 1 ? 0 : (long long)requests * q_heads * splits * (kD + 2));
 }
 
-TLIE_EXPORT int tlie_decode_attention(const void* q, int q_row_stride, const void* pages, const int* positions,
+// fuse_rope 0: q in `q` is rotated and the cache holds the new keys.  fuse_rope 1: rows of `q` are [q | k | v] of the new
+// token, unrotated; inv_freq (kD / 2 frequencies, or null for no rotation) rotates q and k here, and write_cache stores k, v.
+TLIE_EXPORT int tlie_decode_attention(const void* q, int q_row_stride, void* pages, const int* positions,
                                       const int* block_table, int table_stride, void* out, float* scratch, int requests,
                                       int q_heads, int kv_heads, int page_size, int window, float scale, int splits,
-                                      cudaStream_t stream) {
+                                      int fuse_rope, const float* inv_freq, int write_cache, cudaStream_t stream) {
   if (requests <= 0) return 0;
-  if (kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || splits < 1 || (splits > 1 && scratch == nullptr))
+  if (kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || splits < 1 || splits > 32 || scratch == nullptr ||
+      (long long)requests * kv_heads > kMaxTickets || (fuse_rope && inv_freq != nullptr && kD % 32 != 0))
     return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
@@ -310,15 +422,11 @@ TLIE_EXPORT int tlie_decode_attention(const void* q, int q_row_stride, const voi
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  float* partial_o = scratch;
-  float* partial_ml = scratch ? scratch + (size_t)requests * q_heads * splits * kD : nullptr;
+  int* tickets = reinterpret_cast<int*>(scratch);
+  float* partial_o = scratch + kMaxTickets;
+  float* partial_ml = partial_o + (size_t)requests * q_heads * splits * kD;
   dim3 grid(splits, kv_heads, requests);
-  decode_attention_kernel<<<grid, kWarps * 32, kSmemBytes, stream>>>(
-      (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)pages, positions, block_table, table_stride,
-      (__nv_bfloat16*)out, partial_o, partial_ml, q_heads, kv_heads, page_size, window, scale, splits);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess || splits == 1) return (int)e;
-  decode_attention_merge_kernel<<<requests * q_heads, kD < 128 ? 64 : 128, 0, stream>>>(partial_o, partial_ml,
-                                                                                        (__nv_bfloat16*)out, splits);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(decode_attention_kernel, grid, dim3(kWarps * 32), kSmemBytes, stream, (const __nv_bfloat16*)q, q_row_stride,
+                         (__nv_bfloat16*)pages, positions, block_table, table_stride, (__nv_bfloat16*)out, partial_o, partial_ml,
+                         tickets, q_heads, kv_heads, page_size, window, scale, splits, fuse_rope, inv_freq, write_cache);
 }

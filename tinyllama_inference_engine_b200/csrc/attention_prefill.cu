@@ -31,22 +31,30 @@ constexpr int kRow = kD + 8;    // padded shared-memory row (elements)
 constexpr int kChunks = kD / 8;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// A page holds a multiple of 16 keys, so each 16-key quarter of a tile lies in one page: the table is read
+// once per quarter, not once per row.
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_smem, __nv_bfloat16* v_smem, const __nv_bfloat16* pages,
                                              const int* table, int key0, int lo, int n_keys, int kvh, int kv_heads,
                                              int page_size) {
   const size_t plane = (size_t)kv_heads * page_size * kD;
+  const __nv_bfloat16* quarter_base[kKeys / 16];
+#pragma unroll
+  for (int h = 0; h < kKeys / 16; ++h) {
+    const int k = key0 + 16 * h;
+    const bool any = k < n_keys && k + 16 > lo;
+    const int page = any ? table[k / page_size] : 0;
+    quarter_base[h] = pages + (size_t)page * 2 * plane + ((size_t)kvh * page_size + (k % page_size)) * kD;
+  }
+#pragma unroll
   for (int idx = threadIdx.x; idx < kKeys * kChunks; idx += kWarps * 32) {
     const int row = idx / kChunks;
     const int chunk = idx - row * kChunks;
     const int key = key0 + row;
     const bool valid = key >= lo && key < n_keys;
-    const __nv_bfloat16* src = pages;
-    if (valid) {
-      const int page = table[key / page_size];
-      src = pages + (size_t)page * 2 * plane + ((size_t)kvh * page_size + (key % page_size)) * kD + chunk * 8;
-    }
-    cp_async_16(k_smem + row * kRow + chunk * 8, src, valid);
-    cp_async_16(v_smem + row * kRow + chunk * 8, valid ? src + plane : src, valid);
+    const int quarter = row >> 4;
+    const __nv_bfloat16* src = (quarter == 0 ? quarter_base[0] : quarter == 1 ? quarter_base[1] : quarter == 2 ? quarter_base[2] : quarter_base[3]) + (row & 15) * kD + chunk * 8;
+    cp_async_16(k_smem + row * kRow + chunk * 8, valid ? src : pages, valid);
+    cp_async_16(v_smem + row * kRow + chunk * 8, valid ? src + plane : pages, valid);
   }
 }
 

@@ -37,6 +37,9 @@ class DecodeSession:
         self._offsets = offsets
         view = lambda buffer, i: buffer[offsets[i] : offsets[i + 1]]  # noqa: E731
         self.h_tokens, self.h_positions = view(self._host, 0), view(self._host, 1)
+        self._np = self._host.numpy()                       # the same pinned memory, for cheap host writes
+        self._sampled_host = torch.zeros(count, dtype=torch.int32).pin_memory()
+        self._capacity = [0] * count                        # tokens each request's pages hold (least over the groups)
         self.h_tables = [view(self._host, 8 + g).view(count, width) for g in range(groups)]
         view(self._host, 2).copy_(torch.arange(count))
         view(self._host, 3).copy_(torch.arange(count + 1))
@@ -76,12 +79,12 @@ class DecodeSession:
                 raise BatchError(f"request {request_id!r} is not live; a decode session continues requests that were prefilled")
             self.positions[i] = self.cache.computed(request_id)
             slots.append(self.cache.records[request_id].slot)
-        self.h_tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
-        self.h_positions.copy_(torch.tensor(self.positions, dtype=torch.int32))
         o = self._offsets
-        self._host[o[4] : o[5]].copy_(self.h_positions + 1)   # seq_lens
-        self._host[o[5] : o[6]].copy_(self.h_positions)       # first_positions
-        self._host[o[6] : o[7]].copy_(torch.tensor(slots, dtype=torch.int32))
+        self._np[o[0] : o[1]] = tokens
+        self._np[o[1] : o[2]] = self.positions
+        self._np[o[4] : o[5]] = [p + 1 for p in self.positions]   # seq_lens
+        self._np[o[5] : o[6]] = self.positions                    # first_positions
+        self._np[o[6] : o[7]] = slots
         self.ctx.host_state_slots = slots
         self._reserve_and_fill_tables()
         self._fresh = False
@@ -96,16 +99,21 @@ class DecodeSession:
     def _reserve_and_fill_tables(self) -> bool:
         """Pages for this step's positions; returns whether any block-table row changed."""
         changed = False
+        page_size = self.cache.page_size
         for i, request_id in enumerate(self.request_ids):
-            before = [len(self.cache.records[request_id].tables.get(g.index, [])) for g in self.cache.page_groups]
+            if self.positions[i] < self._capacity[i] and not self._fresh:
+                continue  # the position lies in a page the request already holds
             self.cache.reserve(request_id, self.positions[i] + 1)
+            record = self.cache.records[request_id]
+            capacity = 1 << 60
             for g, group in enumerate(self.cache.page_groups):
-                table = self.cache.records[request_id].tables.get(group.index, [])
-                if len(table) != before[g] or self._fresh:
-                    row = self.h_tables[g][i]
-                    row.fill_(-1)
-                    row[: len(table)] = torch.tensor(table, dtype=torch.int32)
-                    changed = True
+                table = record.tables.get(group.index, [])
+                capacity = min(capacity, len(table) * page_size)
+                row = self.h_tables[g][i].numpy()
+                row[:] = -1
+                row[: len(table)] = table
+            self._capacity[i] = capacity
+            changed = True
         return changed
 
     # --- stepping ----------------------------------------------------------------------------
@@ -118,8 +126,14 @@ class DecodeSession:
 
     def set_tokens(self, tokens: list[int]) -> None:
         """Host tokens in: the step's input ids come from pinned host memory."""
-        self.h_tokens.copy_(torch.tensor(tokens, dtype=torch.int32))
+        self._np[: self.count] = tokens
         self._device[: self.count].copy_(self.h_tokens, non_blocking=True)
+
+    def read_tokens(self) -> list[int]:
+        """Host tokens out: the tokens the last step sampled, through pinned host memory."""
+        self._sampled_host.copy_(self.sampled, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._sampled_host.tolist()
 
     def step(self) -> torch.Tensor:
         """One decode step for every request; returns the sampled tokens (device, int32).
@@ -151,9 +165,10 @@ class DecodeSession:
             self.graph.replay()
         else:
             self.graph.replay()
+        advance = self.cache.advance
         for i, request_id in enumerate(self.request_ids):
             self.positions[i] += 1
-            self.cache.advance(request_id, self.positions[i])
+            advance(request_id, self.positions[i])
         self.runner.steps += 1
         self.runner.tokens_run += self.count
         return self.sampled

@@ -54,6 +54,13 @@ class Request:
     def tokens(self) -> list[int]:
         return self.prompt + self.generated
 
+    def next_tokens(self, count: int) -> list[int]:
+        """The ``count`` tokens after the ones already run."""
+        start, split = self.computed, len(self.prompt)
+        if start >= split:
+            return self.generated[start - split : start - split + count]
+        return (self.prompt[start : start + count] + self.generated[: max(0, start + count - split)])[:count]
+
     @property
     def total(self) -> int:
         return len(self.prompt) + len(self.generated)
@@ -61,4 +68,4 @@ class Request:
     @property
     def remaining(self) -> int:
         """Tokens known but not yet run; the last of them yields the next token."""
-        return self.total - self.computed
+        return len(self.prompt) + len(self.generated) - self.computed

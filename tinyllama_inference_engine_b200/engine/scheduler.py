@@ -89,18 +89,21 @@ class Scheduler:
             chosen.append(ScheduledPortion(request, tokens, need))
             return True
 
-        decodes = [r for r in self.running if r.remaining == 1]
-        prefills = sorted((r for r in self.running if r.remaining > 1), key=lambda r: r.arrival)
+        decodes, prefills = [], []
+        for r in self.running:
+            (decodes if r.remaining == 1 else prefills).append(r)
+        prefills.sort(key=lambda r: r.arrival)
         if decodes:
             start = self._cursor % len(decodes)
             decodes = decodes[start:] + decodes[:start]
         taken_decodes = 0
         for request in decodes + prefills:
             while request.state == RUNNING and budget > 0:
-                tokens = min(request.remaining, budget)
+                remaining = request.remaining
+                tokens = min(remaining, budget)
                 if try_take(request, tokens, live=True):
                     budget -= tokens
-                    taken_decodes += request.remaining == 1
+                    taken_decodes += remaining == 1
                     break
                 room = self.cache.max_total(request.request_id, free) - request.computed
                 if 1 <= room < tokens and try_take(request, room, live=True):

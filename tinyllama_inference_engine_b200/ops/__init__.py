@@ -259,6 +259,21 @@ def paged_attention(qkv, pages, positions, token_seq, block_table, out, q_heads:
     )
 
 
+def attention_step(qkv, positions, token_seq, block_table, inv_freq, rotary_dim: int, pages, out, q_heads: int, kv_heads: int,
+                   head_dim: int, page_size: int, window: int = 0, scale: float | None = None, write_cache: bool = True, batch=None) -> None:
+    """Rotate q and k, store k and v in the pages, and attend: ``rope_store`` then ``paged_attention``, in one kernel where one exists."""
+    if qkv.dtype == torch.bfloat16:
+        from . import fast
+
+        if fast.can_fuse_rope_into_decode(batch, qkv, head_dim, q_heads, kv_heads, inv_freq, rotary_dim):
+            splits = fast.decode_splits(batch.num_seqs, kv_heads, batch.max_seq_len)
+            fast.decode_attention(qkv, pages, positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window,
+                                  head_dim ** -0.5 if scale is None else scale, splits, fuse_rope=True, inv_freq=inv_freq, write_cache=write_cache)
+            return
+    rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim, pages, q_heads, kv_heads, head_dim, page_size, write_cache)
+    paged_attention(qkv, pages, positions, token_seq, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, batch)
+
+
 # --- sampling ------------------------------------------------------------------------------
 def argmax(logits, out) -> None:
     """out[r] = index of the largest logit of row r, the lowest index on ties."""

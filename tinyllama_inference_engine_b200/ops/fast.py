@@ -131,38 +131,49 @@ def decode_attention_library(head_dim: int):
 
 
 def decode_splits(requests: int, kv_heads: int, max_context: int) -> int:
-    """Parts the key range is cut into so that about two CTAs per SM exist; at least 128 keys per part."""
-    by_occupancy = -(-2 * SM_COUNT // max(1, requests * kv_heads))
-    by_length = max(1, -(-max_context // 128))
-    return max(1, min(by_occupancy, by_length))
+    """Parts the key range is cut into: about one CTA (eight warps) per SM, at least 256 keys per part, at most 32 parts."""
+    by_occupancy = -(-SM_COUNT // max(1, requests * kv_heads))
+    by_length = max(1, -(-max_context // 256))
+    return max(1, min(by_occupancy, by_length, 32))
 
 
 def scratch(device: torch.device, floats: int) -> torch.Tensor:
     """Scratch memory of stable address (captured graphs keep pointing at it): grown, never freed."""
     held = _scratch.setdefault(device, [])
     if not held or held[-1].numel() < floats:
-        held.append(torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device))
+        held.append(torch.zeros(max(floats, 1 << 20), dtype=torch.float32, device=device))  # zero: it starts with the merge counters
     return held[-1]
 
 
 def decode_attention(qkv, pages, positions, block_table, out, q_heads: int, kv_heads: int, head_dim: int, page_size: int,
-                     window: int, scale: float, splits: int) -> None:
-    """One query token per request (row i of qkv belongs to request i) over its cached keys; bfloat16."""
+                     window: int, scale: float, splits: int, fuse_rope: bool = False, inv_freq=None, write_cache: bool = True) -> None:
+    """One query token per request (row i of qkv belongs to request i) over its cached keys; bfloat16.
+
+    ``fuse_rope``: the rows of qkv are the unrotated [q | k | v] of the new tokens; the kernel rotates q and k with
+    ``inv_freq`` (None: no rotation) and, with ``write_cache``, stores the new key and value in the request's page.
+    """
     ops = _ops()
     requests = qkv.shape[0]
     lib = decode_attention_library(head_dim)
     floats = lib.tlie_decode_attention_scratch_floats(c_int(requests), c_int(q_heads), c_int(splits))
-    buffer = scratch(qkv.device, floats) if floats else None
+    buffer = scratch(qkv.device, floats)
     ops._check(
         lib.tlie_decode_attention(
             ops._ptr(qkv), c_int(qkv.shape[1]), ops._ptr(pages), ops._i32(positions, "positions"), ops._i32(block_table, "block_table"),
             c_int(block_table.shape[1]), ops._ptr(out), ops._ptr(buffer), c_int(requests), c_int(q_heads), c_int(kv_heads), c_int(page_size),
-            c_int(window), c_float(scale), c_int(splits), ops._stream(),
+            c_int(window), c_float(scale), c_int(splits), c_int(1 if fuse_rope else 0), ops._ptr(inv_freq), c_int(1 if write_cache else 0), ops._stream(),
         ),
         "decode_attention",
     )
-    if splits > 1:
-        ops.launch_count += 1  # the merge kernel
+
+
+def can_fuse_rope_into_decode(batch, qkv, head_dim: int, q_heads: int, kv_heads: int, inv_freq, rotary_dim: int) -> bool:
+    """Whether a decode step's rotation and cache write can happen inside the attention kernel."""
+    if batch is None or qkv.dtype != torch.bfloat16 or not batch.decode_only or qkv.shape[0] != batch.num_seqs:
+        return False
+    if head_dim > 128 or q_heads // kv_heads > 16 or batch.num_seqs * kv_heads > 16384:
+        return False
+    return inv_freq is None or (rotary_dim == head_dim and head_dim % 32 == 0)
 
 
 # --- prompt (and mixed) attention -----------------------------------------------------------------

@@ -68,11 +68,10 @@ class Attention(Mixer):
             inv_freq, rotary_dim = None, 0
         else:
             inv_freq, rotary_dim = table
-        ops.rope_store(qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rotary_dim, cache.pages,
-                       self.q_heads, self.kv_heads, self.head_dim, cache.page_size, write_cache=cache.writes)
         mixed = ws.get("attention", tokens, self.q_heads * self.head_dim, dtype)
-        ops.paged_attention(qkv, cache.pages, ctx.positions, ctx.token_seq, cache.block_table, mixed,
-                            self.q_heads, self.kv_heads, self.head_dim, cache.page_size, self.window, self.scale, batch=ctx)
+        ops.attention_step(qkv, ctx.positions, ctx.token_seq, cache.block_table, inv_freq, rotary_dim, cache.pages, mixed,
+                           self.q_heads, self.kv_heads, self.head_dim, cache.page_size, self.window, self.scale,
+                           write_cache=cache.writes, batch=ctx)
         if accumulate_into is not None:
             ops.linear_accumulate(mixed, self.w_o, accumulate_into)
             return None
