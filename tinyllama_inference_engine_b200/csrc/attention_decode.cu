@@ -27,6 +27,7 @@
 // captured graph serves every later step.
 //
 // Compile-time: HEAD_DIM (multiple of 16, <= 256).
+#include "attention_decode.h"
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -429,4 +430,47 @@ TLIE_EXPORT int tlie_decode_attention(const void* q, int q_row_stride, void* pag
   return (int)launch_pdl(decode_attention_kernel, grid, dim3(kWarps * 32), kSmemBytes, stream, (const __nv_bfloat16*)q, q_row_stride,
                          (__nv_bfloat16*)pages, positions, block_table, table_stride, (__nv_bfloat16*)out, partial_o, partial_ml,
                          tickets, q_heads, kv_heads, page_size, window, scale, splits, fuse_rope, inv_freq, write_cache);
+}
+
+// --- the entry point that allocates nothing (declared and documented in attention_decode.h) --------------------
+constexpr int kStaticMaxSlots = 8192;   // (request, head, part) triples the built-in scratch has room for
+constexpr size_t kStaticScratchFloats = (size_t)kMaxTickets + (size_t)kStaticMaxSlots * (kD + 2);
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: the address a kernel can
+// use is looked up once per device, with that device current.
+static float* static_scratch_address(cudaError_t* error) {
+  static float* address[64] = {};
+  int device = 0;
+  *error = cudaGetDevice(&device);
+  if (*error != cudaSuccess) return nullptr;
+  if (device < 0 || device >= 64) {
+    *error = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  if (address[device] == nullptr) {
+    void* found = nullptr;
+    *error = cudaGetSymbolAddress(&found, g_static_scratch);
+    if (*error != cudaSuccess) return nullptr;
+    address[device] = static_cast<float*>(found);
+  }
+  return address[device];
+}
+
+TLIE_EXPORT int tlie_decode_attention_static(const void* q, int q_row_stride, void* pages, const int* positions,
+                                             const int* block_table, int table_stride, void* out, int requests,
+                                             int q_heads, int kv_heads, int page_size, int window, float scale, int splits,
+                                             int fuse_rope, const float* inv_freq, int write_cache, cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  if (splits < 1 || q_heads <= 0 || (long long)requests * q_heads * splits > kStaticMaxSlots ||
+      (long long)requests * kv_heads > kMaxTickets)
+    return (int)cudaErrorInvalidValue;   // beyond the built-in scratch: nothing is launched
+  cudaError_t error = cudaSuccess;
+  float* scratch = static_scratch_address(&error);
+  if (scratch == nullptr) return (int)error;
+  // the arrival counters must start at zero; the rest of the array is written before it is read
+  error = cudaMemsetAsync(scratch, 0, (size_t)requests * kv_heads * sizeof(int), stream);
+  if (error != cudaSuccess) return (int)error;
+  return tlie_decode_attention(q, q_row_stride, pages, positions, block_table, table_stride, out, scratch, requests, q_heads,
+                               kv_heads, page_size, window, scale, splits, fuse_rope, inv_freq, write_cache, stream);
 }
