@@ -192,6 +192,8 @@ def linear_gated(x, weight, out) -> None:
 
     if fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True):
         fast.gemv_fused(x, weight, out, epilogue="gated")
+    elif fast.use_tcgen05 and x.shape[0] >= fast.TCGEN05_MIN_ROWS and weight.shape[1] % 8 == 0 and x.is_contiguous():
+        fast.gemm_tcgen05_gated(x, weight, out)
     else:
         gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
         linear(x, weight, gate_up)

@@ -23,6 +23,7 @@ def build_all() -> list:
     built += [build_library(f"tlie_attn_prefill_d{d}", ["attention_prefill.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
     built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
     built.append(build_library("tlie_gemv_fused", ["gemv_fused.cu"]))
+    built.append(build_library("tlie_gemm_tcgen05", ["gemm_tcgen05.cu"]))
     return built
 
 
@@ -107,12 +108,62 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store") -> None:
     ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), ops._stream()), "gemv_fused")
 
 
+# --- tensor-core product for many rows (tcgen05, TMA, tensor memory) -------------------------------------
+_tcgen05_error: dict[torch.device, torch.Tensor] = {}
+TCGEN05_MIN_ROWS = 128     # from this many rows on the engine's own tcgen05 kernel runs instead of the library's product
+use_tcgen05 = True
+
+
+def tcgen05_library():
+    return load_library("tlie_gemm_tcgen05", ["gemm_tcgen05.cu"])
+
+
+def tcgen05_error_flag(device: torch.device) -> torch.Tensor:
+    """A device int the kernel sets to 1 if one of its bounded waits gave up (read it after a synchronize)."""
+    if device not in _tcgen05_error:
+        _tcgen05_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tcgen05_error[device]
+
+
+def gemm_tcgen05(x, weight, out, tile_n: int | None = None) -> None:
+    """out[M, N] = x[M, K] . weight[N, K]^T on the 5th-generation tensor cores; bfloat16 in, bfloat16 or 32-bit out."""
+    ops = _ops()
+    M, K = x.shape
+    N = weight.shape[0]
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or K % 8 != 0 or not x.is_contiguous():
+        raise KernelError("gemm_tcgen05 takes contiguous bfloat16 operands with K % 8 == 0", code="invalid_shape")
+    if tile_n is None:
+        tile_n = 256 if N >= 1024 and (-(-M // 128)) * (-(-N // 256)) >= 120 else 128
+    ops._check(
+        tcgen05_library().tlie_gemm_tcgen05(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(1 if out.dtype == torch.float32 else 0),
+                                            c_int(tile_n), ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
+        "gemm_tcgen05",
+    )
+
+
+def gemm_tcgen05_gated(x, weight, out) -> None:
+    """out[M, I] = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows] ([2 I, K]), one kernel."""
+    ops = _ops()
+    M, K = x.shape
+    inter = weight.shape[0] // 2
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or K % 8 != 0 or not x.is_contiguous() or out.shape != (M, inter):
+        raise KernelError("gemm_tcgen05_gated takes contiguous bfloat16 operands with K % 8 == 0 and out [M, rows / 2]", code="invalid_shape")
+    ops._check(
+        tcgen05_library().tlie_gemm_tcgen05(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(inter), c_int(K), c_int(2), c_int(256),
+                                            ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
+        "gemm_tcgen05_gated",
+    )
+
+
 def linear_bf16(x, weight, out) -> None:
     global library_gemm_calls
     if weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("linear: the bfloat16 path takes bfloat16 weights", code="invalid_dtype")
     if x.stride(0) % 8 == 0 and gemv_fits(x.shape[0], weight.shape[1], norm=False):
         gemv_fused(x, weight, out)
+        return
+    if use_tcgen05 and x.shape[0] >= TCGEN05_MIN_ROWS and weight.shape[1] % 8 == 0 and x.is_contiguous():
+        gemm_tcgen05(x, weight, out)
         return
     library_gemm_calls += 1
     if out.dtype == torch.float32:

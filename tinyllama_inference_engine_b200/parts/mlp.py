@@ -50,6 +50,8 @@ class GatedMLP(FeedForward):
                 ops.norm_linear(x, self.w_gate_up, act, gated=True)
             else:
                 ops.linear_gated(x, self.w_gate_up, act)
+        elif dtype == torch.bfloat16:
+            ops.linear_gated(x.tensor() if isinstance(x, ops.LazyNorm) else x, self.w_gate_up, act)   # picks the fused kernel for its size
         else:
             if isinstance(x, ops.LazyNorm):
                 x = x.tensor()
