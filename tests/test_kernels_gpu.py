@@ -259,7 +259,8 @@ def test_prefill_attention_flash(ops, q_heads, kv_heads, head_dim, page_size, wi
     plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)
     starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     firsts = np.array([s - q for s, q in zip(seq_lens, q_lens)], dtype=np.int32)
-    tiles = [[i, int(starts[i]) + off] for i, q in enumerate(q_lens) for off in range(0, q, 64)]
+    from tinyllama_inference_engine_b200.engine.batch import ATTENTION_TILE_ROWS
+    tiles = [[i, int(starts[i]) + off] for i, q in enumerate(q_lens) for off in range(0, q, ATTENTION_TILE_ROWS)]
     pages_gpu = pages.cuda()
     held = set(int(p) for p in table.flatten() if p >= 0)
     for page in range(pages.shape[0]):

@@ -6,8 +6,8 @@
 // the cached keys lo..p of that request (lo = max(0, p - window + 1) with a window), with a 32-bit
 // running maximum and sum, so the scores are never materialised.
 //
-// Work is a host-built list of tiles (request, first row): 64 consecutive query rows of one request,
-// one CTA per (tile, query head), four warps of 16 rows each.  Keys and values stream through shared
+// Work is a host-built list of tiles (request, first row): up to PREFILL_ROWS (64) consecutive query rows of one request,
+// one CTA per (tile, query head), one warp per 16 rows.  Keys and values stream through shared
 // memory in 64-key tiles with a two-stage cp.async pipeline, read through the request's block table
 // (rows padded by 16 bytes: ldmatrix without bank conflicts at any head size); q.K^T and P.V run on
 // the tensor cores (mma.sync m16n8k16, bf16 in, 32-bit accumulate).  The eight query heads of a
@@ -24,9 +24,12 @@
 namespace tlie {
 
 constexpr int kD = HEAD_DIM;
-constexpr int kRows = 64;       // query rows per CTA
-constexpr int kKeys = 64;       // keys per tile
-constexpr int kWarps = 4;
+#ifndef PREFILL_ROWS
+#define PREFILL_ROWS 64
+#endif
+constexpr int kRows = PREFILL_ROWS;   // query rows per CTA (16 per warp)
+constexpr int kKeys = 64;             // keys per tile
+constexpr int kWarps = kRows / 16;
 constexpr int kRow = kD + 8;    // padded shared-memory row (elements)
 constexpr int kChunks = kD / 8;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -59,7 +62,7 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_smem, __nv_bfloat1
 }
 
 // tiles: [n_tiles][2] = (request index in the step, first row of the tile in the step's row numbering)
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, kD <= 64 ? (kRows == 64 ? 3 : 2) : 1)
     prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ pages,
                              const int* __restrict__ tiles, const int* __restrict__ seq_starts,
                              const int* __restrict__ first_positions, const int* __restrict__ block_table, int table_stride,
@@ -68,8 +71,10 @@ __global__ void __launch_bounds__(kWarps * 32)
   __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* q_smem = smem;                                   // [64][kRow]
   __nv_bfloat16* kv_smem = smem + kRows * kRow;                   // [2 stages][K, V][64][kRow]
-  const int seq = tiles[blockIdx.x * 2];
-  const int row0 = tiles[blockIdx.x * 2 + 1];
+  // later tiles of a request see more keys and take longer: start them first so that the tail of the grid is short
+  const int tile_index = gridDim.x - 1 - blockIdx.x;
+  const int seq = tiles[tile_index * 2];
+  const int row0 = tiles[tile_index * 2 + 1];
   const int head = blockIdx.y;
   const int kvh = head / (q_heads / kv_heads);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,16 +159,28 @@ __global__ void __launch_bounds__(kWarps * 32)
           mma_bf16(s_frag[jp * 2 + 1], qa[ks], b[2], b[3]);
         }
       }
+      // Scores stay unscaled; the scale is folded into the exponent: p = 2^(s * sl2 - max * sl2).
+      // Only tiles that touch the diagonal (or the window's edge) of this warp's rows need the mask.
+      const int warp_first_pos = pos0 + min(warp * 16, rows_here - 1);
+      const bool need_mask = key0 + kKeys - 1 > warp_first_pos || (window > 0 && key0 < warp_last_pos - window + 1);
       float tile_max[2] = {-INFINITY, -INFINITY};
+      if (need_mask) {
 #pragma unroll
-      for (int j = 0; j < kKeys / 8; ++j) {
+        for (int j = 0; j < kKeys / 8; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = key0 + j * 8 + 2 * t + (e & 1);
-          const int r = e >> 1;
-          const float v = (key >= my_lo[r] && key <= my_pos[r]) ? s_frag[j][e] * sl2 : -INFINITY;
-          s_frag[j][e] = v;
-          tile_max[r] = fmaxf(tile_max[r], v);
+          for (int e = 0; e < 4; ++e) {
+            const int key = key0 + j * 8 + 2 * t + (e & 1);
+            const int r = e >> 1;
+            const float v = (key >= my_lo[r] && key <= my_pos[r]) ? s_frag[j][e] : -INFINITY;
+            s_frag[j][e] = v;
+            tile_max[r] = fmaxf(tile_max[r], v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kKeys / 8; ++j) {
+          tile_max[0] = fmaxf(tile_max[0], fmaxf(s_frag[j][0], s_frag[j][1]));
+          tile_max[1] = fmaxf(tile_max[1], fmaxf(s_frag[j][2], s_frag[j][3]));
         }
       }
       float rescale[2], base[2];
@@ -172,18 +189,19 @@ __global__ void __launch_bounds__(kWarps * 32)
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
         const float new_max = fmaxf(row_max[r], tile_max[r]);
-        base[r] = (new_max == -INFINITY) ? 0.0f : new_max;   // a row may see no key in an early tile (window)
-        rescale[r] = exp2f(row_max[r] - base[r]);
+        const float finite_max = (new_max == -INFINITY) ? 0.0f : new_max;   // a row may see no key in an early tile (window)
+        base[r] = finite_max * sl2;
+        rescale[r] = exp2f((row_max[r] - finite_max) * sl2);
         row_max[r] = new_max;
         row_sum[r] *= rescale[r];
       }
       unsigned pa[kKeys / 16][4];
 #pragma unroll
       for (int j = 0; j < kKeys / 8; ++j) {
-        const float p0 = exp2f(s_frag[j][0] - base[0]);
-        const float p1 = exp2f(s_frag[j][1] - base[0]);
-        const float p2 = exp2f(s_frag[j][2] - base[1]);
-        const float p3 = exp2f(s_frag[j][3] - base[1]);
+        const float p0 = exp2f(fmaf(s_frag[j][0], sl2, -base[0]));
+        const float p1 = exp2f(fmaf(s_frag[j][1], sl2, -base[0]));
+        const float p2 = exp2f(fmaf(s_frag[j][2], sl2, -base[1]));
+        const float p3 = exp2f(fmaf(s_frag[j][3], sl2, -base[1]));
         row_sum[0] += p0 + p1;
         row_sum[1] += p2 + p3;
         pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -236,6 +254,7 @@ constexpr size_t kSmemBytes = ((size_t)kRows * kRow + 2 * 2 * (size_t)kKeys * kR
 using namespace tlie;
 
 TLIE_EXPORT int tlie_prefill_attention_head_dim() { return kD; }
+TLIE_EXPORT int tlie_prefill_attention_tile_rows() { return kRows; }
 
 TLIE_EXPORT int tlie_prefill_attention(const void* q, int q_row_stride, const void* pages, const int* tiles, int n_tiles,
                                        const int* seq_starts, const int* first_positions, const int* block_table,

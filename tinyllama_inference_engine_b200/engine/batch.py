@@ -6,7 +6,7 @@ from dataclasses import dataclass, field
 import torch
 
 
-ATTENTION_TILE_ROWS = 64
+ATTENTION_TILE_ROWS = 64   # rows of one work item of the prompt-attention kernel (csrc/attention_prefill.cu: PREFILL_ROWS)
 
 
 @dataclass
@@ -31,7 +31,7 @@ class StepContext:
       state_slots[B]              the request's slot in per-request state tensors
       want_rows[W]                rows whose logits are returned, in entry and want order
       block_tables[g][B, width]   page ids of every entry in page group g (-1: none)
-      attn_tiles[N, 2]            (entry, first row) of every run of up to 64 consecutive rows of one entry:
+      attn_tiles[N, 2]            (entry, first row) of every run of up to ATTENTION_TILE_ROWS consecutive rows of one entry:
                                   the work list of the prompt-attention kernel
     """
 

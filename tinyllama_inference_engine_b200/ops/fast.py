@@ -230,7 +230,7 @@ def can_fuse_rope_into_decode(batch, qkv, head_dim: int, q_heads: int, kv_heads:
 # --- prompt (and mixed) attention -----------------------------------------------------------------
 def prefill_attention(qkv, pages, tiles, seq_starts, first_positions, block_table, out, q_heads: int, kv_heads: int, head_dim: int,
                       page_size: int, window: int, scale: float) -> None:
-    """Flash attention of every 64-row tile in ``tiles`` (int32 [n, 2]: request, first row) over the paged cache; bfloat16."""
+    """Flash attention of every tile in ``tiles`` (int32 [n, 2]: request, first row; up to 128 rows each) over the paged cache; bfloat16."""
     ops = _ops()
     lib = load_library(f"tlie_attn_prefill_d{head_dim}", ["attention_prefill.cu"], {"HEAD_DIM": head_dim})
     ops._check(
