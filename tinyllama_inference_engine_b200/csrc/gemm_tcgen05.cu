@@ -10,8 +10,10 @@
 //     epilogue when the last MMA is done;
 //   * four epilogue warps read the accumulator with tcgen05.ld (each warp its 32 lanes), convert and store.
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer, warp 2 = tensor-memory allocation (and epilogue),
-// warps 2..5 = epilogue.  One CTA per 128 x BN tile of the output; TMA zero-fills out-of-range rows and k,
-// the epilogue stores only what is inside [M, N].
+// warps 2..5 = epilogue.  CTAs are persistent: one per SM walks the 128 x BN output tiles blockIdx.x, + gridDim.x, ...
+// (m fastest, so the CTAs running together share a few column blocks of w in L2).  Two accumulators in tensor memory
+// alternate between tiles, so the epilogue of one tile runs under the MMAs of the next.  TMA zero-fills out-of-range
+// rows and k, the epilogue stores only what is inside [M, N].
 // Every mbarrier wait is bounded: on a timeout the CTA raises `error_flag`, stops issuing work, lets copies in
 // flight land, frees its tensor memory and returns.
 #include <cuda.h>
@@ -105,6 +107,7 @@ struct GemmShape {
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kStageBytes = (kBM + BN) * kBK * 2;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
 };
 
 // EPI 0: bfloat16 out; EPI 1: 32-bit out; EPI 2 (BN = 256): w holds [gate rows | up rows] (`N` = rows of one half);
@@ -121,12 +124,16 @@ __global__ void __launch_bounds__(kGemmThreads)
   uint8_t* tiles = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles need 1024-byte alignment
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kStages * Shape::kStageBytes);
   uint64_t* empty = full + kStages;
-  uint64_t* accum_done = empty + kStages;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_done + 1);
+  uint64_t* accum_full = empty + kStages;     // [2]: the MMAs of a tile are done
+  uint64_t* accum_empty = accum_full + 2;      // [2]: the epilogue has read the accumulator
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * (EPI == 2 ? BN / 2 : BN);
+  constexpr int kTileN = EPI == 2 ? BN / 2 : BN;   // output columns of a tile
+  constexpr int kTmemCols = 2 * BN;                // two accumulators
+  const int m_blocks = (M + kBM - 1) / kBM;
+  const int num_tiles = m_blocks * ((N + kTileN - 1) / kTileN);
   const int k_blocks = (K + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
@@ -134,13 +141,16 @@ __global__ void __launch_bounds__(kGemmThreads)
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum_done, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&accum_full[a], 1);
+      mbar_init(&accum_empty[a], 4);   // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   if (warp == 2) {   // the whole warp allocates BN columns of tensor memory and lets other CTAs allocate too
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_holder)), "r"(BN));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_holder)), "r"(kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -149,57 +159,75 @@ __global__ void __launch_bounds__(kGemmThreads)
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 0) {
-    if (lane == 0) {   // TMA producer
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t phase = (kb / kStages) & 1;
-        if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) break;
-        uint8_t* a_tile = tiles + s * Shape::kStageBytes;
-        uint8_t* b_tile = a_tile + kBM * kBK * 2;
-        mbar_expect_tx(&full[s], Shape::kStageBytes);
-        tma_load_2d(a_tile, &map_a, kb * kBK, m0, &full[s]);
-        if (EPI == 2) {
-          tma_load_2d(b_tile, &map_b, kb * kBK, n0, &full[s]);                                  // gate rows
-          tma_load_2d(b_tile + (BN / 2) * kBK * 2, &map_b, kb * kBK, N + n0, &full[s]);        // up rows
-        } else {
-          tma_load_2d(b_tile, &map_b, kb * kBK, n0, &full[s]);
+    if (lane == 0) {   // TMA producer: one ring of stages across all of this CTA's tiles
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_blocks) * kBM, n0 = (tile / m_blocks) * kTileN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          ok = mbar_wait(&empty[s], phase ^ 1, abort_flag);
+          if (!ok) break;
+          uint8_t* a_tile = tiles + s * Shape::kStageBytes;
+          uint8_t* b_tile = a_tile + kBM * kBK * 2;
+          mbar_expect_tx(&full[s], Shape::kStageBytes);
+          tma_load_2d(a_tile, &map_a, kb * kBK, m0, &full[s]);
+          if (EPI == 2) {
+            tma_load_2d(b_tile, &map_b, kb * kBK, n0, &full[s]);                                  // gate rows
+            tma_load_2d(b_tile + (BN / 2) * kBK * 2, &map_b, kb * kBK, N + n0, &full[s]);        // up rows
+          } else {
+            tma_load_2d(b_tile, &map_b, kb * kBK, n0, &full[s]);
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {   // MMA issuer
       constexpr uint32_t idesc = umma_instr_desc(kBM, BN);
+      int it = 0, local = 0;
       bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t phase = (kb / kStages) & 1;
-        ok = mbar_wait(&full[s], phase, abort_flag);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        ok = mbar_wait(&accum_empty[acc], ((local >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t a_addr = smem_u32(tiles + s * Shape::kStageBytes);
-        const uint32_t b_addr = a_addr + kBM * kBK * 2;
+        const uint32_t tmem_acc = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          ok = mbar_wait(&full[s], phase, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_addr = smem_u32(tiles + s * Shape::kStageBytes);
+          const uint32_t b_addr = a_addr + kBM * kBK * 2;
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          // 16 k = 32 bytes further inside the 128-byte swizzle span
-          umma_bf16(tmem_base, umma_smem_desc(a_addr + k * kUmmaK * 2), umma_smem_desc(b_addr + k * kUmmaK * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // 16 k = 32 bytes further inside the 128-byte swizzle span
+            umma_bf16(tmem_acc, umma_smem_desc(a_addr + k * kUmmaK * 2), umma_smem_desc(b_addr + k * kUmmaK * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);   // the stage is free once these MMAs have read it
         }
-        umma_commit(&empty[s]);   // the stage is free once these MMAs have read it
+        if (ok) umma_commit(&accum_full[acc]);
       }
-      if (ok) umma_commit(accum_done);
     }
   }
   if (warp >= 2) {   // epilogue: warp w reads tensor-memory lanes 32 * (w % 4) ... + 31
     const int sub = warp & 3;
-    const bool ok = mbar_wait(accum_done, 0, abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    if (ok) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const int m0 = (tile % m_blocks) * kBM, n0 = (tile / m_blocks) * kTileN;
+      if (!mbar_wait(&accum_full[acc], (local >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + acc * BN + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
       if (EPI == 2) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t gate[16], up[16];
-          tmem_load_16(tmem_base + ((uint32_t)(sub * 32) << 16) + c * 16, gate);
-          tmem_load_16(tmem_base + ((uint32_t)(sub * 32) << 16) + BN / 2 + c * 16, up);
+          tmem_load_16(tmem_acc + c * 16, gate);
+          tmem_load_16(tmem_acc + BN / 2 + c * 16, up);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
           const int col = n0 + c * 16;
           if (row < M && col < N) {
@@ -228,37 +256,37 @@ __global__ void __launch_bounds__(kGemmThreads)
         }
       } else {
 #pragma unroll 1
-      for (int c = 0; c < BN / 16; ++c) {
-        uint32_t r[16];
-        tmem_load_16(tmem_base + ((uint32_t)(sub * 32) << 16) + c * 16, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        const int col = n0 + c * 16;
-        if (row < M && col < N) {
-          if (EPI == 0) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
-            if (col + 16 <= N && (N % 8) == 0) {
-              uint4 lo, hi;
-              __nv_bfloat162 p;
-              uint32_t packed[8];
+        for (int c = 0; c < BN / 16; ++c) {
+          uint32_t r[16];
+          tmem_load_16(tmem_acc + c * 16, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          const int col = n0 + c * 16;
+          if (row < M && col < N) {
+            if (EPI == 0) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
+              if (col + 16 <= N && (N % 8) == 0) {
+                uint32_t packed[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                p = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                packed[i] = *reinterpret_cast<uint32_t*>(&p);
+                for (int i = 0; i < 8; ++i) {
+                  __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                  packed[i] = *reinterpret_cast<uint32_t*>(&p);
+                }
+                *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+              } else {
+                for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
               }
-              lo = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              hi = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-              *reinterpret_cast<uint4*>(dst) = lo;
-              *reinterpret_cast<uint4*>(dst + 8) = hi;
             } else {
-              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+              float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
+              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __uint_as_float(r[i]);
             }
-          } else {
-            float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
-            for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __uint_as_float(r[i]);
           }
         }
       }
-      }
+      // this warp is done with the accumulator: hand it back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&accum_empty[acc])) : "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
@@ -269,7 +297,7 @@ __global__ void __launch_bounds__(kGemmThreads)
   }
   __syncthreads();
   if (warp == 2) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(BN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols));
   }
 }
 
@@ -311,7 +339,14 @@ static int launch_gemm(const void* x, const void* w, void* out, int M, int N, in
     configured = true;
   }
   constexpr int kTileN = EPI == 2 ? BN / 2 : BN;
-  dim3 grid((N + kTileN - 1) / kTileN, (M + kBM - 1) / kBM);
+  const int num_tiles = ((N + kTileN - 1) / kTileN) * ((M + kBM - 1) / kBM);
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
   gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, GemmShape<BN>::kSmemBytes, stream>>>(map_a, map_b, out, M, N, K, error_flag);
   return (int)cudaGetLastError();
 }
