@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 # largest |difference| allowed, as a fraction of the largest |logit| of the request set
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
-LENGTHS = {"a": [1, 7, 33, 100, 128, 65], "b": [3, 19, 64, 100, 255, 130], "c": [2, 40, 77, 300, 129, 64]}
+LENGTHS = {"a": [1, 7, 33, 100, 128, 65], "b": [3, 19, 64, 100, 255, 130], "c": [2, 40, 77, 300, 129, 64], "d": [5, 200, 64, 1100, 129, 700]}
 
 
 @pytest.fixture(scope="module")
@@ -32,8 +32,37 @@ def _runner(folder, dtype, max_tokens=2048, page_size=64):
     return ModelRunner(folder, EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8, max_batch_tokens=128, poison_freed_pages=True))
 
 
+def test_far_key_decides_the_logits(model_folders):
+    """Sharpened attention: with q and k projections scaled up, one early token dominates late positions, so a cache
+    page misplaced or a key dropped far back changes the logits by much more than the tolerance."""
+    import json
+
+    from tinyllama_inference_engine_b200.weights import SafetensorsFile, write_safetensors
+
+    source = model_folders["a"]
+    folder = source.parent / "a_sharp"
+    if not (folder / "model.safetensors").exists():
+        folder.mkdir(exist_ok=True)
+        (folder / "config.json").write_text((source / "config.json").read_text())
+        file = SafetensorsFile(source / "model.safetensors")
+        tensors = {name: file.tensor(name).clone() for name in file.names()}
+        file.close()
+        for name in tensors:
+            if "q_proj" in name or "k_proj" in name:
+                tensors[name] = (tensors[name].float() * 12.0).bfloat16()
+        write_safetensors(folder / "model.safetensors", tensors)
+    config, weights = plain_llama.load_model(folder)
+    requests = trace_tools.make_requests(config["vocab_size"], [128, 100, 77], seed=17)
+    full = {rid: plain_llama.forward(config, weights, tokens) for rid, tokens in requests.items()}
+    scale = max(float(v.abs().max()) for v in full.values())
+    for dtype in ("float32", "bfloat16"):
+        for steps in (trace_tools.tail_decode(requests), trace_tools.portions(requests), trace_tools.mixed(requests, seed=9, page_size=16)[0]):
+            runner = _runner(folder, dtype, max_tokens=1024, page_size=16)
+            trace_tools.run_and_compare(runner, steps, full, atol=TOLERANCE[dtype] * scale)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["a", "b", "c"])
+@pytest.mark.parametrize("key", ["a", "b", "c", "d"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
 def test_replay(cases, key, dtype, cut):
     folder, requests, full, scale = cases[key]

@@ -28,4 +28,13 @@ TINY_C = dict(
 )
 SEED_C = 5
 
-ALL = {"a": (TINY_A, SEED_A), "b": (TINY_B, SEED_B), "c": (TINY_C, SEED_C)}
+# 2 layers, 8 query heads over 2 kv heads of 128 (the head size of the larger Llama checkpoints), long context
+TINY_D = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=320, intermediate_size=200, num_hidden_layers=2,
+    num_attention_heads=8, num_key_value_heads=2, head_dim=128, max_position_embeddings=1100, vocab_size=517,
+    rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False, hidden_act="silu", attention_bias=False,
+    bos_token_id=1, eos_token_id=2, torch_dtype="bfloat16",
+)
+SEED_D = 7
+
+ALL = {"a": (TINY_A, SEED_A), "b": (TINY_B, SEED_B), "c": (TINY_C, SEED_C), "d": (TINY_D, SEED_D)}
