@@ -20,6 +20,7 @@ _scratch: dict[torch.device, list[torch.Tensor]] = {}
 
 def build_all() -> list:
     built = [build_library(f"tlie_attn_decode_d{d}", ["attention_decode.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
+    built.append(build_library("tlie_attn_decode_d64_w4", ["attention_decode.cu"], {"HEAD_DIM": 64, "DECODE_WARPS": 4, "DECODE_STAGES": 3}))
     built += [build_library(f"tlie_attn_prefill_d{d}", ["attention_prefill.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
     built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
     built.append(build_library("tlie_gemv_fused", ["gemv_fused.cu"]))
@@ -173,8 +174,17 @@ def linear_bf16(x, weight, out) -> None:
 
 
 # --- decode attention -------------------------------------------------------------------------
-def decode_attention_library(head_dim: int):
-    lib = load_library(f"tlie_attn_decode_d{head_dim}", ["attention_decode.cu"], {"HEAD_DIM": head_dim})
+def decode_attention_library(head_dim: int, narrow: bool = False):
+    """The decode attention library of a head size.
+
+    Default build: eight warps and two stages per CTA for head sizes up to 64 (one CTA per SM pulls enough bandwidth when
+    there are few (request, kv head) pairs).  ``narrow``: four warps and three stages, two CTAs per SM, for steps with
+    more pairs than SMs, where the wide CTAs would run in two uneven waves.
+    """
+    if narrow and head_dim <= 64:
+        lib = load_library(f"tlie_attn_decode_d{head_dim}_w4", ["attention_decode.cu"], {"HEAD_DIM": head_dim, "DECODE_WARPS": 4, "DECODE_STAGES": 3})
+    else:
+        lib = load_library(f"tlie_attn_decode_d{head_dim}", ["attention_decode.cu"], {"HEAD_DIM": head_dim})
     if not getattr(lib, "_tlie_typed", False):
         lib.tlie_decode_attention_scratch_floats.restype = c_longlong
         lib._tlie_typed = True
@@ -205,7 +215,7 @@ def decode_attention(qkv, pages, positions, block_table, out, q_heads: int, kv_h
     """
     ops = _ops()
     requests = qkv.shape[0]
-    lib = decode_attention_library(head_dim)
+    lib = decode_attention_library(head_dim, narrow=requests * kv_heads > SM_COUNT)
     floats = lib.tlie_decode_attention_scratch_floats(c_int(requests), c_int(q_heads), c_int(splits))
     buffer = scratch(qkv.device, floats)
     ops._check(
