@@ -65,25 +65,55 @@ def peaks() -> tuple[dict, str]:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while a timed region runs (reads only)."""
+    """Samples SM clocks and throttle reasons while a timed region runs (NVML reads only; nvidia-smi as a fallback)."""
 
     QUERY = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self):
-        self.samples: list[list[str]] = []
+        self.clocks: list[int] = []
+        self.max_clock = None
+        self.reasons: set[str] = set()
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        self._nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(0)
+            self.max_clock = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            self._nvml = None
+
+    def _sample_nvml(self) -> None:
+        nv = self._nvml
+        self.clocks.append(int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+        try:
+            mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+        except Exception:  # noqa: BLE001
+            mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+        self.reasons |= {name for name, bit in self.REASONS.items() if mask & bit}
+
+    def _sample_smi(self) -> None:
+        out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout.strip()
+        if out:
+            cells = [c.strip() for c in out.splitlines()[0].split(",")]
+            if cells[0].isdigit():
+                self.clocks.append(int(cells[0]))
+            if cells[1].isdigit():
+                self.max_clock = int(cells[1])
+            self.reasons |= {name for name, flag in zip(self.REASONS, cells[2:6]) if flag.lower().startswith("active")}
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([c.strip() for c in out.splitlines()[0].split(",")])
-            except (OSError, subprocess.SubprocessError):
+                self._sample_nvml() if self._nvml is not None else self._sample_smi()
+            except Exception:  # noqa: BLE001
                 return
-            self._stop.wait(0.2)
+            self._stop.wait(0.01 if self._nvml is not None else 0.2)
 
     def __enter__(self):
         self._thread.start()
@@ -94,11 +124,8 @@ class ClockSampler:
         self._thread.join(timeout=6)
 
     def summary(self) -> dict:
-        clocks = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({name for s in self.samples for name, flag in zip(names, s[2:6]) if flag.lower().startswith("active")})
-        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": int(self.samples[0][1]) if self.samples and self.samples[0][1].isdigit() else None,
-                "reasons": reasons, "samples": len(self.samples)}
+        clocks = sorted(self.clocks)
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": self.max_clock, "reasons": sorted(self.reasons), "samples": len(clocks)}
 
 
 def model_folder(layers: int) -> Path:
@@ -174,6 +201,8 @@ def run_engine(args) -> dict:
     engine = Engine(folder, config)
     runner = engine.runner
 
+    library_per_step: dict[int, int] = {}
+
     def device_decode(batch: int) -> tuple[float, float, int, dict]:
         """Tokens per second of K decode steps kept on the device; also ms per step, kernels per step, clocks."""
         ids = [f"d{batch}-{i}" for i in range(batch)]
@@ -187,6 +216,7 @@ def run_engine(args) -> dict:
             ms = event_ms(lambda: [session.step() for _ in range(steps)])
         for rid in ids:
             runner.finish(rid)
+        library_per_step[batch] = session.library_calls_per_step
         return batch * steps / (ms / 1e3), ms / steps, session.kernels_per_step, clocks.summary()
 
     sections = set(args.sections.split(","))
@@ -247,7 +277,7 @@ def run_engine(args) -> dict:
                    "l2": "inputs larger than L2: each step streams ~2 GB of weights", "peaks": peak_kind},
         "e2e": e2e,
         "gpu_launches": kernels_per_step * steps,
-        "library_gemms_per_step": (fast.library_gemm_calls and 7 * layers + 1) if fast.library_gemm_calls else 0,
+        "library_gemms_per_step": library_per_step.get(args.batch, 0),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s", "frac": achieved / peak["hbm_gbs"], "bytes_per_step": step_bytes},
         "points": points,

@@ -63,7 +63,8 @@ class DecodeSession:
         self._loaded = False
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
-        self.kernels_per_step = 0
+        self.kernels_per_step = 0          # kernels of this engine in one step (counted while warming up)
+        self.library_calls_per_step = 0    # vendor-library matrix products in one step
 
     # --- loading -----------------------------------------------------------------------------
     def load(self, request_ids: list, tokens: list[int], params: list | None = None, draw_indices: list[int] | None = None) -> None:
@@ -148,7 +149,9 @@ class DecodeSession:
         if not self.use_graph:
             self._body()
         elif self.graph is None:
-            before = ops.launch_count
+            from ..ops import fast
+
+            before, library_before = ops.launch_count, fast.library_gemm_calls
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
@@ -158,6 +161,7 @@ class DecodeSession:
                 self.counters -= 1
             torch.cuda.current_stream().wait_stream(stream)
             self.kernels_per_step = ops.launch_count - before
+            self.library_calls_per_step = fast.library_gemm_calls - library_before
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
                 self._body()
