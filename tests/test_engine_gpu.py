@@ -111,3 +111,7 @@ def test_command_line_generates_on_the_gpu(model_folders, capsys):
     assert main(["benchmark", str(model_folders["a"]), "20", "6", "1", "2", "--batch", "2"]) == 0
     report = json.loads(capsys.readouterr().out)
     assert report["deterministic"] and report["median_decode_tokens_per_second"] > 0
+    assert main(["kernel-bench", str(model_folders["b"]), "4", "100", "3"]) == 0
+    kernels = json.loads(capsys.readouterr().out)["kernels"]
+    assert {"add_rmsnorm", "rope_store", "linear_qkv", "attention_decode_split_kv", "argmax"} <= set(kernels)
+    assert all(k["median_us"] > 0 for k in kernels.values())

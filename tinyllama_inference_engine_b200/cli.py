@@ -5,6 +5,7 @@
     tinyllama_b200 benchmark MODEL_DIR CONTEXT OUTPUT_TOKENS WARMUP SAMPLES
     tinyllama_b200 reference MODEL_DIR PROMPT MAX_TOKENS [EXPECTED_FIRST_TOKEN]
     tinyllama_b200 random-model OUT_DIR CONFIG_JSON SEED
+    tinyllama_b200 kernel-bench MODEL_DIR ROWS CONTEXT SAMPLES
 
 The first three are the subcommands of ``tinyllama_cuda`` (app/cuda_reference.cu:476-521)
 with the same positional arguments and JSON on standard output; ``reference`` prints
@@ -14,7 +15,8 @@ exit status 1 (app/reference_cli.cpp:20-25).  PROMPT is text when MODEL_DIR hold
 ``tokenizer.model`` (SentencePiece, BOS prepended as src/tokenizer.cpp:103-105 does),
 otherwise a list of token ids separated by commas or spaces.  Options, before or
 after the positionals: ``--dtype bfloat16|float32``, ``--temperature``, ``--top-p``,
-``--seed``, ``--batch``.
+``--seed``, ``--batch``.  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
+(median and 95th percentile), like the reference's benchmarks/kernel_benchmarks.cu:127-325.
 """
 from __future__ import annotations
 
@@ -177,6 +179,71 @@ def _benchmark(args) -> int:
     return 0
 
 
+def _kernel_bench(args) -> int:
+    """Median / p95 of each kernel family at this model's shapes: ROWS tokens in the step, CONTEXT cached tokens each."""
+    import numpy as np
+    import torch
+
+    from . import ops
+    from .config import load_model_config
+    from .ops import fast
+
+    rows, context, samples = _positive(args.rest[0], "ROWS"), _positive(args.rest[1], "CONTEXT"), _positive(args.rest[2], "SAMPLES")
+    _, c = load_model_config(args.model_dir)
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    dev = torch.device("cuda:0")
+    H, I, V, D, QH, KVH, P = c.hidden_size, c.intermediate_size, c.vocab_size, c.head_dim, c.num_attention_heads, c.num_key_value_heads, 64
+    rand = lambda *shape: (torch.randn(*shape, device=dev) * 0.05).to(dtype)  # noqa: E731
+    residual, delta, normed = torch.randn(rows, H, device=dev), rand(rows, H), torch.empty(rows, H, device=dev, dtype=dtype)
+    norm_w = torch.ones(H, device=dev)
+    w_qkv, w_o, w_gu, w_dn, w_head = rand((QH + 2 * KVH) * D, H), rand(H, QH * D), rand(2 * I, H), rand(H, I), rand(V, H)
+    qkv, mixed = rand(rows, (QH + 2 * KVH) * D), torch.empty(rows, QH * D, device=dev, dtype=dtype)
+    gate_up, act, out_h = rand(rows, 2 * I), torch.empty(rows, I, device=dev, dtype=dtype), torch.empty(rows, H, device=dev, dtype=dtype)
+    logits = torch.empty(min(rows, 64), V, device=dev)
+    # a decode-shaped batch: ROWS requests with CONTEXT cached tokens each
+    pages_per = -(-(context + 1) // P)
+    pool = rand(rows * pages_per, 2, KVH, P, D)
+    table = torch.arange(rows * pages_per, dtype=torch.int32, device=dev).view(rows, pages_per).contiguous()
+    positions = torch.full((rows,), context, dtype=torch.int32, device=dev)
+    token_seq = torch.arange(rows, dtype=torch.int32, device=dev)
+    inv_freq = torch.from_numpy(np.power(np.float32(c.rope_theta), (np.float32(-2.0) * np.arange(D // 2, dtype=np.float32)) / np.float32(D))).to(dev)
+    ids = torch.randint(0, V, (rows,), device=dev, dtype=torch.int32)
+    table_e = rand(V, H)
+    sampled = torch.empty(min(rows, 64), dtype=torch.int32, device=dev)
+    cases = {
+        "embedding": lambda: ops.embedding(table_e, ids, residual),
+        "add_rmsnorm": lambda: ops.add_rmsnorm(residual, delta, norm_w, c.rms_norm_eps, normed),
+        "linear_qkv": lambda: ops.linear(normed, w_qkv, qkv),
+        "rope_store": lambda: ops.rope_store(qkv, positions, token_seq, table, inv_freq, D, pool, QH, KVH, D, P, True),
+        "attention_generic": lambda: ops.core().tlie_paged_attention_generic and ops.paged_attention(qkv, pool, positions, token_seq, table, mixed, QH, KVH, D, P, 0, None, None),
+        "linear_o": lambda: ops.linear(mixed, w_o, out_h),
+        "linear_gate_up": lambda: ops.linear(normed, w_gu, gate_up),
+        "silu_mul": lambda: ops.silu_mul(gate_up, act),
+        "linear_down": lambda: ops.linear(act, w_dn, out_h),
+        "linear_head": lambda: ops.linear(normed[: logits.shape[0]], w_head, logits),
+        "argmax": lambda: ops.argmax(logits, sampled),
+    }
+    if dtype == torch.bfloat16 and D <= 128:
+        splits = fast.decode_splits(rows, KVH, context + 1)
+        cases["attention_decode_split_kv"] = lambda: fast.decode_attention(qkv, pool, positions, table, mixed, QH, KVH, D, P, 0, D ** -0.5, splits)
+    report = {}
+    for name, call in cases.items():
+        for _ in range(3):
+            call()
+        times = []
+        for _ in range(samples):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            call()
+            end.record()
+            end.synchronize()
+            times.append(start.elapsed_time(end) * 1e3)
+        times.sort()
+        report[name] = {"median_us": times[len(times) // 2], "p95_us": times[min(len(times) - 1, int(len(times) * 0.95))]}
+    print(json.dumps({"rows": rows, "context": context, "samples": samples, "dtype": args.dtype, "device": torch.cuda.get_device_name(0), "kernels": report}))
+    return 0
+
+
 def _random_model(args) -> int:
     from .config import architecture_for
     from .weights import write_random_model
@@ -189,7 +256,7 @@ def _random_model(args) -> int:
 
 
 _COMMANDS = {"generate": (_generate, (2, 3)), "reference": (_generate, (2, 3)), "logits": (_logits, (1, 1)),
-             "benchmark": (_benchmark, (4, 4)), "random-model": (_random_model, (2, 2))}
+             "benchmark": (_benchmark, (4, 4)), "random-model": (_random_model, (2, 2)), "kernel-bench": (_kernel_bench, (3, 3))}
 
 
 def main(argv: list[str] | None = None) -> int:
