@@ -14,17 +14,28 @@
 
 namespace tlie {
 
+// One block per token.  The block first computes the token's rotary_dim / 2 cosines and sines once into shared
+// memory (every head uses the same ones), then walks the heads two elements at a time.
+constexpr int kMaxRotaryHalf = 128;
+
 template <typename T>
 __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                   const int* __restrict__ token_seq, const int* __restrict__ block_table,
                                   int table_stride, const float* __restrict__ inv_freq, int rotary_dim,
                                   T* __restrict__ pages, int q_heads, int kv_heads, int head_dim, int page_size,
                                   int write_cache) {
+  __shared__ float cos_s[kMaxRotaryHalf], sin_s[kMaxRotaryHalf];
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int row_width = (q_heads + 2 * kv_heads) * head_dim;
   T* row = qkv + (size_t)t * row_width;
   const int half = rotary_dim / 2;
+  for (int d = threadIdx.x; d < half; d += blockDim.x) {
+    const float angle = (float)pos * inv_freq[d];
+    cos_s[d] = cosf(angle);
+    sin_s[d] = sinf(angle);
+  }
+  __syncthreads();
 
   T* k_dst = nullptr;
   T* v_dst = nullptr;
@@ -41,9 +52,10 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
   // q heads and k heads: rotate the first rotary_dim elements, pass the rest through.
   const int rot_heads = q_heads + (write_cache ? kv_heads : 0);
   const int per_head = head_dim - half;  // one work item per pair, one per unrotated element
-  for (int item = threadIdx.x; item < rot_heads * per_head; item += blockDim.x) {
-    const int head = item / per_head;
-    const int d = item - head * per_head;
+  int head = threadIdx.x / per_head;
+  int d = threadIdx.x - head * per_head;
+  const int head_step = blockDim.x / per_head, d_step = blockDim.x - head_step * per_head;
+  for (; head < rot_heads;) {
     T* x = row + (size_t)head * head_dim;
     const bool is_k = head >= q_heads;
     T* dst = is_k ? (k_dst + (size_t)(head - q_heads) * head_stride_in_page) : x;
@@ -51,9 +63,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
       float first = to_float(x[d]);
       float second = to_float(x[d + half]);
       if (inv_freq != nullptr) {
-        const float angle = (float)pos * inv_freq[d];
-        const float c = cosf(angle);
-        const float s = sinf(angle);
+        const float c = cos_s[d], s = sin_s[d];
         const float a = first * c - second * s;
         const float b = second * c + first * s;
         first = a;
@@ -65,13 +75,26 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
       const int e = d + half;  // elements rotary_dim .. head_dim-1
       if (is_k) dst[e] = x[e];
     }
+    // next work item, blockDim.x further on, without a division
+    head += head_step;
+    d += d_step;
+    if (d >= per_head) {
+      d -= per_head;
+      head += 1;
+    }
   }
   if (write_cache) {
     const T* v = row + (size_t)(q_heads + kv_heads) * head_dim;
-    for (int item = threadIdx.x; item < kv_heads * head_dim; item += blockDim.x) {
-      const int head = item / head_dim;
-      const int d = item - head * head_dim;
-      v_dst[(size_t)head * head_stride_in_page + d] = v[item];
+    int vh = threadIdx.x / head_dim, vd = threadIdx.x - vh * head_dim;
+    const int vh_step = blockDim.x / head_dim, vd_step = blockDim.x - vh_step * head_dim;
+    for (; vh < kv_heads;) {
+      v_dst[(size_t)vh * head_stride_in_page + vd] = v[vh * head_dim + vd];
+      vh += vh_step;
+      vd += vd_step;
+      if (vd >= head_dim) {
+        vd -= head_dim;
+        vh += 1;
+      }
     }
   }
 }
@@ -85,7 +108,7 @@ TLIE_EXPORT int tlie_rope_store(int dtype, void* qkv, const int* positions, cons
                                 void* pages, int tokens, int q_heads, int kv_heads, int head_dim, int page_size,
                                 int write_cache, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || rotary_dim / 2 > kMaxRotaryHalf) return (int)cudaErrorInvalidValue;
   const int block = 256;
   if (dtype == TLIE_F32)
     rope_store_kernel<float><<<tokens, block, 0, stream>>>((float*)qkv, positions, token_seq, block_table,
