@@ -407,3 +407,43 @@ def test_gemm_tcgen05_gated(ops, M, inter, K):
     torch.cuda.synchronize()
     assert int(fast.tcgen05_error_flag(got.device)) == 0
     assert float((got.cpu().float() - want).abs().max()) <= 1.6e-2 * float(want.abs().max()) + 2e-3 * float(both.abs().max())
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,page_size,window", [(32, 4, 64, 0), (8, 2, 64, 100), (4, 4, 128, 0), (16, 1, 64, 37), (3, 3, 64, 0)])
+def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, window):
+    """The tcgen05 prompt kernel (head size 64) against the plain function: portions that start anywhere, page edges, single rows."""
+    from tinyllama_inference_engine_b200.engine.batch import ATTENTION_TC_TILE_ROWS
+    from tinyllama_inference_engine_b200.ops import fast
+
+    head_dim = 64
+    rng = np.random.default_rng(15)
+    torch.manual_seed(15)
+    seq_lens = [300, 64, 65, 1, 127, 131, 700, 2, 129, 1000]
+    q_lens = [300, 64, 2, 1, 1, 131, 70, 2, 65, 512]
+    qkv, pages, positions, token_seq, table = _paged_case(rng, torch.bfloat16, seq_lens, q_lens, kv_heads, head_dim, page_size, q_heads)
+    row = sum(q_lens[:6]) + 69
+    page, slot = int(table[6, 5 // page_size]), 5 % page_size
+    for h in range(q_heads):
+        qv = qkv.view(qkv.shape[0], -1, head_dim)[row, h].float()
+        pages[page, 0, h // (q_heads // kv_heads), slot] = (qv * (6.0 * head_dim ** 0.5 / float(qv.norm()) ** 2)).bfloat16()
+    tokens = qkv.shape[0]
+    want = torch.empty(tokens, q_heads * head_dim, dtype=torch.bfloat16)
+    plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)
+    starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    firsts = np.array([s - q for s, q in zip(seq_lens, q_lens)], dtype=np.int32)
+    tiles = [[i, int(starts[i]) + off] for i, q in enumerate(q_lens) for off in range(0, q, ATTENTION_TC_TILE_ROWS)]
+    pages_gpu = pages.cuda()
+    held = set(int(p) for p in table.flatten() if p >= 0)
+    for page in range(pages.shape[0]):
+        if page not in held:
+            pages_gpu[page] = float("nan")
+    for i, n in enumerate(seq_lens):
+        if n % page_size:
+            pages_gpu[int(table[i, n // page_size]), :, :, n % page_size :] = float("nan")
+    got = torch.full((tokens, q_heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    fast.prefill_attention_tc(qkv.cuda(), pages_gpu, torch.tensor(tiles, dtype=torch.int32).cuda(), torch.from_numpy(starts).cuda(), torch.from_numpy(firsts).cuda(),
+                              table.cuda(), got, q_heads, kv_heads, page_size, window, head_dim ** -0.5)
+    torch.cuda.synchronize()
+    assert int(fast.tcgen05_error_flag(got.device)) == 0, "a bounded wait inside the kernel gave up"
+    error = (got.cpu().float() - want.float()).abs().max(1).values
+    assert float(error.max()) <= 1.6e-2 * 2, (int(error.argmax()), float(error.max()))

@@ -7,6 +7,7 @@ import torch
 
 
 ATTENTION_TILE_ROWS = 64   # rows of one work item of the prompt-attention kernel (csrc/attention_prefill.cu: PREFILL_ROWS)
+ATTENTION_TC_TILE_ROWS = 128   # rows of one work item of the tensor-memory kernel (csrc/attention_prefill_tc.cu)
 
 
 @dataclass
@@ -54,6 +55,7 @@ class StepContext:
     max_q_len: int
     max_seq_len: int
     attn_tiles: torch.Tensor | None = None
+    attn_tiles_tc: torch.Tensor | None = None   # the same work list in runs of ATTENTION_TC_TILE_ROWS rows
 
     @property
     def decode_only(self) -> bool:
@@ -82,7 +84,11 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
     for index, count in enumerate(q_lens):
         for offset in range(0, count, ATTENTION_TILE_ROWS):
             tiles += [index, seq_starts[index] + offset]
-    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows, tiles]
+    tiles_tc: list[int] = []
+    for index, count in enumerate(q_lens):
+        for offset in range(0, count, ATTENTION_TC_TILE_ROWS):
+            tiles_tc += [index, seq_starts[index] + offset]
+    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows, tiles, tiles_tc]
     flat: list[int] = []
     offsets = []
     for section in sections:
@@ -107,4 +113,5 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=q_lens,
         host_first_positions=list(first_positions), host_state_slots=list(slots),
         max_q_len=max(q_lens), max_seq_len=max(seq_lens), attn_tiles=views[8].view(-1, 2),
+        attn_tiles_tc=views[9].view(-1, 2),
     )

@@ -25,6 +25,7 @@ def build_all() -> list:
     built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
     built.append(build_library("tlie_gemv_fused", ["gemv_fused.cu"]))
     built.append(build_library("tlie_gemm_tcgen05", ["gemm_tcgen05.cu"]))
+    built.append(build_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"]))
     return built
 
 
@@ -253,6 +254,26 @@ def prefill_attention(qkv, pages, tiles, seq_starts, first_positions, block_tabl
     )
 
 
+use_tc_attention = True    # the tcgen05 / tensor-memory prompt attention (head size 64, pages of a multiple of 64 keys)
+TC_ATTENTION_MIN_ROWS_PER_TILE = 32
+
+
+def prefill_attention_tc(qkv, pages, tiles, seq_starts, first_positions, block_table, out, q_heads: int, kv_heads: int, page_size: int,
+                         window: int, scale: float) -> None:
+    """Flash attention of every 128-row tile in ``tiles`` on the 5th-generation tensor cores; head size 64, bfloat16."""
+    ops = _ops()
+    lib = load_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"])
+    ops._check(
+        lib.tlie_prefill_attention_tc(
+            ops._ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), ops._ptr(pages), c_int(pages.shape[0]), ops._i32(tiles, "tiles"), c_int(tiles.shape[0]),
+            ops._i32(seq_starts, "seq_starts"), ops._i32(first_positions, "first_positions"), ops._i32(block_table, "block_table"),
+            c_int(block_table.shape[1]), ops._ptr(out), c_int(q_heads), c_int(kv_heads), c_int(page_size), c_int(window), c_float(scale),
+            ops._ptr(tcgen05_error_flag(qkv.device)), ops._stream(),
+        ),
+        "prefill_attention_tc",
+    )
+
+
 def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, batch) -> bool:
     """Run a specialised kernel if one covers this shape; False sends the caller to the general one."""
     if batch is None or pages.dtype != torch.bfloat16:
@@ -260,6 +281,11 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
     if batch.decode_only and qkv.shape[0] == batch.num_seqs and head_dim <= 128 and q_heads // kv_heads <= 16:
         splits = decode_splits(batch.num_seqs, kv_heads, batch.max_seq_len)
         decode_attention(qkv, pages, positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, splits)
+        return True
+    tc_tiles = getattr(batch, "attn_tiles_tc", None)
+    if (use_tc_attention and tc_tiles is not None and head_dim == 64 and page_size % 64 == 0 and pages.is_contiguous()
+            and batch.num_tokens >= TC_ATTENTION_MIN_ROWS_PER_TILE * tc_tiles.shape[0]):
+        prefill_attention_tc(qkv, pages, tc_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads, page_size, window, scale)
         return True
     if batch.attn_tiles is not None and head_dim <= 128:
         prefill_attention(qkv, pages, batch.attn_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads,
