@@ -92,16 +92,21 @@ __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
+// 64 consecutive 32-bit columns of this thread's lane: four loads in flight, one wait.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[c * 16 + 0]), "=r"(r[c * 16 + 1]), "=r"(r[c * 16 + 2]), "=r"(r[c * 16 + 3]), "=r"(r[c * 16 + 4]), "=r"(r[c * 16 + 5]),
+          "=r"(r[c * 16 + 6]), "=r"(r[c * 16 + 7]), "=r"(r[c * 16 + 8]), "=r"(r[c * 16 + 9]), "=r"(r[c * 16 + 10]), "=r"(r[c * 16 + 11]),
+          "=r"(r[c * 16 + 12]), "=r"(r[c * 16 + 13]), "=r"(r[c * 16 + 14]), "=r"(r[c * 16 + 15])
+        : "r"(taddr + c * 16));
+  }
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 struct SmemTC {
@@ -230,7 +235,21 @@ __global__ void __launch_bounds__(kThreadsTC)
 #pragma unroll
     for (int i = 0; i < kD; ++i) o[i] = 0.0f;
     float row_max = -INFINITY, row_sum = 0.0f;
+    float pending_alpha = 1.0f;   // the factor that belongs to the product P . V still in flight
     bool ok = true;
+    // O = O * alpha + (P . V of tile j): read one tile late, so that the product runs under the next tile's softmax
+    auto absorb_pv = [&](int j) {
+      if (!bar_wait(&sm.pv_full, j & 1, abort_flag)) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      float pv[kD];
+      tmem_ld64(tmem + lane_base + 2 * kKeysTC, pv);
+#pragma unroll
+      for (int i = 0; i < kD; ++i) o[i] = fmaf(o[i], pending_alpha, pv[i]);
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive(&sm.pv_empty);
+      return true;
+    };
     for (int j = 0; j < num_kt && ok; ++j) {
       const int b = j & 1, s = j % kKvStages;
       const int key0 = (first_kt + j) * kKeysTC;
@@ -238,13 +257,7 @@ __global__ void __launch_bounds__(kThreadsTC)
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       float sc[kKeysTC];
-#pragma unroll
-      for (int c = 0; c < kKeysTC / 16; ++c) {
-        float v[16];
-        tmem_ld16(tmem + lane_base + b * kKeysTC + c * 16, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) sc[c * 16 + i] = v[i];
-      }
+      tmem_ld64(tmem + lane_base + b * kKeysTC, sc);
       // S_b has been read: the issuer may overwrite it with tile j + 2
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
@@ -267,23 +280,28 @@ __global__ void __launch_bounds__(kThreadsTC)
       const float base = finite_max * sl2;
       const float alpha = exp2f((row_max - finite_max) * sl2);
       row_max = new_max;
-      // P as bfloat16 into the swizzled K-major tile: row r at (r / 8) * 1024 + (r % 8) * 128, 16-byte chunk c at c ^ (r % 8)
-      uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p[b]) + (row >> 3) * 1024 + (row & 7) * 128;
+      uint32_t packed[kKeysTC / 2];
       float sum = 0.0f;
 #pragma unroll
-      for (int c = 0; c < kKeysTC / 8; ++c) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float p0 = exp2f(fmaf(sc[c * 8 + 2 * i], sl2, -base));
-          const float p1 = exp2f(fmaf(sc[c * 8 + 2 * i + 1], sl2, -base));
-          sum += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          packed[i] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int i = 0; i < kKeysTC / 2; ++i) {
+        const float p0 = exp2f(fmaf(sc[2 * i], sl2, -base));
+        const float p1 = exp2f(fmaf(sc[2 * i + 1], sl2, -base));
+        sum += p0 + p1;
+        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        packed[i] = *reinterpret_cast<uint32_t*>(&h);
       }
       row_sum = row_sum * alpha + sum;
+      // the previous tile's product has had this tile's softmax to finish: take it in before its buffer is reused
+      if (j > 0) {
+        ok = absorb_pv(j - 1);
+        if (!ok) break;
+      }
+      pending_alpha = alpha;
+      // P as bfloat16 into the swizzled K-major tile: row r at (r / 8) * 1024 + (r % 8) * 128, 16-byte chunk c at c ^ (r % 8)
+      uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p[b]) + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+      for (int c = 0; c < kKeysTC / 8; ++c)
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       // The last tile of a request may hold keys past its end whose values were never written: zero those V rows,
       // so that 0 * (whatever is there) stays 0.  A V row is 128 contiguous bytes whatever the swizzle.
       if (key0 + kKeysTC > n_keys) {
@@ -296,21 +314,8 @@ __global__ void __launch_bounds__(kThreadsTC)
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) bar_arrive(&sm.p_full[b]);
-      // O = O * alpha + P . V
-      ok = bar_wait(&sm.pv_full, j & 1, abort_flag);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < kD / 16; ++c) {
-        float v[16];
-        tmem_ld16(tmem + lane_base + 2 * kKeysTC + c * 16, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[c * 16 + i] = fmaf(o[c * 16 + i], alpha, v[i]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      __syncwarp();
-      if (lane == 0) bar_arrive(&sm.pv_empty);
     }
+    if (ok && num_kt > 0) ok = absorb_pv(num_kt - 1);
     if (ok && row < rows_here) {
       const float inv = 1.0f / row_sum;
       __nv_bfloat16* dst = out + ((size_t)(row0 + row) * q_heads + head) * kD;
