@@ -412,7 +412,7 @@ def test_gemm_tcgen05_gated(ops, M, inter, K):
 @pytest.mark.parametrize("q_heads,kv_heads,page_size,window", [(32, 4, 64, 0), (8, 2, 64, 100), (4, 4, 128, 0), (16, 1, 64, 37), (3, 3, 64, 0)])
 def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, window):
     """The tcgen05 prompt kernel (head size 64) against the plain function: portions that start anywhere, page edges, single rows."""
-    from tinyllama_inference_engine_b200.engine.batch import ATTENTION_TC_TILE_ROWS
+    from tinyllama_inference_engine_b200.engine.batch import paired_attention_tiles
     from tinyllama_inference_engine_b200.ops import fast
 
     head_dim = 64
@@ -431,7 +431,8 @@ def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, wind
     plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)
     starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     firsts = np.array([s - q for s, q in zip(seq_lens, q_lens)], dtype=np.int32)
-    tiles = [[i, int(starts[i]) + off] for i, q in enumerate(q_lens) for off in range(0, q, ATTENTION_TC_TILE_ROWS)]
+    tiles = paired_attention_tiles(q_lens, [int(f) for f in firsts], [int(x) for x in starts])
+    assert len(tiles) // 4 == (sum(-(-q // 128) for q in q_lens) + 1) // 2
     pages_gpu = pages.cuda()
     held = set(int(p) for p in table.flatten() if p >= 0)
     for page in range(pages.shape[0]):
@@ -441,7 +442,7 @@ def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, wind
         if n % page_size:
             pages_gpu[int(table[i, n // page_size]), :, :, n % page_size :] = float("nan")
     got = torch.full((tokens, q_heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
-    fast.prefill_attention_tc(qkv.cuda(), pages_gpu, torch.tensor(tiles, dtype=torch.int32).cuda(), torch.from_numpy(starts).cuda(), torch.from_numpy(firsts).cuda(),
+    fast.prefill_attention_tc(qkv.cuda(), pages_gpu, torch.tensor(tiles, dtype=torch.int32).view(-1, 4).cuda(), torch.from_numpy(starts).cuda(), torch.from_numpy(firsts).cuda(),
                               table.cuda(), got, q_heads, kv_heads, page_size, window, head_dim ** -0.5)
     torch.cuda.synchronize()
     assert int(fast.tcgen05_error_flag(got.device)) == 0, "a bounded wait inside the kernel gave up"

@@ -115,12 +115,12 @@ struct SmemTC {
   __nv_bfloat16 k[kKvStages][kKeysTC * kD];          // 8 KB each
   __nv_bfloat16 v[kKvStages][kKeysTC * kD];          // 8 KB each
   __nv_bfloat16 p[2][kRowsTC * kKeysTC];             // 16 KB each
-  uint64_t q_full, kv_full[kKvStages], kv_empty[kKvStages], s_full[2], s_empty[2], p_full[2], pv_full, pv_empty;
+  uint64_t q_full, q_empty, kv_full[kKvStages], kv_empty[kKvStages], s_full[2], s_empty[2], p_full[2], pv_full, pv_empty;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-// tiles: [n_tiles][2] = (request index in the step, first row of the tile in the step's row numbering), 128 rows each
+// tiles: [n_items][4] = (request, first row, request, first row): one or two 128-row tiles per CTA (second request -1: none)
 __global__ void __launch_bounds__(kThreadsTC)
     prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                 const int* __restrict__ tiles, const int* __restrict__ seq_starts, const int* __restrict__ first_positions,
@@ -131,24 +131,40 @@ __global__ void __launch_bounds__(kThreadsTC)
   volatile int* abort_flag = &sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // heavier tiles (later rows see more keys) first
-  const int tile_index = gridDim.x - 1 - blockIdx.x;
-  const int seq = tiles[tile_index * 2];
-  const int row0 = tiles[tile_index * 2 + 1];
+  // A work item is a pair of row tiles (the second may be absent): the host pairs a tile that sees many keys with one
+  // that sees few, so that all CTAs carry about the same work and the grid ends together.
+  const int* item = tiles + (size_t)blockIdx.x * 4;
   const int head = blockIdx.y;
   const int kvh = head / (q_heads / kv_heads);
-  const int rows_here = min(kRowsTC, seq_starts[seq + 1] - row0);
-  const int pos0 = first_positions[seq] + (row0 - seq_starts[seq]);
-  const int n_keys = pos0 + rows_here;                 // keys the last row of the tile sees
-  const int lo_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-  const int first_kt = lo_tile / kKeysTC;
-  const int end_kt = (n_keys + kKeysTC - 1) / kKeysTC;
-  const int num_kt = end_kt - first_kt;
-  const int* table = block_table + (size_t)seq * table_stride;
   constexpr int kTmemCols = 256;   // S0 [0,64), S1 [64,128), PV [128,192)
+
+  struct RowTile {
+    int row0, rows_here, pos0, n_keys, first_kt, num_kt;
+    const int* table;
+  };
+  auto row_tile = [&](int u) {
+    RowTile t;
+    const int seq = item[2 * u];
+    t.row0 = item[2 * u + 1];
+    if (seq < 0) {
+      t.num_kt = 0;
+      t.rows_here = t.pos0 = t.n_keys = t.first_kt = 0;
+      t.table = block_table;
+      return t;
+    }
+    t.rows_here = min(kRowsTC, seq_starts[seq + 1] - t.row0);
+    t.pos0 = first_positions[seq] + (t.row0 - seq_starts[seq]);
+    t.n_keys = t.pos0 + t.rows_here;                 // keys the last row of the tile sees
+    const int lo_tile = (window > 0 && t.pos0 - window + 1 > 0) ? t.pos0 - window + 1 : 0;
+    t.first_kt = lo_tile / kKeysTC;
+    t.num_kt = (t.n_keys + kKeysTC - 1) / kKeysTC - t.first_kt;
+    t.table = block_table + (size_t)seq * table_stride;
+    return t;
+  };
 
   if (threadIdx.x == 0) {
     bar_init(&sm.q_full, 1);
+    bar_init(&sm.q_empty, 1);
     for (int s = 0; s < kKvStages; ++s) {
       bar_init(&sm.kv_full[s], 1);
       bar_init(&sm.kv_empty[s], 1);
@@ -173,34 +189,42 @@ __global__ void __launch_bounds__(kThreadsTC)
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem = sm.tmem_base;
 
+  // g counts key tiles over both row tiles: every ring (kv stages, the two S / P buffers, the P.V buffer) is indexed by it.
   if (warp == 0) {
-    if (lane == 0) {   // TMA producer: Q once, then one K box and one V box per tile
-      bar_expect_tx(&sm.q_full, kRowsTC * kD * 2);
-      tma_box_2d(sm.q, &map_q, head * kD, row0, &sm.q_full);
-      const int rows_per_page = page_size;   // rows of the [rows, 64] view of the pool per (page, plane, head)
-      for (int j = 0; j < num_kt; ++j) {
-        const int s = j % kKvStages;
-        if (!bar_wait(&sm.kv_empty[s], ((j / kKvStages) & 1) ^ 1, abort_flag)) break;
-        const int key0 = (first_kt + j) * kKeysTC;
-        const int page = table[key0 / page_size];
-        const int in_page = key0 % page_size;
-        const int k_row = ((page * 2 + 0) * kv_heads + kvh) * rows_per_page + in_page;
-        const int v_row = ((page * 2 + 1) * kv_heads + kvh) * rows_per_page + in_page;
-        bar_expect_tx(&sm.kv_full[s], 2 * kKeysTC * kD * 2);
-        tma_box_2d(sm.k[s], &map_kv, 0, k_row, &sm.kv_full[s]);
-        tma_box_2d(sm.v[s], &map_kv, 0, v_row, &sm.kv_full[s]);
+    if (lane == 0) {   // TMA producer: per row tile Q once, then one K box and one V box per key tile
+      int g = 0;
+      bool ok = true;
+      for (int u = 0; u < 2 && ok; ++u) {
+        const RowTile t = row_tile(u);
+        if (t.num_kt == 0) continue;
+        if (u > 0) ok = bar_wait(&sm.q_empty, 0, abort_flag);   // the first row tile's score products have read Q
+        if (!ok) break;
+        bar_expect_tx(&sm.q_full, kRowsTC * kD * 2);
+        tma_box_2d(sm.q, &map_q, head * kD, t.row0, &sm.q_full);
+        for (int j = 0; j < t.num_kt; ++j, ++g) {
+          const int s = g % kKvStages;
+          ok = bar_wait(&sm.kv_empty[s], ((g / kKvStages) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const int key0 = (t.first_kt + j) * kKeysTC;
+          const int page = t.table[key0 / page_size];
+          const int in_page = key0 % page_size;
+          const int k_row = ((page * 2 + 0) * kv_heads + kvh) * page_size + in_page;   // row of the [rows, 64] view of the pool
+          const int v_row = ((page * 2 + 1) * kv_heads + kvh) * page_size + in_page;
+          bar_expect_tx(&sm.kv_full[s], 2 * kKeysTC * kD * 2);
+          tma_box_2d(sm.k[s], &map_kv, 0, k_row, &sm.kv_full[s]);
+          tma_box_2d(sm.v[s], &map_kv, 0, v_row, &sm.kv_full[s]);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {   // MMA issuer
       constexpr uint32_t idesc_s = instr_desc(kRowsTC, kKeysTC, 0);    // S = Q . K^T   (B = K tile, K-major)
       constexpr uint32_t idesc_pv = instr_desc(kRowsTC, kD, 1);        // PV = P . V    (B = V tile, MN-major)
-      bool ok = bar_wait(&sm.q_full, 0, abort_flag);
       const uint32_t q_addr = smem_addr(sm.q);
-      auto issue_s = [&](int j) {   // scores of tile j into S buffer j & 1
-        const int s = j % kKvStages, b = j & 1;
-        if (!bar_wait(&sm.kv_full[s], (j / kKvStages) & 1, abort_flag)) return false;
-        if (!bar_wait(&sm.s_empty[b], ((j >> 1) & 1) ^ 1, abort_flag)) return false;
+      auto issue_s = [&](int g) {   // scores of key tile g into S buffer g & 1
+        const int s = g % kKvStages, b = g & 1;
+        if (!bar_wait(&sm.kv_full[s], (g / kKvStages) & 1, abort_flag)) return false;
+        if (!bar_wait(&sm.s_empty[b], ((g >> 1) & 1) ^ 1, abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t k_addr = smem_addr(sm.k[s]);
 #pragma unroll
@@ -208,126 +232,143 @@ __global__ void __launch_bounds__(kThreadsTC)
         mma_commit(&sm.s_full[b]);
         return true;
       };
-      if (ok && num_kt > 0) ok = issue_s(0);
-      for (int j = 0; j < num_kt && ok; ++j) {
-        if (j + 1 < num_kt) ok = issue_s(j + 1);   // the next tile's scores run under this tile's softmax
-        if (!ok) break;
-        const int s = j % kKvStages, b = j & 1;
-        ok = bar_wait(&sm.p_full[b], (j >> 1) & 1, abort_flag) && bar_wait(&sm.pv_empty, (j & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t p_addr = smem_addr(sm.p[b]), v_addr = smem_addr(sm.v[s]);
+      int g = 0, q_phase = 0;
+      bool ok = true;
+      for (int u = 0; u < 2 && ok; ++u) {
+        const RowTile t = row_tile(u);
+        if (t.num_kt == 0) continue;
+        ok = bar_wait(&sm.q_full, q_phase, abort_flag);
+        q_phase ^= 1;
+        if (ok) ok = issue_s(g);
+        for (int j = 0; j < t.num_kt && ok; ++j, ++g) {
+          if (j + 1 < t.num_kt) {
+            ok = issue_s(g + 1);   // the next tile's scores run under this tile's softmax
+          } else {
+            mma_commit(&sm.q_empty);   // all score products of this row tile are issued: Q may be replaced when they are done
+          }
+          if (!ok) break;
+          const int s = g % kKvStages, b = g & 1;
+          ok = bar_wait(&sm.p_full[b], (g >> 1) & 1, abort_flag) && bar_wait(&sm.pv_empty, (g & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t p_addr = smem_addr(sm.p[b]), v_addr = smem_addr(sm.v[s]);
 #pragma unroll
-        for (int kk = 0; kk < kKeysTC / 16; ++kk)   // 16 keys further: 32 bytes inside P's rows, 16 rows (2048 bytes) down in V
-          mma_ss(tmem + 2 * kKeysTC, tile_desc(p_addr + kk * 32), tile_desc(v_addr + kk * 16 * kD * 2), idesc_pv, kk > 0 ? 1u : 0u);
-        mma_commit(&sm.pv_full);
-        mma_commit(&sm.kv_empty[s]);   // both products of this stage are done when this fires
+          for (int kk = 0; kk < kKeysTC / 16; ++kk)   // 16 keys further: 32 bytes inside P's rows, 16 rows (2048 bytes) down in V
+            mma_ss(tmem + 2 * kKeysTC, tile_desc(p_addr + kk * 32), tile_desc(v_addr + kk * 16 * kD * 2), idesc_pv, kk > 0 ? 1u : 0u);
+          mma_commit(&sm.pv_full);
+          mma_commit(&sm.kv_empty[s]);   // both products of this stage are done when this fires
+        }
       }
     }
   } else {   // softmax: thread = one query row = one lane of tensor memory
     const int sub = warp & 3;
     const int row = sub * 32 + lane;
     const uint32_t lane_base = (uint32_t)(sub * 32) << 16;
-    const int my_pos = pos0 + min(row, rows_here - 1);   // rows past the end behave like the last row; never stored
-    const int my_lo = (window > 0 && my_pos - window + 1 > 0) ? my_pos - window + 1 : 0;
     const float sl2 = scale * kLog2eTC;
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.0f;
-    float row_max = -INFINITY, row_sum = 0.0f;
-    float pending_alpha = 1.0f;   // the factor that belongs to the product P . V still in flight
+    int g = 0;
     bool ok = true;
-    // O = O * alpha + (P . V of tile j): read one tile late, so that the product runs under the next tile's softmax
-    auto absorb_pv = [&](int j) {
-      if (!bar_wait(&sm.pv_full, j & 1, abort_flag)) return false;
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      float pv[kD];
-      tmem_ld64(tmem + lane_base + 2 * kKeysTC, pv);
+    for (int u = 0; u < 2 && ok; ++u) {
+      const RowTile t = row_tile(u);
+      if (t.num_kt == 0) continue;
+      const int my_pos = t.pos0 + min(row, t.rows_here - 1);   // rows past the end behave like the last row; never stored
+      const int my_lo = (window > 0 && my_pos - window + 1 > 0) ? my_pos - window + 1 : 0;
+      float o[kD];
 #pragma unroll
-      for (int i = 0; i < kD; ++i) o[i] = fmaf(o[i], pending_alpha, pv[i]);
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      __syncwarp();
-      if (lane == 0) bar_arrive(&sm.pv_empty);
-      return true;
-    };
-    for (int j = 0; j < num_kt && ok; ++j) {
-      const int b = j & 1, s = j % kKvStages;
-      const int key0 = (first_kt + j) * kKeysTC;
-      ok = bar_wait(&sm.s_full[b], (j >> 1) & 1, abort_flag);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      float sc[kKeysTC];
-      tmem_ld64(tmem + lane_base + b * kKeysTC, sc);
-      // S_b has been read: the issuer may overwrite it with tile j + 2
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      __syncwarp();
-      if (lane == 0) bar_arrive(&sm.s_empty[b]);
-      const bool need_mask = key0 + kKeysTC - 1 > pos0 || (window > 0 && key0 < pos0 + rows_here - window);
-      float tile_max = -INFINITY;
-      if (need_mask) {
+      for (int i = 0; i < kD; ++i) o[i] = 0.0f;
+      float row_max = -INFINITY, row_sum = 0.0f;
+      float pending_alpha = 1.0f;   // the factor that belongs to the product P . V still in flight
+      // O = O * alpha + (P . V of key tile gg): read one tile late, so that the product runs under the next tile's softmax
+      auto absorb_pv = [&](int gg) {
+        if (!bar_wait(&sm.pv_full, gg & 1, abort_flag)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        float pv[kD];
+        tmem_ld64(tmem + lane_base + 2 * kKeysTC, pv);
 #pragma unroll
-        for (int i = 0; i < kKeysTC; ++i) {
-          const int key = key0 + i;
-          sc[i] = (key >= my_lo && key <= my_pos) ? sc[i] : -INFINITY;
-          tile_max = fmaxf(tile_max, sc[i]);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < kKeysTC; ++i) tile_max = fmaxf(tile_max, sc[i]);
-      }
-      const float new_max = fmaxf(row_max, tile_max);
-      const float finite_max = (new_max == -INFINITY) ? 0.0f : new_max;
-      const float base = finite_max * sl2;
-      const float alpha = exp2f((row_max - finite_max) * sl2);
-      row_max = new_max;
-      uint32_t packed[kKeysTC / 2];
-      float sum = 0.0f;
-#pragma unroll
-      for (int i = 0; i < kKeysTC / 2; ++i) {
-        const float p0 = exp2f(fmaf(sc[2 * i], sl2, -base));
-        const float p1 = exp2f(fmaf(sc[2 * i + 1], sl2, -base));
-        sum += p0 + p1;
-        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-        packed[i] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      row_sum = row_sum * alpha + sum;
-      // the previous tile's product has had this tile's softmax to finish: take it in before its buffer is reused
-      if (j > 0) {
-        ok = absorb_pv(j - 1);
+        for (int i = 0; i < kD; ++i) o[i] = fmaf(o[i], pending_alpha, pv[i]);
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) bar_arrive(&sm.pv_empty);
+        return true;
+      };
+      for (int j = 0; j < t.num_kt && ok; ++j, ++g) {
+        const int b = g & 1, s = g % kKvStages;
+        const int key0 = (t.first_kt + j) * kKeysTC;
+        ok = bar_wait(&sm.s_full[b], (g >> 1) & 1, abort_flag);
         if (!ok) break;
-      }
-      pending_alpha = alpha;
-      // P as bfloat16 into the swizzled K-major tile: row r at (r / 8) * 1024 + (r % 8) * 128, 16-byte chunk c at c ^ (r % 8)
-      uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p[b]) + (row >> 3) * 1024 + (row & 7) * 128;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        float sc[kKeysTC];
+        tmem_ld64(tmem + lane_base + b * kKeysTC, sc);
+        // S_b has been read: the issuer may overwrite it with key tile g + 2
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) bar_arrive(&sm.s_empty[b]);
+        const bool need_mask = key0 + kKeysTC - 1 > t.pos0 || (window > 0 && key0 < t.pos0 + t.rows_here - window);
+        float tile_max = -INFINITY;
+        if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < kKeysTC / 8; ++c)
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      // The last tile of a request may hold keys past its end whose values were never written: zero those V rows,
-      // so that 0 * (whatever is there) stays 0.  A V row is 128 contiguous bytes whatever the swizzle.
-      if (key0 + kKeysTC > n_keys) {
-        const int first_bad = n_keys - key0;
-        for (int r = first_bad + (row >> 3); r < kKeysTC; r += kRowsTC / 8) {
-          uint8_t* v_row = reinterpret_cast<uint8_t*>(sm.v[s]) + (r >> 3) * 1024 + (r & 7) * 128;
-          *reinterpret_cast<uint4*>(v_row + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < kKeysTC; ++i) {
+            const int key = key0 + i;
+            sc[i] = (key >= my_lo && key <= my_pos) ? sc[i] : -INFINITY;
+            tile_max = fmaxf(tile_max, sc[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < kKeysTC; ++i) tile_max = fmaxf(tile_max, sc[i]);
         }
-      }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) bar_arrive(&sm.p_full[b]);
-    }
-    if (ok && num_kt > 0) ok = absorb_pv(num_kt - 1);
-    if (ok && row < rows_here) {
-      const float inv = 1.0f / row_sum;
-      __nv_bfloat16* dst = out + ((size_t)(row0 + row) * q_heads + head) * kD;
+        const float new_max = fmaxf(row_max, tile_max);
+        const float finite_max = (new_max == -INFINITY) ? 0.0f : new_max;
+        const float base = finite_max * sl2;
+        const float alpha = exp2f((row_max - finite_max) * sl2);
+        row_max = new_max;
+        uint32_t packed[kKeysTC / 2];
+        float sum = 0.0f;
 #pragma unroll
-      for (int c = 0; c < kD / 8; ++c) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
+        for (int i = 0; i < kKeysTC / 2; ++i) {
+          const float p0 = exp2f(fmaf(sc[2 * i], sl2, -base));
+          const float p1 = exp2f(fmaf(sc[2 * i + 1], sl2, -base));
+          sum += p0 + p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           packed[i] = *reinterpret_cast<uint32_t*>(&h);
         }
-        *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        row_sum = row_sum * alpha + sum;
+        // the previous tile's product has had this tile's softmax to finish: take it in before its buffer is reused
+        if (j > 0) {
+          ok = absorb_pv(g - 1);
+          if (!ok) break;
+        }
+        pending_alpha = alpha;
+        // P as bfloat16 into the swizzled K-major tile: row r at (r / 8) * 1024 + (r % 8) * 128, 16-byte chunk c at c ^ (r % 8)
+        uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p[b]) + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < kKeysTC / 8; ++c)
+          *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+        // The last tile of a request may hold keys past its end whose values were never written: zero those V rows,
+        // so that 0 * (whatever is there) stays 0.  A V row is 128 contiguous bytes whatever the swizzle.
+        if (key0 + kKeysTC > t.n_keys) {
+          const int first_bad = t.n_keys - key0;
+          for (int r = first_bad + (row >> 3); r < kKeysTC; r += kRowsTC / 8) {
+            uint8_t* v_row = reinterpret_cast<uint8_t*>(sm.v[s]) + (r >> 3) * 1024 + (r & 7) * 128;
+            *reinterpret_cast<uint4*>(v_row + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) bar_arrive(&sm.p_full[b]);
+      }
+      if (ok) ok = absorb_pv(g - 1);
+      if (ok && row < t.rows_here) {
+        const float inv = 1.0f / row_sum;
+        __nv_bfloat16* dst = out + ((size_t)(t.row0 + row) * q_heads + head) * kD;
+#pragma unroll
+        for (int c = 0; c < kD / 8; ++c) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
+            packed[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -373,7 +414,8 @@ using namespace tlie;
 TLIE_EXPORT int tlie_prefill_attention_tc_tile_rows() { return kRowsTC; }
 
 // q: the step's rows [tokens, q_row_stride] starting with the rotated q heads (head size 64); pages: one layer's pool
-// [num_pages, 2, kv_heads, page_size, 64]; tiles: int32 [n_tiles, 2] of 128-row work items; error_flag: device int, zero.
+// [num_pages, 2, kv_heads, page_size, 64]; tiles: int32 [n_tiles, 4] work items of one or two 128-row tiles (request, first
+// row, request or -1, first row); error_flag: device int, zero.
 TLIE_EXPORT int tlie_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* pages, int num_pages, const int* tiles,
                                           int n_tiles, const int* seq_starts, const int* first_positions, const int* block_table,
                                           int table_stride, void* out, int q_heads, int kv_heads, int page_size, int window, float scale,

@@ -10,6 +10,34 @@ ATTENTION_TILE_ROWS = 64   # rows of one work item of the prompt-attention kerne
 ATTENTION_TC_TILE_ROWS = 128   # rows of one work item of the tensor-memory kernel (csrc/attention_prefill_tc.cu)
 
 
+def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int]) -> list[int]:
+    """Work items of the tensor-memory attention kernel: (entry, first row, entry or -1, first row) per item.
+
+    A run of ATTENTION_TC_TILE_ROWS rows late in a long request sees many keys, an early one few.  Pairing the heaviest
+    tile with the lightest, the second heaviest with the second lightest, and so on, gives every CTA about the same
+    number of key tiles, so the grid finishes together instead of waiting for the last heavy tiles.
+    """
+    singles = []
+    for index, count in enumerate(q_lens):
+        for offset in range(0, count, ATTENTION_TC_TILE_ROWS):
+            rows = min(ATTENTION_TC_TILE_ROWS, count - offset)
+            work = -(-(first_positions[index] + offset + rows) // 64)
+            singles.append((work, index, seq_starts[index] + offset))
+    singles.sort(key=lambda item: -item[0])
+    flat: list[int] = []
+    low, high = 0, len(singles) - 1
+    while low <= high:
+        _, index, row = singles[low]
+        if low < high:
+            _, index2, row2 = singles[high]
+            flat += [index, row, index2, row2]
+        else:
+            flat += [index, row, -1, 0]
+        low += 1
+        high -= 1
+    return flat
+
+
 @dataclass
 class StepEntry:
     """The next tokens of one request and the places among them whose logits are wanted."""
@@ -55,7 +83,7 @@ class StepContext:
     max_q_len: int
     max_seq_len: int
     attn_tiles: torch.Tensor | None = None
-    attn_tiles_tc: torch.Tensor | None = None   # the same work list in runs of ATTENTION_TC_TILE_ROWS rows
+    attn_tiles_tc: torch.Tensor | None = None   # work items of the tensor-memory kernel: pairs of 128-row runs (int32 [n, 4])
 
     @property
     def decode_only(self) -> bool:
@@ -84,10 +112,7 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
     for index, count in enumerate(q_lens):
         for offset in range(0, count, ATTENTION_TILE_ROWS):
             tiles += [index, seq_starts[index] + offset]
-    tiles_tc: list[int] = []
-    for index, count in enumerate(q_lens):
-        for offset in range(0, count, ATTENTION_TC_TILE_ROWS):
-            tiles_tc += [index, seq_starts[index] + offset]
+    tiles_tc = paired_attention_tiles(q_lens, first_positions, seq_starts)
     sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows, tiles, tiles_tc]
     flat: list[int] = []
     offsets = []
@@ -113,5 +138,5 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=q_lens,
         host_first_positions=list(first_positions), host_state_slots=list(slots),
         max_q_len=max(q_lens), max_seq_len=max(seq_lens), attn_tiles=views[8].view(-1, 2),
-        attn_tiles_tc=views[9].view(-1, 2),
+        attn_tiles_tc=views[9].view(-1, 4),
     )

@@ -260,7 +260,7 @@ TC_ATTENTION_MIN_ROWS_PER_TILE = 32
 
 def prefill_attention_tc(qkv, pages, tiles, seq_starts, first_positions, block_table, out, q_heads: int, kv_heads: int, page_size: int,
                          window: int, scale: float) -> None:
-    """Flash attention of every 128-row tile in ``tiles`` on the 5th-generation tensor cores; head size 64, bfloat16."""
+    """Flash attention of the work items in ``tiles`` (int32 [n, 4], see ``paired_attention_tiles``) on the 5th-generation tensor cores; head size 64, bfloat16."""
     ops = _ops()
     lib = load_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"])
     ops._check(
@@ -284,7 +284,7 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
         return True
     tc_tiles = getattr(batch, "attn_tiles_tc", None)
     if (use_tc_attention and tc_tiles is not None and head_dim == 64 and page_size % 64 == 0 and pages.is_contiguous()
-            and batch.num_tokens >= TC_ATTENTION_MIN_ROWS_PER_TILE * tc_tiles.shape[0]):
+            and batch.num_tokens >= TC_ATTENTION_MIN_ROWS_PER_TILE * 2 * tc_tiles.shape[0]):
         prefill_attention_tc(qkv, pages, tc_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads, page_size, window, scale)
         return True
     if batch.attn_tiles is not None and head_dim <= 128:
