@@ -115,3 +115,30 @@ def test_command_line_generates_on_the_gpu(model_folders, capsys):
     kernels = json.loads(capsys.readouterr().out)["kernels"]
     assert {"add_rmsnorm", "rope_store", "linear_qkv", "attention_decode_split_kv", "argmax"} <= set(kernels)
     assert all(k["median_us"] > 0 for k in kernels.values())
+
+
+def test_steps_launched_ahead_keep_the_engine_consistent(model_folders):
+    """Pure decode steps are launched one ahead of their step() call; cancelling and adding requests meanwhile must not
+    disturb anybody's tokens nor leak pages."""
+    config, weights = plain_llama.load_model(model_folders["b"])
+    prompts = _prompts(config["vocab_size"], [9, 30, 17, 5], seed=23)
+    want = [plain_llama.generate_greedy(config, weights, p, 24) for p in prompts]
+    engine = _engine(model_folders["b"], use_cuda_graphs=True)
+    ids = [engine.add_request(p, SamplingParams(max_tokens=24)) for p in prompts[:3]]
+    steps = 0
+    late = None
+    while engine.has_unfinished():
+        engine.step()
+        steps += 1
+        if steps == 6:
+            assert engine._ahead is not None, "a decode step should be in flight between step() calls"
+            engine.cancel(ids[1])                                   # its token of the step in flight is dropped
+            late = engine.add_request(prompts[3], SamplingParams(max_tokens=24))   # joins after the step in flight
+        assert steps < 200
+    assert engine.requests[ids[0]].generated == want[0]
+    assert engine.requests[ids[2]].generated == want[2]
+    assert engine.requests[late].generated == want[3]
+    assert engine.requests[ids[1]].finish_reason == "cancelled" and len(engine.requests[ids[1]].generated) < 24
+    assert engine.requests[ids[1]].generated == want[1][: len(engine.requests[ids[1]].generated)]
+    engine.runner.cache.check()
+    assert engine.runner.cache.free_pages() == engine.runner.cache.total_pages()
