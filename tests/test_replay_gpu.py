@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 
 # largest |difference| allowed, as a fraction of the largest |logit| of the request set
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
-LENGTHS = {"a": [1, 7, 33, 100, 128, 65], "b": [3, 19, 64, 100, 255, 130], "c": [2, 40, 77, 300, 129, 64], "d": [5, 200, 64, 1100, 129, 700]}
+LENGTHS = {"a": [1, 7, 33, 100, 128, 65], "b": [3, 19, 64, 100, 255, 130], "c": [2, 40, 77, 300, 129, 64], "d": [5, 200, 64, 1100, 129, 700],
+           "e": [4, 640, 65, 31, 257, 128]}
 
 
 @pytest.fixture(scope="module")
@@ -62,7 +63,7 @@ def test_far_key_decides_the_logits(model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("key", ["a", "b", "c", "d", "e"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
 def test_replay(cases, key, dtype, cut):
     folder, requests, full, scale = cases[key]

@@ -37,4 +37,13 @@ TINY_D = dict(
 )
 SEED_D = 7
 
-ALL = {"a": (TINY_A, SEED_A), "b": (TINY_B, SEED_B), "c": (TINY_C, SEED_C), "d": (TINY_D, SEED_D)}
+# 2 layers, 6 query heads over 3 kv heads of 64 (the head size of the 1.1B model), widths that are no power of two
+TINY_E = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=200, intermediate_size=304, num_hidden_layers=2,
+    num_attention_heads=6, num_key_value_heads=3, head_dim=64, max_position_embeddings=700, vocab_size=333,
+    rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False, hidden_act="silu", attention_bias=False,
+    bos_token_id=1, eos_token_id=2, torch_dtype="bfloat16",
+)
+SEED_E = 11
+
+ALL = {"a": (TINY_A, SEED_A), "b": (TINY_B, SEED_B), "c": (TINY_C, SEED_C), "d": (TINY_D, SEED_D), "e": (TINY_E, SEED_E)}

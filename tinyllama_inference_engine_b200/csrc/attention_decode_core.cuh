@@ -89,6 +89,9 @@ struct DecodeAttnItem {
   int pos, n_keys, lo, tile_begin, tile_end, next_load;
   const int* table;
   bool patch_new;
+  // cos (first half) and sin (second half) of this position's rotation angles, in shared memory: worked out in the first
+  // step, one angle per thread, since positions are known before q is
+  float* rotation;
 };
 
 constexpr size_t kPipelineBytes = (size_t)kWarps * kStages * 2 * kTileElems * sizeof(__nv_bfloat16);
@@ -117,6 +120,16 @@ __device__ __forceinline__ void decode_attn_prologue(const DecodeAttnParams& p, 
   // cache another run wrote finds the key in the page already.)
   it.patch_new = p.fuse_rope && p.write_cache && it.pos / kTileKeys >= it.tile_begin && it.pos / kTileKeys < it.tile_end &&
                          ((it.pos / kTileKeys - it.tile_begin) % kWarps) == warp;
+
+  __shared__ float rotation_table[kD];
+  it.rotation = rotation_table;
+  if (p.fuse_rope && p.inv_freq != nullptr) {
+    for (int d = threadIdx.x; d < kD / 2; d += kWarps * 32) {
+      const float angle = (float)it.pos * p.inv_freq[d];
+      rotation_table[d] = cosf(angle);
+      rotation_table[kD / 2 + d] = sinf(angle);
+    }
+  }
 
   // prologue: this warp's tiles are it.tile_begin + warp, + kWarps, ...
   it.next_load = it.tile_begin + warp;
@@ -152,6 +165,7 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
   }
 
   if (p.fuse_rope && p.inv_freq != nullptr) {
+    __syncthreads();   // the rotation table of the first step is complete
     // pair (d, d + kD/2): k-steps ks and ks + kD/32 hold them in the same register slot of the same thread
     if constexpr (kD % 32 == 0) {
 #pragma unroll
@@ -159,8 +173,7 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int d = ks * 16 + 2 * t + half * 8;
-          const float a0 = (float)it.pos * p.inv_freq[d], a1 = (float)it.pos * p.inv_freq[d + 1];
-          const float c0 = cosf(a0), s0 = sinf(a0), c1 = cosf(a1), s1 = sinf(a1);
+          const float c0 = it.rotation[d], s0 = it.rotation[kD / 2 + d], c1 = it.rotation[d + 1], s1 = it.rotation[kD / 2 + d + 1];
 #pragma unroll
           for (int row = 0; row < 2; ++row) {
             const int r = half * 2 + row;
@@ -205,11 +218,13 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
       const size_t plane = (size_t)p.kv_heads * p.page_size * kD;
       __nv_bfloat16* k_dst = p.pages + (size_t)it.table[it.pos / p.page_size] * 2 * plane + ((size_t)it.kvh * p.page_size + (it.pos % p.page_size)) * kD;
       const int row = it.pos % kTileKeys;
-      for (int d = lane; d < kD / 2; d += 32) {
+#pragma unroll
+      for (int i = 0; i < (kD / 2 + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= kD / 2) break;
         float first = ldcg_bf16(k_new + d), second = ldcg_bf16(k_new + d + kD / 2);
         if (p.inv_freq != nullptr) {
-          const float angle = (float)it.pos * p.inv_freq[d];
-          const float c = cosf(angle), sn = sinf(angle);
+          const float c = it.rotation[d], sn = it.rotation[kD / 2 + d];
           const float a = first * c - second * sn, b = second * c + first * sn;
           first = a;
           second = b;
@@ -366,27 +381,45 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
   __syncthreads();
   if (!*last_arrival) return;
   __threadfence();
-  // one warp per query head; lane sp holds part sp's maximum and sum (p.splits <= 32), so every load is issued at once
+  // One warp per query head, lane sp holds part sp's maximum and sum (p.splits <= 32).  The parts' outputs do not depend
+  // on those, so their loads go out first, eight parts at a time, and everything is one trip to L2 and back.
   for (int r = warp; r < group; r += kWarps) {
     const size_t pair = (size_t)it.seq * p.q_heads + it.kvh * group + r;
     const float* ml = p.partial_ml + pair * p.splits * 2;
-    float part_max = -INFINITY, part_sum = 0.0f;
-    if (lane < p.splits) {
-      part_max = __ldcg(ml + lane * 2);
-      part_sum = __ldcg(ml + lane * 2 + 1);
-    }
-    const float m = warp_max(part_max);
-    const float f = (part_max == -INFINITY) ? 0.0f : exp2f(part_max - m);
-    const float sum = warp_sum(f * part_sum);
-    for (int d0 = 0; d0 < kD; d0 += 32) {
-      const int d = d0 + lane;
-      float acc = 0.0f;
-#pragma unroll 8
-      for (int sp = 0; sp < p.splits; ++sp) {
-        const float fs = __shfl_sync(0xffffffffu, f, sp);
-        if (d < kD) acc += fs * __ldcg(p.partial_o + (pair * p.splits + sp) * kD + d);
+    constexpr int kPerLane = (kD + 31) / 32;
+    float acc[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) acc[i] = 0.0f;
+    float part_max = -INFINITY, part_sum = 0.0f, m = 0.0f, f = 0.0f, sum = 0.0f;
+    for (int sp0 = 0; sp0 < p.splits; sp0 += 8) {
+      float part[8][kPerLane];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+          const int d = lane + 32 * i;
+          part[j][i] = (sp0 + j < p.splits && d < kD) ? __ldcg(p.partial_o + (pair * p.splits + sp0 + j) * kD + d) : 0.0f;
+        }
+      if (sp0 == 0) {
+        if (lane < p.splits) {
+          part_max = __ldcg(ml + lane * 2);
+          part_sum = __ldcg(ml + lane * 2 + 1);
+        }
+        m = warp_max(part_max);
+        f = (part_max == -INFINITY) ? 0.0f : exp2f(part_max - m);
+        sum = warp_sum(f * part_sum);
       }
-      if (d < kD) p.out[pair * kD + d] = __float2bfloat16_rn(acc / sum);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float fs = __shfl_sync(0xffffffffu, f, (sp0 + j) & 31);
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) acc[i] += fs * part[j][i];   // parts past p.splits were loaded as zeros
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < kD) p.out[pair * kD + d] = __float2bfloat16_rn(acc[i] / sum);
     }
   }
   if (threadIdx.x == 0) p.tickets[it.seq * p.kv_heads + it.kvh] = 0;   // ready for the next launch

@@ -1,7 +1,6 @@
 // The weight-streaming product for up to 16 rows as building blocks: one struct per (rows, input, output) variant with
 // the three steps a kernel strings together -- issue the weight loads of a round, stage x, run the tiles.  The stand-alone
-// kernels (gemv_fused.cu) call them around a programmatic-dependency wait; the fused decode step (decode_step_fused.cu)
-// calls them around its grid barriers.  Activations another CTA may have written are read through L2 (ld.global.cg /
+// kernels (gemv_fused.cu) call them around a programmatic-dependency wait.  Activations another CTA may have written are read through L2 (ld.global.cg /
 // cp.async.cg), never through a stale L1 line; weights are read-only and bypass L1.
 #pragma once
 
@@ -32,6 +31,113 @@ __device__ __forceinline__ uint4 load_stream_16(const void* p) {
   return v;
 }
 
+
+// x into shared memory as bfloat16 (nothing for X_DIRECT); ends with a block-wide barrier.  X_NORM stores
+// bf16(residual * norm_weight) and leaves 1 / rms of each row in row_scale: the epilogue applies it.
+// kBatch: 16-byte loads of the residual a lane has in flight (more: fewer dependent round trips, more registers).
+template <int MT, int XMODE, int kBatch = 8>
+__device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* xs, float* row_scale) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = a.K;
+  // --- stage x in shared memory as bfloat16, once per CTA ----------------------------------------
+  // Shared memory is kept small on purpose: the weight loads in flight are tracked in L1, which shrinks as
+  // shared memory grows, and with it the bandwidth a CTA can pull.
+  if (XMODE == X_PLAIN) {
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
+    const int chunks = K / 8;
+    for (int idx = threadIdx.x; idx < MT * 8 * chunks; idx += kGemvWarps * 32) {
+      const int m = idx / chunks;
+      const int c = idx - m * chunks;
+      cp_async_16(xs + (size_t)m * a.x_stride + c * 8, x + (size_t)(m < a.M ? m : 0) * a.ldx + c * 8, m < a.M);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+  } else if (XMODE == X_NORM) {
+    const float* residual = reinterpret_cast<const float*>(a.x);
+    const int chunks = K / 4;
+    for (int m = warp; m < MT * 8; m += kGemvWarps) {
+      __nv_bfloat16* dst = xs + (size_t)m * a.x_stride;
+      float sum = 0.0f;
+      if (m < a.M) {
+        const float* r = residual + (size_t)(a.rows ? a.rows[m] : m) * K;
+        for (int c0 = lane; c0 < chunks; c0 += 32 * kBatch) {
+          float4 v[kBatch];
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i) {
+            const int c = c0 + 32 * i;
+            v[i] = c < chunks ? __ldcg(reinterpret_cast<const float4*>(r + c * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i) {
+            const int c = c0 + 32 * i;
+            sum += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+            if (c < chunks) {
+              const float4 nw = __ldg(reinterpret_cast<const float4*>(a.norm_weight + c * 4));   // every warp reads these: L1 hits
+              *reinterpret_cast<uint2*>(dst + c * 4) = make_uint2(pack_bf16(v[i].x * nw.x, v[i].y * nw.y), pack_bf16(v[i].z * nw.z, v[i].w * nw.w));
+            }
+          }
+        }
+      } else {
+        for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint2*>(dst + c * 4) = make_uint2(0, 0);
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) row_scale[m] = 1.0f / sqrtf(sum / (float)K + a.eps);
+    }
+    __syncthreads();
+  }
+}
+
+// The end of a 16-row tile: the warps' partial tiles are summed through `red` ([warp][TILES][16][MT * 8 + 1] floats) and
+// stored by the variant's epilogue.  acc[tile][mt] is a warp's m16n8 accumulator (weight rows x activation rows).
+template <int MT, int XMODE, int EPI>
+__device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float (&acc)[(EPI == EPI_GATED) ? 2 : 1][MT][4], float* red,
+                                                  const float* row_scale, int n0) {
+  constexpr int TILES = (EPI == EPI_GATED) ? 2 : 1;
+  constexpr int kRedRow = MT * 8 + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_rows = (EPI == EPI_GATED) ? a.N / 2 : a.N;
+#pragma unroll
+  for (int tile = 0; tile < TILES; ++tile) {
+    float* base = red + ((size_t)warp * TILES + tile) * 16 * kRedRow;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      base[g * kRedRow + mt * 8 + 2 * t] = acc[tile][mt][0];
+      base[g * kRedRow + mt * 8 + 2 * t + 1] = acc[tile][mt][1];
+      base[(g + 8) * kRedRow + mt * 8 + 2 * t] = acc[tile][mt][2];
+      base[(g + 8) * kRedRow + mt * 8 + 2 * t + 1] = acc[tile][mt][3];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * MT * 8; idx += kGemvWarps * 32) {
+    const int m = idx / 16;
+    const int r = idx - m * 16;
+    if (m >= a.M || n0 + r >= n_rows) continue;
+    float sum[TILES];
+#pragma unroll
+    for (int tile = 0; tile < TILES; ++tile) {
+      sum[tile] = 0.0f;
+#pragma unroll
+      for (int wi = 0; wi < kGemvWarps; ++wi) sum[tile] += red[((size_t)wi * TILES + tile) * 16 * kRedRow + r * kRedRow + m];
+      if (XMODE == X_NORM) sum[tile] *= row_scale[m];
+    }
+    const size_t o = (size_t)m * n_rows + n0 + r;
+    if (EPI == EPI_STORE_BF16) {
+      reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(sum[0]);
+    } else if (EPI == EPI_STORE_F32) {
+      reinterpret_cast<float*>(a.out)[o] = sum[0];
+    } else if (EPI == EPI_ACCUM) {
+      reinterpret_cast<float*>(a.out)[o] = __ldcg(reinterpret_cast<const float*>(a.out) + o) + sum[0];
+    } else {
+      // gate and up are rounded to bfloat16 first, as when the product is stored and read back
+      const float gate = __bfloat162float(__float2bfloat16_rn(sum[0]));
+      const float up = __bfloat162float(__float2bfloat16_rn(sum[TILES - 1]));
+      reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
+    }
+  }
+  __syncthreads();   // red is written again by the next tile
+}
 
 // TILES: 1 (16 weight rows) or 2 (GATED: 16 gate rows + the 16 up rows N/2 below).
 template <int MT, int XMODE, int EPI>
@@ -71,60 +177,7 @@ struct GemvPhase {
     }
   }
 
-  // x into shared memory as bfloat16 (nothing for X_DIRECT); ends with a block-wide barrier
-  __device__ __forceinline__ void stage_x(const GemvArgs& a, __nv_bfloat16* xs, float* row_scale) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int K = a.K;
-  // --- stage x in shared memory as bfloat16, once per CTA ----------------------------------------
-  // Shared memory is kept small on purpose: the weight loads in flight are tracked in L1, which shrinks as
-  // shared memory grows, and with it the bandwidth a CTA can pull.
-  if (XMODE == X_PLAIN) {
-    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
-    const int chunks = K / 8;
-    for (int idx = threadIdx.x; idx < MT * 8 * chunks; idx += kGemvWarps * 32) {
-      const int m = idx / chunks;
-      const int c = idx - m * chunks;
-      cp_async_16(xs + (size_t)m * a.x_stride + c * 8, x + (size_t)(m < a.M ? m : 0) * a.ldx + c * 8, m < a.M);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-  } else if (XMODE == X_NORM) {
-    const float* residual = reinterpret_cast<const float*>(a.x);
-    const int chunks = K / 4;
-    constexpr int kBatch = 8;   // float4 per lane in flight
-    for (int m = warp; m < MT * 8; m += kGemvWarps) {
-      __nv_bfloat16* dst = xs + (size_t)m * a.x_stride;
-      float sum = 0.0f;
-      if (m < a.M) {
-        const float* r = residual + (size_t)(a.rows ? a.rows[m] : m) * K;
-        for (int c0 = lane; c0 < chunks; c0 += 32 * kBatch) {
-          float4 v[kBatch];
-#pragma unroll
-          for (int i = 0; i < kBatch; ++i) {
-            const int c = c0 + 32 * i;
-            v[i] = c < chunks ? __ldcg(reinterpret_cast<const float4*>(r + c * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-#pragma unroll
-          for (int i = 0; i < kBatch; ++i) {
-            const int c = c0 + 32 * i;
-            sum += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-            if (c < chunks) {
-              const float4 nw = __ldg(reinterpret_cast<const float4*>(a.norm_weight + c * 4));   // every warp reads these: L1 hits
-              *reinterpret_cast<uint2*>(dst + c * 4) = make_uint2(pack_bf16(v[i].x * nw.x, v[i].y * nw.y), pack_bf16(v[i].z * nw.z, v[i].w * nw.w));
-            }
-          }
-        }
-      } else {
-        for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint2*>(dst + c * 4) = make_uint2(0, 0);
-      }
-      sum = warp_sum(sum);
-      if (lane == 0) row_scale[m] = 1.0f / sqrtf(sum / (float)K + a.eps);
-    }
-    __syncthreads();
-  }
-
-  }
+  __device__ __forceinline__ void stage_x(const GemvArgs& a, __nv_bfloat16* xs, float* row_scale) { gemv_stage_x<MT, XMODE>(a, xs, row_scale); }
 
   // tiles first_tile, first_tile + tile_step, ...; the first round of the first tile is in wreg already if first_round_issued
   __device__ __forceinline__ void run(const GemvArgs& a, __nv_bfloat16* xs, float* red, const float* row_scale, int first_tile, int tile_step,
@@ -155,7 +208,7 @@ struct GemvPhase {
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const int m = mt * 8 + g;
-            xdirect[u][mt] = (k < K && m < a.M) ? *reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + k) : make_uint4(0, 0, 0, 0);
+            xdirect[u][mt] = (k < K && m < a.M) ? __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + k)) : make_uint4(0, 0, 0, 0);
           }
         }
       }
@@ -184,46 +237,7 @@ struct GemvPhase {
       }
     }
 
-    // sum the warps' tiles, then the epilogue
-#pragma unroll
-    for (int tile = 0; tile < TILES; ++tile) {
-      float* base = red + ((size_t)warp * TILES + tile) * 16 * kRedRow;
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        base[g * kRedRow + mt * 8 + 2 * t] = acc[tile][mt][0];
-        base[g * kRedRow + mt * 8 + 2 * t + 1] = acc[tile][mt][1];
-        base[(g + 8) * kRedRow + mt * 8 + 2 * t] = acc[tile][mt][2];
-        base[(g + 8) * kRedRow + mt * 8 + 2 * t + 1] = acc[tile][mt][3];
-      }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < 16 * MT * 8; idx += kGemvWarps * 32) {
-      const int m = idx / 16;
-      const int r = idx - m * 16;
-      if (m >= a.M || n0 + r >= n_rows) continue;
-      float sum[TILES];
-#pragma unroll
-      for (int tile = 0; tile < TILES; ++tile) {
-        sum[tile] = 0.0f;
-#pragma unroll
-        for (int wi = 0; wi < kGemvWarps; ++wi) sum[tile] += red[((size_t)wi * TILES + tile) * 16 * kRedRow + r * kRedRow + m];
-        if (XMODE == X_NORM) sum[tile] *= row_scale[m];
-      }
-      const size_t o = (size_t)m * n_rows + n0 + r;
-      if (EPI == EPI_STORE_BF16) {
-        reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(sum[0]);
-      } else if (EPI == EPI_STORE_F32) {
-        reinterpret_cast<float*>(a.out)[o] = sum[0];
-      } else if (EPI == EPI_ACCUM) {
-        reinterpret_cast<float*>(a.out)[o] = __ldcg(reinterpret_cast<const float*>(a.out) + o) + sum[0];
-      } else {
-        // gate and up are rounded to bfloat16 first, as when the product is stored and read back
-        const float gate = __bfloat162float(__float2bfloat16_rn(sum[0]));
-        const float up = __bfloat162float(__float2bfloat16_rn(sum[TILES - 1]));
-        reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
-      }
-    }
-    __syncthreads();   // red is written again by the next tile
+    gemv_reduce_store<MT, XMODE, EPI>(a, acc, red, row_scale, n0);
   }
   }
 };
