@@ -77,3 +77,15 @@ def test_step_refuses_bad_batches(model_folders, monkeypatch):
     assert list(runner.cache.records) == ["x"]
     runner.finish("x")
     runner.cache.check()
+
+
+def test_gemm_tile_width_prefers_full_waves():
+    """Waves of 148 persistent CTAs x tile width: the product whose 256-wide tiles fill one wave and a sliver gets 160."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    assert fast.gemm_tile_width(2048, 2560) == 160      # 160 tiles of 256 would be two waves; 256 tiles of 160 are two narrower ones
+    assert fast.gemm_tile_width(2048, 2048) == 256      # 128 tiles: one wave
+    assert fast.gemm_tile_width(256, 2048) == 128       # few row blocks: narrow tiles keep more CTAs busy
+    for rows in (128, 300, 5000):
+        for cols in (64, 1000, 32000):
+            assert fast.gemm_tile_width(rows, cols) in fast.GEMM_TILE_WIDTHS

@@ -121,7 +121,8 @@ def test_linear_bf16(ops, M, N, K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,rotary_dim,theta", [(4, 2, 16, 16, 16, 1e4), (6, 2, 32, 32, 32, 5e5), (3, 3, 48, 16, 24, 777.0), (8, 1, 128, 64, 128, 1e4)])
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,rotary_dim,theta", [(4, 2, 16, 16, 16, 1e4), (6, 2, 32, 32, 32, 5e5), (3, 3, 48, 16, 24, 777.0), (8, 1, 128, 64, 128, 1e4),
+                                                                             (5, 1, 64, 16, 32, 1e4)])
 def test_rope_store(ops, dtype, q_heads, kv_heads, head_dim, page_size, rotary_dim, theta):
     rng = np.random.default_rng(5)
     torch.manual_seed(5)
@@ -373,7 +374,7 @@ def test_decode_attention_with_rotation_and_cache_write(ops, q_heads, kv_heads, 
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (2048, 2560, 2048), (300, 200, 136), (2048, 2048, 5632), (129, 1000, 2048), (1000, 131, 80)])
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 160, 192, 256])
 def test_gemm_tcgen05(ops, M, N, K, tile_n):
     """The tcgen05 / TMA / tensor-memory product against a 32-bit product of the same bfloat16 values, tails included."""
     from tinyllama_inference_engine_b200.ops import fast

@@ -102,12 +102,16 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) 
       : "r"(taddr));
 }
 
+// BN: any multiple of 16 up to 256 (the N of one tcgen05.mma with M = 128).  Widths between 128 and 256 exist for products
+// whose tiles would otherwise fill one wave of CTAs and a sliver of a second one.
 template <int BN>
 struct GemmShape {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kStageBytes = (kBM + BN) * kBK * 2;
+  static constexpr int kStages = (220 * 1024 / kStageBytes) < 6 ? (220 * 1024 / kStageBytes) : 6;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
-  static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
+  static constexpr int kAccStride = BN <= 128 ? 128 : 256;   // tensor memory is allocated in powers of two
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "the N of a tcgen05.mma with M = 128");
+  static_assert(2 * kAccStride <= 512, "two accumulators must fit the 512 columns of tensor memory");
 };
 
 // EPI 0: bfloat16 out; EPI 1: 32-bit out; EPI 2 (BN = 256): w holds [gate rows | up rows] (`N` = rows of one half);
@@ -131,7 +135,7 @@ __global__ void __launch_bounds__(kGemmThreads)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kTileN = EPI == 2 ? BN / 2 : BN;   // output columns of a tile
-  constexpr int kTmemCols = 2 * BN;                // two accumulators
+  constexpr int kTmemCols = 2 * Shape::kAccStride;   // two accumulators
   const int m_blocks = (M + kBM - 1) / kBM;
   const int num_tiles = m_blocks * ((N + kTileN - 1) / kTileN);
   const int k_blocks = (K + kBK - 1) / kBK;
@@ -192,7 +196,7 @@ __global__ void __launch_bounds__(kGemmThreads)
         ok = mbar_wait(&accum_empty[acc], ((local >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t tmem_acc = tmem_base + acc * BN;
+        const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1;
@@ -220,7 +224,7 @@ __global__ void __launch_bounds__(kGemmThreads)
       const int m0 = (tile % m_blocks) * kBM, n0 = (tile / m_blocks) * kTileN;
       if (!mbar_wait(&accum_full[acc], (local >> 1) & 1, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const uint32_t tmem_acc = tmem_base + acc * BN + ((uint32_t)(sub * 32) << 16);
+      const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
       if (EPI == 2) {
 #pragma unroll 1
@@ -357,7 +361,7 @@ using namespace tlie;
 
 // out[M, N] = x[M, K] . w[N, K]^T.  x and w bfloat16 row-major with 16-byte aligned bases and K % 8 == 0 (TMA strides);
 // out bfloat16 (out_f32 = 0), 32-bit (1), or out_f32 = 2: w is [gate rows | up rows] of N rows each and out [M, N] = silu(gate) * up.
-// tile_n is 128 or 256.  `error_flag` (device int, zero) becomes 1 if a wait gave up.
+// tile_n is 128, 160, 192 or 256.  `error_flag` (device int, zero) becomes 1 if a wait gave up.
 TLIE_EXPORT int tlie_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int tile_n, int* error_flag,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -365,6 +369,12 @@ TLIE_EXPORT int tlie_gemm_tcgen05(const void* x, const void* w, void* out, int M
   if (out_f32 == 2) return launch_gemm<256, 2>(x, w, out, M, N, K, error_flag, stream);   // gated: N = rows of one half of w
   if (tile_n == 256) {
     return out_f32 ? launch_gemm<256, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<256, 0>(x, w, out, M, N, K, error_flag, stream);
+  }
+  if (tile_n == 192) {
+    return out_f32 ? launch_gemm<192, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<192, 0>(x, w, out, M, N, K, error_flag, stream);
+  }
+  if (tile_n == 160) {
+    return out_f32 ? launch_gemm<160, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<160, 0>(x, w, out, M, N, K, error_flag, stream);
   }
   if (tile_n == 128) {
     return out_f32 ? launch_gemm<128, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<128, 0>(x, w, out, M, N, K, error_flag, stream);

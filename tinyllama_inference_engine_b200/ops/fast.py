@@ -127,6 +127,16 @@ def tcgen05_error_flag(device: torch.device) -> torch.Tensor:
     return _tcgen05_error[device]
 
 
+GEMM_TILE_WIDTHS = (256, 192, 160, 128)
+
+
+def gemm_tile_width(M: int, N: int) -> int:
+    """The tile width whose waves of persistent CTAs cost least: waves x width, the wider tile on a tie (it reads x less often)."""
+    sms = SM_COUNT
+    row_blocks = -(-M // 128)
+    return min(GEMM_TILE_WIDTHS, key=lambda width: (-(-(row_blocks * -(-N // width)) // sms) * width, -width))
+
+
 def gemm_tcgen05(x, weight, out, tile_n: int | None = None) -> None:
     """out[M, N] = x[M, K] . weight[N, K]^T on the 5th-generation tensor cores; bfloat16 in, bfloat16 or 32-bit out."""
     ops = _ops()
@@ -135,7 +145,7 @@ def gemm_tcgen05(x, weight, out, tile_n: int | None = None) -> None:
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or K % 8 != 0 or not x.is_contiguous():
         raise KernelError("gemm_tcgen05 takes contiguous bfloat16 operands with K % 8 == 0", code="invalid_shape")
     if tile_n is None:
-        tile_n = 256 if N >= 1024 and (-(-M // 128)) * (-(-N // 256)) >= 120 else 128
+        tile_n = gemm_tile_width(M, N)
     ops._check(
         tcgen05_library().tlie_gemm_tcgen05(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(1 if out.dtype == torch.float32 else 0),
                                             c_int(tile_n), ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
