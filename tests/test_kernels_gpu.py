@@ -374,8 +374,9 @@ def test_decode_attention_with_rotation_and_cache_write(ops, q_heads, kv_heads, 
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (2048, 2560, 2048), (300, 200, 136), (2048, 2048, 5632), (129, 1000, 2048), (1000, 131, 80)])
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("tile_n", [128, 160, 192, 256])
-def test_gemm_tcgen05(ops, M, N, K, tile_n):
+def test_gemm_tcgen05(ops, M, N, K, tile_n, pair):
     """The tcgen05 / TMA / tensor-memory product against a 32-bit product of the same bfloat16 values, tails included."""
     from tinyllama_inference_engine_b200.ops import fast
 
@@ -386,15 +387,16 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n):
     scale = float(want.abs().max())
     for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 1.6e-2)):
         got = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
-        fast.gemm_tcgen05(x.cuda(), w.cuda(), got, tile_n=tile_n)
+        fast.gemm_tcgen05(x.cuda(), w.cuda(), got, tile_n=tile_n, pair=pair)
         torch.cuda.synchronize()
         assert int(fast.tcgen05_error_flag(got.device)) == 0, "a bounded wait inside the kernel gave up"
         error = (got.cpu().float() - want).abs()
         assert float(error.max()) <= tol * scale, (float(error.max()), scale, int(error.argmax()) // N, int(error.argmax()) % N)
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (2048, 5632, 2048), (300, 176, 136), (1000, 200, 80)])
-def test_gemm_tcgen05_gated(ops, M, inter, K):
+def test_gemm_tcgen05_gated(ops, M, inter, K, pair):
     from tinyllama_inference_engine_b200.ops import fast
 
     torch.manual_seed(14)
@@ -404,7 +406,7 @@ def test_gemm_tcgen05_gated(ops, M, inter, K):
     g, u = both[:, :inter], both[:, inter:]
     want = (g / (1 + torch.exp(-g))) * u
     got = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
-    fast.gemm_tcgen05_gated(x.cuda(), w.cuda(), got)
+    fast.gemm_tcgen05_gated(x.cuda(), w.cuda(), got, pair=pair)
     torch.cuda.synchronize()
     assert int(fast.tcgen05_error_flag(got.device)) == 0
     assert float((got.cpu().float() - want).abs().max()) <= 1.6e-2 * float(want.abs().max()) + 2e-3 * float(both.abs().max())

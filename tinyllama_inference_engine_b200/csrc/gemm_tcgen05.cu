@@ -16,91 +16,9 @@
 // rows and k, the epilogue stores only what is inside [M, N].
 // Every mbarrier wait is bounded: on a timeout the CTA raises `error_flag`, stops issuing work, lets copies in
 // flight land, frees its tensor memory and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05_utils.cuh"
 
 namespace tlie {
-
-constexpr int kBM = 128;
-constexpr int kBK = 64;                 // 64 bf16 = 128 bytes = one swizzle span
-constexpr int kUmmaK = 16;
-constexpr int kGemmThreads = 192;
-constexpr long long kWaitLimit = 1ll << 20;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Waits for the barrier's phase with a limit; false (and the CTA-wide abort flag set) when it gives up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (long long i = 0; i < kWaitLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(smem_u32(smem_dst)),
-               "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-               : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
-  uint64_t desc = 0;
-  desc |= (uint64_t)((smem_addr >> 4) & 0x3FFF);        // start address, 16-byte units
-  desc |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
-  desc |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
-  desc |= (uint64_t)1 << 46;                            // descriptor version of sm_100
-  desc |= (uint64_t)2 << 61;                            // layout: 128-byte swizzle
-  return desc;
-}
-
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, tile M x N.
-__host__ __device__ constexpr uint32_t umma_instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-}
 
 // BN: any multiple of 16 up to 256 (the N of one tcgen05.mma with M = 128).  Widths between 128 and 256 exist for products
 // whose tiles would otherwise fill one wave of CTAs and a sliver of a second one.
@@ -303,32 +221,6 @@ __global__ void __launch_bounds__(kGemmThreads)
   if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols));
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* found = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &status) == cudaSuccess && status == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(found);
-  }
-  return fn;
-}
-
-// A [rows, K] bfloat16 row-major matrix as a 2-D tensor map with boxes of box_rows x 64 and 128-byte swizzle.
-static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_tiled();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN, int EPI>

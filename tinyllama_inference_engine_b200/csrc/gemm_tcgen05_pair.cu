@@ -1,0 +1,293 @@
+// The tcgen05 product on pairs of SMs: out[M, N] = x[M, K] . w[N, K]^T, bfloat16 in, 32-bit accumulate.
+//
+// gemm_tcgen05.cu gives every CTA a 128 x BN tile and loads (128 + BN) x 64 elements per stage; at full tensor speed that
+// asks more of the path from L2 to the SMs than it delivers, and the tensor pipe idles a third to a half of the time.
+// Here two CTAs of a cluster share a 256 x BN tile (tcgen05.mma.cta_group::2): each loads its own 128 rows of x and only
+// HALF of the BN rows of w, the MMA reads both halves out of both CTAs' shared memory, and each CTA's tensor memory
+// receives its own 128 rows of the result.  A third less comes in per flop, and six stages fit where four did.
+//   * rank 0 of the pair (the leader) issues every MMA; both CTAs run a TMA producer and four epilogue warps;
+//   * both producers' copies complete on the LEADER's `full` barrier (the copy names it by its address in the pair's
+//     shared window); the leader expects the bytes of both;
+//   * tcgen05.commit arrives on the `empty` (stage read) and `accum_full` (tile done) barriers of both CTAs at once;
+//   * the epilogue warps of both CTAs arrive on the leader's `accum_empty` barrier (eight arrivals).
+// No copy is multicast: every CTA fetches what it needs itself.  Tiles: 256 rows x BN columns, pair p takes tiles
+// p, p + pairs, ... (m fastest).  Every wait is bounded as in gemm_tcgen05.cu; the pair leaves together (cluster barrier).
+#include "tcgen05_utils.cuh"
+
+namespace tlie {
+
+constexpr uint32_t kLeaderWindow = 0xFEFFFFFFu;   // a shared-memory address with the pair-rank bit cleared: the same offset in rank 0
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+  return rank;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// a tile load of this CTA into its own shared memory whose bytes are counted on the leader's barrier
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(map), "r"(smem_u32(bar) & kLeaderWindow), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair when the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "h"(both)
+               : "memory");
+}
+__device__ __forceinline__ void arrive_at_leader(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & kLeaderWindow) : "memory");
+}
+
+template <int BN>
+struct PairShape {
+  static constexpr int kStageBytes = (kBM + BN / 2) * kBK * 2;   // per CTA: its rows of x and its half of the rows of w
+  static constexpr int kStages = (220 * 1024 / kStageBytes) < 8 ? (220 * 1024 / kStageBytes) : 8;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kAccStride = BN <= 128 ? 128 : 256;       // tensor memory is allocated in powers of two
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "each CTA holds BN / 2 rows of w, in groups of 8");
+};
+
+// EPI as in gemm_tcgen05.cu: 0 bfloat16 out, 1 32-bit out, 2 (BN = 256) w = [gate rows | up rows] and out = silu(gate) * up.
+template <int BN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ out, int M, int N, int K,
+                     int* __restrict__ error_flag) {
+  using Shape = PairShape<BN>;
+  constexpr int kStages = Shape::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles need 1024-byte alignment
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kStages * Shape::kStageBytes);   // used in the leader only
+  uint64_t* empty = full + kStages;
+  uint64_t* accum_full = empty + kStages;      // [2]: the MMAs of a tile are done
+  uint64_t* accum_empty = accum_full + 2;      // [2], used in the leader only: both CTAs' epilogues have read the accumulator
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_rank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  constexpr int kTileN = EPI == 2 ? BN / 2 : BN;   // output columns of a tile
+  constexpr int kTmemCols = 2 * Shape::kAccStride;   // two accumulators
+  const int m_blocks = (M + 2 * kBM - 1) / (2 * kBM);
+  const int num_tiles = m_blocks * ((N + kTileN - 1) / kTileN);
+  const int k_blocks = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&accum_full[a], 1);
+      mbar_init(&accum_empty[a], 8);   // one arrival per epilogue warp of either CTA
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 2) {   // the same warp of both CTAs allocates, for the pair
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_holder)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything arrives on them
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {   // TMA producer of this CTA: one ring of stages across all of the pair's tiles
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+        const int m0 = (tile % m_blocks) * 2 * kBM + rank * kBM, n0 = (tile / m_blocks) * kTileN;
+        // this CTA's half of the tile's rows of w: rank 0 the first BN / 2 (the gate rows if gated), rank 1 the rest (the up rows)
+        const int w_row = EPI == 2 ? rank * N + n0 : n0 + rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          ok = mbar_wait(&empty[s], phase ^ 1, abort_flag);
+          if (!ok) break;
+          uint8_t* a_tile = tiles + s * Shape::kStageBytes;
+          uint8_t* b_tile = a_tile + kBM * kBK * 2;
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * Shape::kStageBytes);   // this CTA's bytes and the peer's
+          tma_load_2d_pair(a_tile, &map_a, kb * kBK, m0, &full[s]);
+          tma_load_2d_pair(b_tile, &map_b, kb * kBK, w_row, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {   // MMA issuer of the pair
+      constexpr uint32_t idesc = umma_instr_desc(2 * kBM, BN);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++local) {
+        const int acc = local & 1;
+        ok = mbar_wait(&accum_empty[acc], ((local >> 1) & 1) ^ 1, abort_flag);   // both epilogues have drained this accumulator
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          ok = mbar_wait(&full[s], phase, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_addr = smem_u32(tiles + s * Shape::kStageBytes);
+          const uint32_t b_addr = a_addr + kBM * kBK * 2;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            umma_bf16_pair(tmem_acc, umma_smem_desc(a_addr + k * kUmmaK * 2), umma_smem_desc(b_addr + k * kUmmaK * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[s]);   // the stage is free in both CTAs once these MMAs have read it
+        }
+        if (ok) umma_commit_pair(&accum_full[acc]);
+      }
+    }
+  }
+  if (warp >= 2) {   // epilogue: warp w reads tensor-memory lanes 32 * (w % 4) ... + 31 of this CTA's 128 rows
+    const int sub = warp & 3;
+    int local = 0;
+    for (int tile = pair; tile < num_tiles; tile += pairs, ++local) {
+      const int acc = local & 1;
+      const int m0 = (tile % m_blocks) * 2 * kBM + rank * kBM, n0 = (tile / m_blocks) * kTileN;
+      if (!mbar_wait(&accum_full[acc], (local >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
+      const int row = m0 + sub * 32 + lane;
+      if (EPI == 2) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t gate[16], up[16];
+          tmem_load_16(tmem_acc + c * 16, gate);
+          tmem_load_16(tmem_acc + BN / 2 + c * 16, up);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          const int col = n0 + c * 16;
+          if (row < M && col < N) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
+            float act[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              // gate and up are rounded to bfloat16 first, as when the product is stored and read back
+              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[i])));
+              const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[i])));
+              act[i] = (g / (1.0f + expf(-g))) * u;
+            }
+            if (col + 16 <= N && (N % 8) == 0) {
+              uint32_t packed[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 p = __floats2bfloat162_rn(act[2 * i], act[2 * i + 1]);
+                packed[i] = *reinterpret_cast<uint32_t*>(&p);
+              }
+              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(act[i]);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 16; ++c) {
+          uint32_t r[16];
+          tmem_load_16(tmem_acc + c * 16, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          const int col = n0 + c * 16;
+          if (row < M && col < N) {
+            if (EPI == 0) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
+              if (col + 16 <= N && (N % 8) == 0) {
+                uint32_t packed[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                  packed[i] = *reinterpret_cast<uint32_t*>(&p);
+                }
+                *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+              } else {
+                for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+              }
+            } else {
+              float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
+              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __uint_as_float(r[i]);
+            }
+          }
+        }
+      }
+      // this warp is done with the accumulator: tell the pair's MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) arrive_at_leader(&accum_empty[acc]);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  }
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(error_flag, 1);
+    // copies that were issued may still be landing in this CTA's shared memory: give them time before it is released
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols));
+  }
+}
+
+template <int BN, int EPI>
+static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  // each CTA fetches boxes of 128 rows of x and BN / 2 rows of w (gated: w has 2 N rows, one CTA takes gate rows, the other up rows)
+  if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, BN / 2)) return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairShape<BN>::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  constexpr int kTileN = EPI == 2 ? BN / 2 : BN;
+  const int num_tiles = ((N + kTileN - 1) / kTileN) * ((M + 2 * kBM - 1) / (2 * kBM));
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  const int pairs = num_tiles < sm_count / 2 ? num_tiles : sm_count / 2;
+  gemm_pair_kernel<BN, EPI><<<dim3(2 * pairs), kGemmThreads, PairShape<BN>::kSmemBytes, stream>>>(map_a, map_b, out, M, N, K, error_flag);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+// As tlie_gemm_tcgen05 (gemm_tcgen05.cu), on pairs of SMs; tile_n is 128, 160, 192 or 256.
+TLIE_EXPORT int tlie_gemm_tcgen05_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int tile_n, int* error_flag,
+                                       cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || error_flag == nullptr || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
+  if (out_f32 == 2) return launch_pair<256, 2>(x, w, out, M, N, K, error_flag, stream);   // gated: N = rows of one half of w
+  if (tile_n == 256) return out_f32 ? launch_pair<256, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<256, 0>(x, w, out, M, N, K, error_flag, stream);
+  if (tile_n == 192) return out_f32 ? launch_pair<192, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<192, 0>(x, w, out, M, N, K, error_flag, stream);
+  if (tile_n == 160) return out_f32 ? launch_pair<160, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<160, 0>(x, w, out, M, N, K, error_flag, stream);
+  if (tile_n == 128) return out_f32 ? launch_pair<128, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<128, 0>(x, w, out, M, N, K, error_flag, stream);
+  return (int)cudaErrorInvalidValue;
+}

@@ -24,7 +24,7 @@ def build_all() -> list:
     built += [build_library(f"tlie_attn_prefill_d{d}", ["attention_prefill.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
     built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
     built.append(build_library("tlie_gemv_fused", ["gemv_fused.cu"]))
-    built.append(build_library("tlie_gemm_tcgen05", ["gemm_tcgen05.cu"]))
+    built.append(build_library("tlie_gemm_tcgen05", TCGEN05_SOURCES))
     built.append(build_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"]))
     return built
 
@@ -116,8 +116,11 @@ TCGEN05_MIN_ROWS = 128     # from this many rows on the engine's own tcgen05 ker
 use_tcgen05 = True
 
 
+TCGEN05_SOURCES = ["gemm_tcgen05.cu", "gemm_tcgen05_pair.cu"]
+
+
 def tcgen05_library():
-    return load_library("tlie_gemm_tcgen05", ["gemm_tcgen05.cu"])
+    return load_library("tlie_gemm_tcgen05", TCGEN05_SOURCES)
 
 
 def tcgen05_error_flag(device: torch.device) -> torch.Tensor:
@@ -130,39 +133,57 @@ def tcgen05_error_flag(device: torch.device) -> torch.Tensor:
 GEMM_TILE_WIDTHS = (256, 192, 160, 128)
 
 
-def gemm_tile_width(M: int, N: int) -> int:
-    """The tile width whose waves of persistent CTAs cost least: waves x width, the wider tile on a tie (it reads x less often)."""
-    sms = SM_COUNT
-    row_blocks = -(-M // 128)
-    return min(GEMM_TILE_WIDTHS, key=lambda width: (-(-(row_blocks * -(-N // width)) // sms) * width, -width))
+# Tiles of 256 rows on pairs of SMs (tcgen05 cta_group::2, gemm_tcgen05_pair.cu) bring a third less from L2 per flop.  Measured at
+# 2,048 rows they are level with the one-SM tiles for the plain products (the wider tile fits the waves of small products
+# worse) and a little ahead for the gated one, which is what they are used for.
+PAIR_MIN_ROWS = 1024
+use_sm_pairs = True
 
 
-def gemm_tcgen05(x, weight, out, tile_n: int | None = None) -> None:
-    """out[M, N] = x[M, K] . weight[N, K]^T on the 5th-generation tensor cores; bfloat16 in, bfloat16 or 32-bit out."""
+def gemm_tile_width(M: int, N: int, pair: bool = False) -> int:
+    """The tile width whose waves of persistent CTAs (or pairs of them) cost least: waves x width, the wider tile on a tie
+    (it reads x less often)."""
+    workers = SM_COUNT // 2 if pair else SM_COUNT
+    row_blocks = -(-M // (256 if pair else 128))
+    return min(GEMM_TILE_WIDTHS, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * width, -width))
+
+
+def gemm_tcgen05(x, weight, out, tile_n: int | None = None, pair: bool | None = None) -> None:
+    """out[M, N] = x[M, K] . weight[N, K]^T on the 5th-generation tensor cores; bfloat16 in, bfloat16 or 32-bit out.
+
+    ``pair``: 256-row tiles on pairs of SMs (each CTA loads half of the weight rows of a tile)."""
     ops = _ops()
     M, K = x.shape
     N = weight.shape[0]
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or K % 8 != 0 or not x.is_contiguous():
         raise KernelError("gemm_tcgen05 takes contiguous bfloat16 operands with K % 8 == 0", code="invalid_shape")
+    if pair is None:
+        pair = False
     if tile_n is None:
-        tile_n = gemm_tile_width(M, N)
+        tile_n = gemm_tile_width(M, N, pair)
+    library = tcgen05_library()
+    entry = library.tlie_gemm_tcgen05_pair if pair else library.tlie_gemm_tcgen05
     ops._check(
-        tcgen05_library().tlie_gemm_tcgen05(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(1 if out.dtype == torch.float32 else 0),
-                                            c_int(tile_n), ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
+        entry(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(1 if out.dtype == torch.float32 else 0),
+              c_int(tile_n), ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
         "gemm_tcgen05",
     )
 
 
-def gemm_tcgen05_gated(x, weight, out) -> None:
+def gemm_tcgen05_gated(x, weight, out, pair: bool | None = None) -> None:
     """out[M, I] = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows] ([2 I, K]), one kernel."""
     ops = _ops()
     M, K = x.shape
     inter = weight.shape[0] // 2
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or K % 8 != 0 or not x.is_contiguous() or out.shape != (M, inter):
         raise KernelError("gemm_tcgen05_gated takes contiguous bfloat16 operands with K % 8 == 0 and out [M, rows / 2]", code="invalid_shape")
+    if pair is None:
+        pair = use_sm_pairs and M >= PAIR_MIN_ROWS
+    library = tcgen05_library()
+    entry = library.tlie_gemm_tcgen05_pair if pair else library.tlie_gemm_tcgen05
     ops._check(
-        tcgen05_library().tlie_gemm_tcgen05(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(inter), c_int(K), c_int(2), c_int(256),
-                                            ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
+        entry(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(inter), c_int(K), c_int(2), c_int(256),
+              ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
         "gemm_tcgen05_gated",
     )
 
