@@ -142,3 +142,17 @@ def test_steps_launched_ahead_keep_the_engine_consistent(model_folders):
     assert engine.requests[ids[1]].generated == want[1][: len(engine.requests[ids[1]].generated)]
     engine.runner.cache.check()
     assert engine.runner.cache.free_pages() == engine.runner.cache.total_pages()
+
+
+def test_batches_that_pass_through_a_size_are_not_captured(model_folders):
+    """Requests finishing one per step: the sizes the batch only passes through run kernel by kernel, the lasting one as a graph."""
+    config, weights = plain_llama.load_model(model_folders["b"])
+    prompts = _prompts(config["vocab_size"], [9, 9, 9, 9], seed=8)
+    params = [SamplingParams(max_tokens=n) for n in (12, 13, 14, 30)]
+    engine = _engine(model_folders["b"], use_cuda_graphs=True)
+    got = [r.generated_tokens for r in engine.generate(prompts, params)]
+    assert got == [plain_llama.generate_greedy(config, weights, p, q.max_tokens) for p, q in zip(prompts, params)]
+    sessions = engine._sessions
+    assert sessions[4].graph is not None and sessions[1].graph is not None   # eleven and sixteen steps
+    assert sessions[3].graph is None and sessions[2].graph is None           # one step each
+    engine.runner.cache.check()

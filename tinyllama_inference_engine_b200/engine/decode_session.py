@@ -17,6 +17,11 @@ from .. import ops
 from ..errors import BatchError
 from .batch import StepContext
 
+# A session runs its first steps kernel by kernel and is captured as a graph only when it is still in use after them:
+# a batch that changes with every step (requests finishing one after another) would otherwise pay a capture, which costs
+# as much as ten steps, for every size it passes through.
+EAGER_STEPS_BEFORE_CAPTURE = 2
+
 
 class DecodeSession:
     def __init__(self, runner, count: int, use_graph: bool = True):
@@ -61,6 +66,7 @@ class DecodeSession:
         self.use_graph = use_graph
         self._fresh = True
         self._loaded = False
+        self._eager_steps = 0
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
         self.kernels_per_step = 0          # kernels of this engine in one step (counted while warming up)
@@ -146,25 +152,31 @@ class DecodeSession:
                 o = self._offsets
                 self._device[o[8] :].copy_(self._host[o[8] :], non_blocking=True)
         self._loaded = False
-        if not self.use_graph:
-            self._body()
-        elif self.graph is None:
-            from ..ops import fast
+        if not self.use_graph or self.graph is None and self._eager_steps < EAGER_STEPS_BEFORE_CAPTURE:
+            if self._eager_steps == 0:
+                from ..ops import fast
 
-            before, library_before = ops.launch_count, fast.library_gemm_calls
+                before, library_before = ops.launch_count, fast.library_gemm_calls
+                self._body()
+                self.kernels_per_step = ops.launch_count - before
+                self.library_calls_per_step = fast.library_gemm_calls - library_before
+            else:
+                self._body()
+            self._eager_steps += 1
+        elif self.graph is None:
+            # The steps run so far have made the workspaces and library handles, so the step can be captured as it is.
+            # capture_begin / capture_end directly: the context manager of torch.cuda.graph also collects garbage and
+            # empties the allocator's cache first, which can take longer than a hundred steps.
+            self.graph = torch.cuda.CUDAGraph()
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
-                self._body()  # warm-up outside capture: workspaces, library handles
-                # the warm-up ran the step; put the metadata back before capturing the same step
-                self._device.copy_(self._host, non_blocking=True)
-                self.counters -= 1
+                self.graph.capture_begin()
+                try:
+                    self._body()
+                finally:
+                    self.graph.capture_end()
             torch.cuda.current_stream().wait_stream(stream)
-            self.kernels_per_step = ops.launch_count - before
-            self.library_calls_per_step = fast.library_gemm_calls - library_before
-            self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self._body()
             # capture does not run anything: the step itself is the first replay
             self.graph.replay()
         else:
