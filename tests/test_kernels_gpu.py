@@ -176,6 +176,18 @@ def test_argmax_and_sampling(ops):
     want = torch.empty(6, dtype=torch.int32)
     plain_ops.argmax(logits, want)
     assert torch.equal(out.cpu(), want) and int(want[0]) == 10 and int(want[1]) == 999
+    # rows long enough for several rounds of the 16-byte loads, maxima at a round's edge, at the end, and tied across rounds
+    wide = torch.randn(4, 20000)
+    wide[0, 4096 * 4 - 1] = 30.0
+    wide[1, 19999] = 30.0
+    wide[2, 17001] = wide[2, 4099] = 30.0
+    wide[3, 0] = 30.0
+    out = torch.empty(4, dtype=torch.int32, device="cuda")
+    ops.argmax(wide.cuda(), out)
+    assert out.cpu().tolist() == [4096 * 4 - 1, 19999, 4099, 0]
+    greedy = torch.empty(4, dtype=torch.int32, device="cuda")
+    ops.sample(wide.cuda(), torch.zeros(4).cuda(), torch.ones(4).cuda(), torch.zeros(4, dtype=torch.int64).cuda(), torch.zeros(4, dtype=torch.int64).cuda(), greedy)
+    assert greedy.cpu().tolist() == [4096 * 4 - 1, 19999, 4099, 0]
     assert ops.uniform_from(11, 5) == plain_ops.uniform_from(11, 5) == pytest.approx(ops.core().tlie_uniform_from(11, 5))
     rows = 64
     logits = torch.randn(rows, 131) * 2

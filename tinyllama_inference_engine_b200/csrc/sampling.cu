@@ -16,6 +16,40 @@ namespace tlie {
 
 constexpr int kSampleThreads = 1024;
 
+// A thread's share of a row's maximum and the lowest index that holds it.  Rows that allow it are read 16 bytes at a
+// time, four loads in flight per thread: one block reads a whole row, so its time is the latency of its loads in turn.
+__device__ __forceinline__ void row_max_and_arg(const float* __restrict__ row, int vocab, float& best, int& arg) {
+  auto take = [&](float v, int i) {
+    if (v > best || (v == best && i < arg)) {
+      best = v;
+      arg = i;
+    }
+  };
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int quads = vocab >> 2;
+    constexpr int kInFlight = 4;
+    for (int q0 = threadIdx.x; q0 < quads; q0 += kInFlight * blockDim.x) {
+      float4 v[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int q = q0 + u * blockDim.x;
+        v[u] = q < quads ? row4[q] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = (q0 + u * blockDim.x) * 4;
+        take(v[u].x, i);
+        take(v[u].y, i + 1);
+        take(v[u].z, i + 2);
+        take(v[u].w, i + 3);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) take(row[i], i);
+  }
+}
+
 __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __restrict__ logits, int vocab,
                                                                 int* __restrict__ out) {
   __shared__ float best_value[32];
@@ -23,13 +57,7 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __r
   const float* row = logits + (size_t)blockIdx.x * vocab;
   float value = -INFINITY;
   int index = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (v > value || (v == value && i < index)) {
-      value = v;
-      index = i;
-    }
-  }
+  row_max_and_arg(row, vocab, value, index);
   for (int offset = 16; offset > 0; offset >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, value, offset);
     const int oi = __shfl_xor_sync(0xffffffffu, index, offset);
@@ -82,13 +110,7 @@ __global__ void __launch_bounds__(kSampleThreads)
 
   float local_max = -INFINITY;
   int local_arg = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (v > local_max || (v == local_max && i < local_arg)) {
-      local_max = v;
-      local_arg = i;
-    }
-  }
+  row_max_and_arg(row, vocab, local_max, local_arg);
   const float row_max = block_max(local_max, scratch);
   if (!(temp > 0.0f)) {
     // greedy: lowest id among the maxima
