@@ -88,92 +88,89 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* x
   }
 }
 
-// The end of a 16-row tile: the warps' partial tiles are summed through `red` ([warp][TILES][16][MT * 8 + 1] floats) and
-// stored by the variant's epilogue.  acc[tile][mt] is a warp's m16n8 accumulator (weight rows x activation rows).
+// The end of a tile: the warps' partial tiles are summed through `red` ([warp][16][MT * 8 + 1] floats) and stored by the
+// variant's epilogue.  acc[mt] is a warp's m16n8 accumulator (weight rows x activation rows).  A gated tile holds 8 gate
+// rows in the upper half of the accumulator's rows and the 8 up rows of the same outputs in the lower half.
 template <int MT, int XMODE, int EPI>
-__device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float (&acc)[(EPI == EPI_GATED) ? 2 : 1][MT][4], float* red,
-                                                  const float* row_scale, int n0) {
-  constexpr int TILES = (EPI == EPI_GATED) ? 2 : 1;
+__device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float (&acc)[MT][4], float* red, const float* row_scale, int n0) {
   constexpr int kRedRow = MT * 8 + 1;
+  constexpr int kTileRows = (EPI == EPI_GATED) ? 8 : 16;      // outputs of a tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_rows = (EPI == EPI_GATED) ? a.N / 2 : a.N;
+  float* base = red + (size_t)warp * 16 * kRedRow;
 #pragma unroll
-  for (int tile = 0; tile < TILES; ++tile) {
-    float* base = red + ((size_t)warp * TILES + tile) * 16 * kRedRow;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      base[g * kRedRow + mt * 8 + 2 * t] = acc[tile][mt][0];
-      base[g * kRedRow + mt * 8 + 2 * t + 1] = acc[tile][mt][1];
-      base[(g + 8) * kRedRow + mt * 8 + 2 * t] = acc[tile][mt][2];
-      base[(g + 8) * kRedRow + mt * 8 + 2 * t + 1] = acc[tile][mt][3];
-    }
+  for (int mt = 0; mt < MT; ++mt) {
+    base[g * kRedRow + mt * 8 + 2 * t] = acc[mt][0];
+    base[g * kRedRow + mt * 8 + 2 * t + 1] = acc[mt][1];
+    base[(g + 8) * kRedRow + mt * 8 + 2 * t] = acc[mt][2];
+    base[(g + 8) * kRedRow + mt * 8 + 2 * t + 1] = acc[mt][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < 16 * MT * 8; idx += kGemvWarps * 32) {
-    const int m = idx / 16;
-    const int r = idx - m * 16;
+  for (int idx = threadIdx.x; idx < kTileRows * MT * 8; idx += kGemvWarps * 32) {
+    const int m = idx / kTileRows;
+    const int r = idx - m * kTileRows;
     if (m >= a.M || n0 + r >= n_rows) continue;
-    float sum[TILES];
+    float sum = 0.0f, second = 0.0f;
 #pragma unroll
-    for (int tile = 0; tile < TILES; ++tile) {
-      sum[tile] = 0.0f;
-#pragma unroll
-      for (int wi = 0; wi < kGemvWarps; ++wi) sum[tile] += red[((size_t)wi * TILES + tile) * 16 * kRedRow + r * kRedRow + m];
-      if (XMODE == X_NORM) sum[tile] *= row_scale[m];
+    for (int wi = 0; wi < kGemvWarps; ++wi) {
+      sum += red[(size_t)wi * 16 * kRedRow + r * kRedRow + m];
+      if (EPI == EPI_GATED) second += red[(size_t)wi * 16 * kRedRow + (r + 8) * kRedRow + m];
+    }
+    if (XMODE == X_NORM) {
+      sum *= row_scale[m];
+      second *= row_scale[m];
     }
     const size_t o = (size_t)m * n_rows + n0 + r;
     if (EPI == EPI_STORE_BF16) {
-      reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(sum[0]);
+      reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(sum);
     } else if (EPI == EPI_STORE_F32) {
-      reinterpret_cast<float*>(a.out)[o] = sum[0];
+      reinterpret_cast<float*>(a.out)[o] = sum;
     } else if (EPI == EPI_ACCUM) {
-      reinterpret_cast<float*>(a.out)[o] = __ldcg(reinterpret_cast<const float*>(a.out) + o) + sum[0];
+      reinterpret_cast<float*>(a.out)[o] = __ldcg(reinterpret_cast<const float*>(a.out) + o) + sum;
     } else {
       // gate and up are rounded to bfloat16 first, as when the product is stored and read back
-      const float gate = __bfloat162float(__float2bfloat16_rn(sum[0]));
-      const float up = __bfloat162float(__float2bfloat16_rn(sum[TILES - 1]));
+      const float gate = __bfloat162float(__float2bfloat16_rn(sum));
+      const float up = __bfloat162float(__float2bfloat16_rn(second));
       reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
     }
   }
   __syncthreads();   // red is written again by the next tile
 }
 
-// TILES: 1 (16 weight rows) or 2 (GATED: 16 gate rows + the 16 up rows N/2 below).
+// A tile is 16 weight rows (the A operand of the MMA), or for GATED 8 gate rows and the 8 up rows N / 2 below them: the
+// outputs of a gated tile are 8, so that the tiles of the widest product can be dealt evenly to the CTAs.  (Tiles of 8 rows
+// with the other half of the MMA empty were tried for the down projection, 128 tiles of 16 x 5632: 11.1 us against 7.9 us.)
 template <int MT, int XMODE, int EPI>
 struct GemvPhase {
-  static constexpr int TILES = (EPI == EPI_GATED) ? 2 : 1;
-  static constexpr int UNROLL = (EPI == EPI_GATED || (XMODE == X_DIRECT && MT > 1)) ? 4 : 8;
+  static constexpr int kTileRows = (EPI == EPI_GATED) ? 8 : 16;
+  static constexpr int UNROLL = (XMODE == X_DIRECT && MT > 1) ? 4 : 8;
   static constexpr int kRedRow = MT * 8 + 1;
-  uint4 wreg[UNROLL][TILES][2];
+  uint4 wreg[UNROLL][2];
 
   // Shared memory this variant needs: x as bfloat16 (unless read directly) and the warps' partial tiles.
   static __host__ __device__ size_t smem_bytes(int x_stride) {
-    return (XMODE == X_DIRECT ? 0 : (size_t)MT * 8 * x_stride * 2) + (size_t)kGemvWarps * TILES * 16 * kRedRow * sizeof(float);
+    return (XMODE == X_DIRECT ? 0 : (size_t)MT * 8 * x_stride * 2) + (size_t)kGemvWarps * 16 * kRedRow * sizeof(float);
   }
   static __device__ __forceinline__ float* red_of(unsigned char* smem, int x_stride) {
     return reinterpret_cast<float*>(smem + (XMODE == X_DIRECT ? 0 : (size_t)MT * 8 * x_stride * 2));
   }
 
-  // this warp's weights of k blocks kb0, kb0 + 8, ... of the 16-row tile at n0
+  // this warp's weights of k blocks kb0, kb0 + 8, ... of the tile whose first output is n0
   __device__ __forceinline__ void issue(const GemvArgs& a, int n0, int kb0) {
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int K = a.K;
     const int n_rows = (EPI == EPI_GATED) ? a.N / 2 : a.N;
-
+    // MMA rows g and g + 8: two weight rows 8 apart, or the gate row and the up row of output n0 + g
+    const __nv_bfloat16* r0 = a.w + (size_t)min(n0 + g, n_rows - 1) * K + t * 8;
+    const __nv_bfloat16* r1 = a.w + (size_t)(EPI == EPI_GATED ? n_rows + min(n0 + g, n_rows - 1) : min(n0 + g + 8, n_rows - 1)) * K + t * 8;
 #pragma unroll
-    for (int tile = 0; tile < TILES; ++tile) {
-      const int base = tile * n_rows;
-      const __nv_bfloat16* r0 = a.w + (size_t)(base + min(n0 + g, n_rows - 1)) * K + t * 8;
-      const __nv_bfloat16* r1 = a.w + (size_t)(base + min(n0 + g + 8, n_rows - 1)) * K + t * 8;
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int kb = kb0 + u * kGemvWarps;
-        const bool valid = kb * 32 + t * 8 < K;
-        wreg[u][tile][0] = valid ? load_stream_16(r0 + (size_t)kb * 32) : make_uint4(0, 0, 0, 0);
-        wreg[u][tile][1] = valid ? load_stream_16(r1 + (size_t)kb * 32) : make_uint4(0, 0, 0, 0);
-      }
+    for (int u = 0; u < UNROLL; ++u) {
+      const int kb = kb0 + u * kGemvWarps;
+      const bool valid = kb * 32 + t * 8 < K;
+      wreg[u][0] = valid ? load_stream_16(r0 + (size_t)kb * 32) : make_uint4(0, 0, 0, 0);
+      wreg[u][1] = valid ? load_stream_16(r1 + (size_t)kb * 32) : make_uint4(0, 0, 0, 0);
     }
   }
 
@@ -186,59 +183,56 @@ struct GemvPhase {
     const int g = lane >> 2, t = lane & 3;
     const int K = a.K;
     const int n_rows = (EPI == EPI_GATED) ? a.N / 2 : a.N;      // rows of one half
-    const int tiles = (n_rows + 15) / 16;
+    const int tiles = (n_rows + kTileRows - 1) / kTileRows;
     const int blocks = (K + 31) / 32;
-  // --- tiles of 16 weight rows: blockIdx.x, + gridDim.x, ... -----------------------------------------
-  for (int tile_index = first_tile; tile_index < tiles; tile_index += tile_step) {
-    const int n0 = tile_index * 16;
-    float acc[TILES][MT][4];
+    bool issued = first_round_issued;
+    for (int tile_index = first_tile; tile_index < tiles; tile_index += tile_step) {
+      const int n0 = tile_index * kTileRows;
+      float acc[MT][4];
 #pragma unroll
-    for (int tile = 0; tile < TILES; ++tile)
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) acc[tile][mt][0] = acc[tile][mt][1] = acc[tile][mt][2] = acc[tile][mt][3] = 0.0f;
+      for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
 
-    for (int kb0 = warp; kb0 < blocks; kb0 += kGemvWarps * UNROLL) {
-      if (kb0 != warp || tile_index != first_tile || !first_round_issued) issue(a, n0, kb0);
-      uint4 xdirect[XMODE == X_DIRECT ? UNROLL : 1][MT];
-      if (XMODE == X_DIRECT) {
-        const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
+      for (int kb0 = warp; kb0 < blocks; kb0 += kGemvWarps * UNROLL) {
+        if (kb0 != warp || !issued) issue(a, n0, kb0);
+        uint4 xdirect[XMODE == X_DIRECT ? UNROLL : 1][MT];
+        if (XMODE == X_DIRECT) {
+          const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const int k = (kb0 + u * kGemvWarps) * 32 + t * 8;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const int m = mt * 8 + g;
+              xdirect[u][mt] = (k < K && m < a.M) ? __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + k)) : make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-          const int k = (kb0 + u * kGemvWarps) * 32 + t * 8;
+          const int kb = kb0 + u * kGemvWarps;
+          if (kb >= blocks) continue;          // the same for every lane: mma.sync needs the whole warp
+          const int k = kb * 32 + t * 8;
+          const unsigned lo[4] = {wreg[u][0].x, wreg[u][1].x, wreg[u][0].y, wreg[u][1].y};
+          const unsigned hi[4] = {wreg[u][0].z, wreg[u][1].z, wreg[u][0].w, wreg[u][1].w};
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            const int m = mt * 8 + g;
-            xdirect[u][mt] = (k < K && m < a.M) ? __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + k)) : make_uint4(0, 0, 0, 0);
+            // lanes past K (a last block of fewer than 32) contribute zeros: their weights are zero too
+            uint4 xv = make_uint4(0, 0, 0, 0);
+            if (XMODE == X_DIRECT) {
+              xv = xdirect[u][mt];
+            } else if (k < K) {
+              xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mt * 8 + g) * a.x_stride + k);
+            }
+            mma_bf16(acc[mt], lo, xv.x, xv.y);
+            mma_bf16(acc[mt], hi, xv.z, xv.w);
           }
         }
       }
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int kb = kb0 + u * kGemvWarps;
-        if (kb >= blocks) continue;          // the same for every lane: mma.sync needs the whole warp
-        const int k = kb * 32 + t * 8;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          // lanes past K (a last block of fewer than 32) contribute zeros: their weights are zero too
-          uint4 xv = make_uint4(0, 0, 0, 0);
-          if (XMODE == X_DIRECT) {
-            xv = xdirect[u][mt];
-          } else if (k < K) {
-            xv = *reinterpret_cast<const uint4*>(xs + (size_t)(mt * 8 + g) * a.x_stride + k);
-          }
-#pragma unroll
-          for (int tile = 0; tile < TILES; ++tile) {
-            const unsigned lo[4] = {wreg[u][tile][0].x, wreg[u][tile][1].x, wreg[u][tile][0].y, wreg[u][tile][1].y};
-            const unsigned hi[4] = {wreg[u][tile][0].z, wreg[u][tile][1].z, wreg[u][tile][0].w, wreg[u][tile][1].w};
-            mma_bf16(acc[tile][mt], lo, xv.x, xv.y);
-            mma_bf16(acc[tile][mt], hi, xv.z, xv.w);
-          }
-        }
-      }
+      // the weights of the next tile's first round go out before this tile is summed and stored
+      issued = tile_index + tile_step < tiles;
+      if (issued) issue(a, (tile_index + tile_step) * kTileRows, warp);
+      gemv_reduce_store<MT, XMODE, EPI>(a, acc, red, row_scale, n0);
     }
-
-    gemv_reduce_store<MT, XMODE, EPI>(a, acc, red, row_scale, n0);
-  }
   }
 };
 

@@ -17,8 +17,9 @@
 //   output  STORE    bfloat16 or 32-bit [M, N];
 //           ACCUM    residual[m, n] += result in 32-bit (each element owned by one thread, so the
 //                    sum is deterministic): the reference's add kernel (src/cuda/kernels.cu:208-215);
-//           GATED    the CTA computes rows n of the gate half and of the up half of w and stores
-//                    silu(gate) * up (src/operators.cpp:148-164) as bfloat16 [M, N/2].
+//           GATED    a tile is 8 rows of the gate half of w and the 8 rows of the up half for the same outputs (the
+//                    two halves of the MMA's 16 rows); the CTA stores silu(gate) * up (src/operators.cpp:148-164)
+//                    as bfloat16 [M, N/2].  Tiles of 8 outputs deal the widest product evenly to the CTAs.
 // Mechanics: 16 weight rows are the A operand of mma.sync m16n8k16 and 8 rows of x the B operand
 // (M = 8 wastes nothing); the contraction index is permuted so that a thread fetches 8 consecutive
 // k of a weight row with one 16-byte load feeding two MMAs; the 8 warps of a CTA split K, keep
@@ -35,9 +36,9 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_fused_kernel(const GemvA
   __shared__ float row_scale[MT * 8];
   GemvPhase<MT, XMODE, EPI> phase;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [MT * 8][x_stride]
-  float* red = phase.red_of(smem_raw, a.x_stride);                  // [warps][TILES][16][MT * 8 + 1]
+  float* red = phase.red_of(smem_raw, a.x_stride);                  // [warps][16][MT * 8 + 1]
   // weights of the first round, before anything that depends on the previous kernel
-  phase.issue(a, blockIdx.x * 16, threadIdx.x >> 5);
+  phase.issue(a, blockIdx.x * phase.kTileRows, threadIdx.x >> 5);
   grid_launch_dependents();
   grid_dependency_wait();
   phase.stage_x(a, xs, row_scale);
@@ -57,12 +58,16 @@ static int launch_one(const GemvArgs& a, int grid, cudaStream_t stream) {
   return (int)launch_pdl(gemv_fused_kernel<MT, XMODE, EPI>, dim3(grid), dim3(kGemvWarps * 32), smem, stream, a);
 }
 
+constexpr int kGemvCtasPerSm = 2;   // how many CTAs of a product an SM is dealt at most (measured: 1 and 3 are slower for the wide products)
+
 template <int XMODE, int EPI>
 static int launch_rows(const GemvArgs& a, cudaStream_t stream) {
   const int n_rows = (EPI == EPI_GATED) ? a.N / 2 : a.N;
-  const int tiles = (n_rows + 15) / 16;
-  // x is staged once per CTA, so a CTA takes several tiles when there are more than two CTAs per SM; equal shares
-  const int per_cta = (tiles + 2 * 148 - 1) / (2 * 148);
+  const int tile_rows = (EPI == EPI_GATED) ? 8 : 16;
+  const int tiles = (n_rows + tile_rows - 1) / tile_rows;
+  // x is staged once per CTA, so a CTA takes several tiles when there are more than `slots` of them; equal shares
+  const int slots = kGemvCtasPerSm * 148;
+  const int per_cta = (tiles + slots - 1) / slots;
   const int grid = (tiles + per_cta - 1) / per_cta;
   if (XMODE == X_PLAIN && per_cta == 1) {   // every element of x is used once per CTA: no point in staging it
     if (a.M <= 8) return launch_one<1, X_DIRECT, EPI>(a, grid, stream);

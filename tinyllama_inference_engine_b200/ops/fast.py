@@ -72,7 +72,7 @@ def gemv_fits(rows: int, K: int, norm: bool, gated: bool = False) -> bool:
     padded_rows = 8 if rows <= 8 else 16
     stride = K + ((32 - K % 64) + 64) % 64
     stride += 64 if stride == K else 0
-    need = padded_rows * stride * 2 + 8 * (2 if gated else 1) * 16 * (padded_rows + 1) * 4
+    need = padded_rows * stride * 2 + 8 * 16 * (padded_rows + 1) * 4
     return need <= 200 * 1024
 
 
