@@ -286,10 +286,10 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
     unsigned pa[kTileKeys / 16][4];
 #pragma unroll
     for (int j = 0; j < kTileKeys / 8; ++j) {
-      const float p0 = exp2f(s_frag[j][0] - row_max[0]);
-      const float p1 = exp2f(s_frag[j][1] - row_max[0]);
-      const float p2 = exp2f(s_frag[j][2] - row_max[1]);
-      const float p3 = exp2f(s_frag[j][3] - row_max[1]);
+      const float p0 = exp2_approx(s_frag[j][0] - row_max[0]);
+      const float p1 = exp2_approx(s_frag[j][1] - row_max[0]);
+      const float p2 = exp2_approx(s_frag[j][2] - row_max[1]);
+      const float p3 = exp2_approx(s_frag[j][3] - row_max[1]);
       row_sum[0] += p0 + p1;
       row_sum[1] += p2 + p3;
       pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);

@@ -198,10 +198,10 @@ __global__ void __launch_bounds__(kWarps * 32, kD <= 64 ? (kRows == 64 ? 3 : 2) 
       unsigned pa[kKeys / 16][4];
 #pragma unroll
       for (int j = 0; j < kKeys / 8; ++j) {
-        const float p0 = exp2f(fmaf(s_frag[j][0], sl2, -base[0]));
-        const float p1 = exp2f(fmaf(s_frag[j][1], sl2, -base[0]));
-        const float p2 = exp2f(fmaf(s_frag[j][2], sl2, -base[1]));
-        const float p3 = exp2f(fmaf(s_frag[j][3], sl2, -base[1]));
+        const float p0 = exp2_approx(fmaf(s_frag[j][0], sl2, -base[0]));
+        const float p1 = exp2_approx(fmaf(s_frag[j][1], sl2, -base[0]));
+        const float p2 = exp2_approx(fmaf(s_frag[j][2], sl2, -base[1]));
+        const float p3 = exp2_approx(fmaf(s_frag[j][3], sl2, -base[1]));
         row_sum[0] += p0 + p1;
         row_sum[1] += p2 + p3;
         pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);

@@ -324,8 +324,8 @@ __global__ void __launch_bounds__(kThreadsTC)
         float sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < kKeysTC / 2; ++i) {
-          const float p0 = exp2f(fmaf(sc[2 * i], sl2, -base));
-          const float p1 = exp2f(fmaf(sc[2 * i + 1], sl2, -base));
+          const float p0 = exp2_approx(fmaf(sc[2 * i], sl2, -base));
+          const float p1 = exp2_approx(fmaf(sc[2 * i + 1], sl2, -base));
           sum += p0 + p1;
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           packed[i] = *reinterpret_cast<uint32_t*>(&h);
