@@ -1,7 +1,10 @@
-"""Generality of the parts: a toy mixer with per-request state of its own, defined here, is registered,
-built into a model beside attention layers, and stepped, without touching the framework's files.
+"""Generality of the parts: a toy mixer with per-request state of its own, a toy feed-forward that routes every token to
+one of two experts, and a toy position encoding that is no rotation, all defined here, are registered, built into a model
+beside attention layers, and stepped, without touching the framework's files.
 
-The toy is no model of anyone's: s_t = decay * s_{t-1} + W_in x_t, y_t = W_out s_t, one state vector per request.
+The toys are no model of anyone's.  Mixer: s_t = decay * s_{t-1} + W_in x_t, y_t = W_out s_t, one state vector per
+request.  Feed-forward: y_t = W_e x_t with e = argmax(R x_t), the router in 32-bit.  Position: q and k are multiplied by
+1 + 0.1 sin(0.3 position + dim).
 """
 from __future__ import annotations
 
@@ -16,7 +19,8 @@ from tinyllama_inference_engine_b200 import EngineConfig
 from tinyllama_inference_engine_b200.config import Architecture, register_architecture, unregister_architecture
 from tinyllama_inference_engine_b200.engine.batch import StepEntry
 from tinyllama_inference_engine_b200.engine.runner import ModelRunner
-from tinyllama_inference_engine_b200.parts import CacheNeed, LayerSpec, Mixer, ModelSpec, OrderEntry, PartSpec, TensorSpec, register_part, unregister_part
+from tinyllama_inference_engine_b200.parts import (CacheNeed, FeedForward, LayerSpec, Mixer, ModelSpec, OrderEntry, PartSpec, PositionEncoding, TensorSpec,
+                                                   register_part, unregister_part)
 from tinyllama_inference_engine_b200.weights import write_random_model
 
 
@@ -50,6 +54,30 @@ class DecayMixer(Mixer):
         return out
 
 
+class RoutedFeedForward(FeedForward):
+    @classmethod
+    def tensor_specs(cls, spec, prefix):
+        h = spec["hidden_size"]
+        return [TensorSpec(f"{prefix}.router.weight", (2, h), std=1.0)] + [TensorSpec(f"{prefix}.expert{e}.weight", (h, h), std=0.1) for e in range(2)]
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.router = weights.get(f"{prefix}.router.weight", torch.float32)
+        self.experts = torch.stack([weights.get(f"{prefix}.expert{e}.weight", torch.float32) for e in range(2)])
+
+    def forward(self, x, ctx):
+        choice = (x.float() @ self.router.T).argmax(1)                      # router logits in 32-bit
+        return torch.einsum("thk,tk->th", self.experts[choice], x.float()).to(x.dtype)
+
+
+class WavePosition(PositionEncoding):
+    def apply(self, qkv, ctx, q_heads, kv_heads, head_dim):                # rotary_table() stays None: no rotation kernel applies
+        dims = torch.arange(head_dim, device=qkv.device, dtype=torch.float32)
+        factor = 1 + 0.1 * torch.sin(0.3 * ctx.positions.float()[:, None] + dims[None, :])
+        heads = qkv.view(qkv.shape[0], q_heads + 2 * kv_heads, head_dim)
+        heads[:, : q_heads + kv_heads] = (heads[:, : q_heads + kv_heads].float() * factor[:, None, :]).to(qkv.dtype)
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     hidden_size: int = 48
@@ -75,14 +103,19 @@ def build_toy_spec(c: ToyConfig) -> ModelSpec:
                                        "position": PartSpec("rotary", {"rotary_dim": 16, "theta": 100.0})})
     windowed = PartSpec("attention", {**attention.params, "window": 20})
     decay = PartSpec("toy_decay", {"hidden_size": c.hidden_size, "state_size": c.state_size, "decay": c.decay})
+    waved = PartSpec("attention", {**attention.params, "num_heads": 2, "num_kv_heads": 2, "position": PartSpec("toy_wave", {})})
+    routed = PartSpec("toy_routed", {"hidden_size": c.hidden_size})
 
-    def block(mixer):
+    def block(mixer, feed_forward=ff):
         return PartSpec("pre_norm_residual", {"mixer_norm": norm, "mixer_norm_name": "n1", "mixer": mixer, "mixer_name": "mix",
-                                              "feed_forward_norm": norm, "feed_forward_norm_name": "n2", "feed_forward": ff, "feed_forward_name": "ff"})
+                                              "feed_forward_norm": norm, "feed_forward_norm_name": "n2", "feed_forward": feed_forward, "feed_forward_name": "ff"})
 
-    layers = (LayerSpec("toy.l0", block(attention)), LayerSpec("toy.l1", block(decay)), LayerSpec("toy.l2", block(windowed)))
-    # layer 1 runs twice (two cache streams of its own); the last run of layer 0 reads the keys its first run cached
-    order = (OrderEntry(0, cache=0), OrderEntry(1, cache=1), OrderEntry(2, cache=2), OrderEntry(1, cache=3), OrderEntry(0, cache=0, writes_cache=False))
+    layers = (LayerSpec("toy.l0", block(attention)), LayerSpec("toy.l1", block(decay)), LayerSpec("toy.l2", block(windowed)),
+              LayerSpec("toy.l3", block(waved, routed)))
+    # layer 1 runs twice (two cache streams of its own); the last run of layer 0 reads the keys its first run cached;
+    # layer 3 has the toy position encoding and the routed feed-forward
+    order = (OrderEntry(0, cache=0), OrderEntry(1, cache=1), OrderEntry(2, cache=2), OrderEntry(1, cache=3), OrderEntry(3, cache=4),
+             OrderEntry(0, cache=0, writes_cache=False))
     return ModelSpec("ToyDecayForCausalLM", c.hidden_size, c.vocab_size, c.max_position_embeddings,
                      PartSpec("token_embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size, "name": "toy.embed"}),
                      layers, order, PartSpec("rmsnorm", {"size": c.hidden_size, "eps": 1e-5, "name": "toy.norm"}),
@@ -92,10 +125,14 @@ def build_toy_spec(c: ToyConfig) -> ModelSpec:
 @pytest.fixture()
 def toy_folder(tmp_path):
     register_part("mixer", "toy_decay", DecayMixer, replace=True)
+    register_part("feed_forward", "toy_routed", RoutedFeedForward, replace=True)
+    register_part("position", "toy_wave", WavePosition, replace=True)
     register_architecture(Architecture("ToyDecayForCausalLM", ToyConfig, build_toy_spec), replace=True)
     yield write_random_model(tmp_path / "toy", ToyConfig(), seed=8, storage_dtype="bfloat16")
     unregister_architecture("ToyDecayForCausalLM")
     unregister_part("mixer", "toy_decay")
+    unregister_part("feed_forward", "toy_routed")
+    unregister_part("position", "toy_wave")
 
 
 def _check_toy(folder, device, dtype, fraction):
@@ -104,7 +141,8 @@ def _check_toy(folder, device, dtype, fraction):
     requests = {name: [int(t) for t in rng.integers(0, 97, size=n)] for name, n in (("p", 61), ("q", 45), ("r", 30))}
     whole = ModelRunner(folder, config)
     groups = whole.cache.page_groups
-    assert [(g.need.window, g.streams) for g in groups] == [(0, [0]), (20, [2])] and [g.streams for g in whole.cache.state_groups] == [[1, 3]]
+    assert [(g.need.window, g.need.kv_heads, g.streams) for g in groups] == [(0, 1, [0]), (20, 1, [2]), (0, 2, [4])]
+    assert [g.streams for g in whole.cache.state_groups] == [[1, 3]]
     full = {}
     for name, tokens in requests.items():
         full[name] = whole.step([StepEntry(name, tokens, list(range(len(tokens))))]).cpu()
