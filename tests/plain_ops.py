@@ -52,11 +52,6 @@ def linear(x, weight, out) -> None:
     _store(out, x.float() @ weight.float().T)
 
 
-def gated_linear(gate_up, weight, out, activated) -> None:
-    silu_mul(gate_up, activated)
-    linear(activated, weight, out)
-
-
 def fused_rows_limit(dtype, device) -> int:
     return 0
 
@@ -134,7 +129,7 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
         out[r] = plain_llama.sample_top_p(logits[r].float(), float(temperature[r]), float(top_p[r]), u)
 
 
-_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "gather_rows", "to_float", "linear", "gated_linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample"]
+_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "gather_rows", "to_float", "linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample"]
 
 
 def install(monkeypatch) -> None:

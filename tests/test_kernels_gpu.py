@@ -289,33 +289,6 @@ def test_prefill_attention_flash(ops, q_heads, kv_heads, head_dim, page_size, wi
     assert float(error.max()) <= 1.6e-2 * 2, (int(error.argmax()), error.max())
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
-@pytest.mark.parametrize("N,K", [(131, 80), (2560, 2048), (2048, 5632), (1000, 200), (16, 4096)])
-def test_gemm_skinny(ops, M, N, K):
-    """The weight-streaming product against a 32-bit product of the same bfloat16 values, plain and with the fused gate."""
-    from tinyllama_inference_engine_b200.ops import fast
-
-    torch.manual_seed(10)
-    x = torch.randn(M, K).bfloat16()
-    w = (torch.randn(N, K) * 0.05).bfloat16()
-    want = x.float() @ w.float().T
-    for out_dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 1.6e-2)):
-        got = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
-        fast.gemm_skinny(x.cuda(), w.cuda(), got)
-        assert torch.allclose(got.cpu().float(), want, atol=tol * float(want.abs().max()), rtol=0), float((got.cpu().float() - want).abs().max())
-    padded = torch.randn(M, K + 24).bfloat16().cuda()  # rows with a stride larger than K
-    got = torch.empty(M, N, dtype=torch.float32, device="cuda")
-    fast.gemm_skinny(padded[:, :K], w.cuda(), got)
-    assert torch.allclose(got.cpu(), padded[:, :K].cpu().float() @ w.float().T, atol=1e-4 * float(want.abs().max()) + 1e-5)
-    gate_up = (torch.randn(M, 2 * K) * 1.5).bfloat16()
-    act = torch.empty(M, K, dtype=torch.bfloat16)
-    plain_ops.silu_mul(gate_up, act)
-    want = act.float() @ w.float().T
-    got = torch.empty(M, N, dtype=torch.float32, device="cuda")
-    fast.gemm_skinny(gate_up.cuda(), w.cuda(), got, gated=True)
-    assert torch.allclose(got.cpu(), want, atol=1e-3 * float(want.abs().max()) + 1e-5), float((got.cpu() - want).abs().max())
-
-
 @pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(130, 80), (2560, 2048), (2048, 5632), (1000, 200), (352, 176)])
 def test_gemv_fused(ops, M, N, K):

@@ -200,18 +200,6 @@ def linear_gated(x, weight, out) -> None:
         silu_mul(gate_up, out)
 
 
-def gated_linear(gate_up, weight, out, activated) -> None:
-    """out = (silu(gate) * up) . weight^T for rows [gate | up]; ``activated`` is scratch for the unfused route."""
-    if gate_up.dtype == torch.bfloat16:
-        from . import fast
-
-        if gate_up.shape[0] <= fast.SKINNY_MAX_ROWS and weight.shape[1] % 8 == 0:
-            fast.gemm_skinny(gate_up, weight, out, gated=True)
-            return
-    silu_mul(gate_up, activated)
-    linear(activated, weight, out)
-
-
 # --- position encoding and cache write ---------------------------------------------------
 def rope_store(qkv, positions, token_seq, block_table, inv_freq, rotary_dim: int, pages, q_heads: int, kv_heads: int, head_dim: int, page_size: int, write_cache: bool = True) -> None:
     """Rotate q (in place) and k, and store k, v of every token into its request's pages."""

@@ -22,7 +22,6 @@ def build_all() -> list:
     built = [build_library(f"tlie_attn_decode_d{d}", ["attention_decode.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
     built.append(build_library("tlie_attn_decode_d64_w4", ["attention_decode.cu"], {"HEAD_DIM": 64, "DECODE_WARPS": 4, "DECODE_STAGES": 3}))
     built += [build_library(f"tlie_attn_prefill_d{d}", ["attention_prefill.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
-    built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
     built.append(build_library("tlie_gemv_fused", ["gemv_fused.cu"]))
     built.append(build_library("tlie_gemm_tcgen05", TCGEN05_SOURCES))
     built.append(build_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"]))
@@ -33,28 +32,6 @@ def _ops():
     from .. import ops
 
     return ops
-
-
-SKINNY_MAX_ROWS = 16   # up to this many rows the weight-streaming kernel beats the library's product
-
-
-def skinny_library():
-    return load_library("tlie_gemm_skinny", ["gemm_skinny.cu"])
-
-
-def gemm_skinny(x, weight, out, gated: bool = False) -> None:
-    """out[M, N] = x . weight^T for M <= 64 rows; with ``gated`` x is [gate | up] and the operand is silu(gate) * up."""
-    ops = _ops()
-    M, N, K = x.shape[0], weight.shape[0], weight.shape[1]
-    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or K % 8 != 0 or M > 64 or x.shape[1] != (2 * K if gated else K):
-        raise KernelError(f"gemm_skinny cannot take x {tuple(x.shape)} (strides {x.stride()}) with weight {tuple(weight.shape)}", code="invalid_shape")
-    if not x.is_cuda:
-        raise KernelError("this engine has no CPU path: a kernel was given a tensor that is not on a CUDA device")
-    ops._check(
-        skinny_library().tlie_gemm_skinny(c_void_p(x.data_ptr()), c_int(x.stride(0)), ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K),
-                                          c_int(1 if gated else 0), c_int(1 if out.dtype == torch.float32 else 0), ops._stream()),
-        "gemm_skinny",
-    )
 
 
 FUSED_MAX_ROWS = 16     # the fused decode kernels (norm + product, product + residual add, gate) take up to this many rows
