@@ -40,14 +40,6 @@ def silu_mul(gate_up, out) -> None:
     _store(out, (g / (1.0 + torch.exp(-g))) * u)
 
 
-def gather_rows(src, rows, out) -> None:
-    out.copy_(src[rows.long()])
-
-
-def to_float(src, out) -> None:
-    out.copy_(src.float())
-
-
 def linear(x, weight, out) -> None:
     _store(out, x.float() @ weight.float().T)
 
@@ -129,7 +121,7 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
         out[r] = plain_llama.sample_top_p(logits[r].float(), float(temperature[r]), float(top_p[r]), u)
 
 
-_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "gather_rows", "to_float", "linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample"]
+_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample"]
 
 
 def install(monkeypatch) -> None:

@@ -156,22 +156,6 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   }
 }
 
-// out[r, :] = src[rows[r], :]
-template <typename T>
-__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows, T* __restrict__ out, int width) {
-  const int r = blockIdx.x;
-  const T* s = src + (size_t)rows[r] * width;
-  T* d = out + (size_t)r * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) d[i] = s[i];
-}
-
-// out (float) = float(in)
-template <typename T>
-__global__ void to_float_kernel(const T* __restrict__ in, float* __restrict__ out, size_t count) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
-    out[i] = to_float(in[i]);
-}
-
 }  // namespace tlie
 
 using namespace tlie;
@@ -245,23 +229,3 @@ TLIE_EXPORT int tlie_silu_mul(int dtype, const void* gate_up, void* out, int row
   return (int)cudaGetLastError();
 }
 
-TLIE_EXPORT int tlie_gather_rows(int dtype, const void* src, const int* rows, void* out, int out_rows, int width,
-                                 cudaStream_t stream) {
-  if (out_rows <= 0) return 0;
-  if (dtype == TLIE_F32)
-    gather_rows_kernel<float><<<out_rows, 256, 0, stream>>>((const float*)src, rows, (float*)out, width);
-  else
-    gather_rows_kernel<__nv_bfloat16><<<out_rows, 256, 0, stream>>>((const __nv_bfloat16*)src, rows,
-                                                                    (__nv_bfloat16*)out, width);
-  return (int)cudaGetLastError();
-}
-
-TLIE_EXPORT int tlie_to_float(int dtype, const void* in, float* out, long long count, cudaStream_t stream) {
-  if (count <= 0) return 0;
-  if (dtype == TLIE_F32)
-    to_float_kernel<float><<<grid_for(count, 256), 256, 0, stream>>>((const float*)in, out, (size_t)count);
-  else
-    to_float_kernel<__nv_bfloat16><<<grid_for(count, 256), 256, 0, stream>>>((const __nv_bfloat16*)in, out,
-                                                                             (size_t)count);
-  return (int)cudaGetLastError();
-}

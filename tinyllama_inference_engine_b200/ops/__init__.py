@@ -112,14 +112,6 @@ def silu_mul(gate_up, out) -> None:
     _check(core().tlie_silu_mul(_code(out), _ptr(gate_up), _ptr(out), c_int(rows), c_int(inter), _stream()), "silu_mul")
 
 
-def gather_rows(src, rows, out) -> None:
-    _check(core().tlie_gather_rows(_code(src), _ptr(src), _i32(rows, "rows"), _ptr(out), c_int(out.shape[0]), c_int(out.shape[1]), _stream()), "gather_rows")
-
-
-def to_float(src, out) -> None:
-    _check(core().tlie_to_float(_code(src), _ptr(src), _ptr(out), c_longlong(src.numel()), _stream()), "to_float")
-
-
 # --- matrix products --------------------------------------------------------------------
 def linear(x, weight, out) -> None:
     """out[M, N] = x[M, K] . weight[N, K]^T in the tensors' dtype (32-bit accumulation)."""
