@@ -326,6 +326,23 @@ def test_gemv_fused(ops, M, N, K):
         fast.gemv_fused(stream.cuda(), w.cuda(), got, norm=(norm_weight.cuda(), 1e-5, None if rows is None else rows.cuda()))
         # the kernel rounds residual * weight to bfloat16 and scales the 32-bit sum: the same product, rounded elsewhere
         assert torch.allclose(got.cpu(), want_n, atol=6e-3 * float(want_n.abs().max())), float((got.cpu() - want_n).abs().max())
+    # a product that completes the residual prepares the norm that follows: the next product reads what it left
+    # (bfloat16(residual * weight) and the rows' sums of squares) and gives what the norm-in-front kernel gives
+    if N % 8 == 0:
+        residual = torch.randn(M, N) * 2
+        next_weight = 1 + 0.1 * torch.randn(N)
+        w2 = (torch.randn(40, N) * 0.05).bfloat16()
+        total = residual.clone().cuda()
+        x_out, squares = fast.prepared_norm_buffers(M, N, "cuda")
+        fast.gemv_fused(x.cuda(), w.cuda(), total, epilogue="accumulate", prepare=(next_weight.cuda(), x_out, squares))
+        assert torch.allclose(total.cpu(), residual + want, atol=1e-4 * scale + 1e-5)
+        assert torch.equal(x_out.cpu(), (total.cpu() * next_weight).bfloat16())
+        assert torch.allclose(squares.sum(1).cpu(), (total.cpu() ** 2).sum(1), rtol=1e-5)
+        via_prepared = torch.empty(M, 40, dtype=torch.float32, device="cuda")
+        fast.gemv_fused(x_out, w2.cuda(), via_prepared, prepared=(squares, 1e-5))
+        via_norm = torch.empty(M, 40, dtype=torch.float32, device="cuda")
+        fast.gemv_fused(total, w2.cuda(), via_norm, norm=(next_weight.cuda(), 1e-5, None))
+        assert torch.allclose(via_prepared, via_norm, rtol=1e-5, atol=1e-6 * float(via_norm.abs().max()))
 
 
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window,rotate", [

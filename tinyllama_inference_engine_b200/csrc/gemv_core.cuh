@@ -10,7 +10,7 @@
 namespace tlie {
 
 constexpr int kGemvWarps = 8;
-enum { X_PLAIN = 0, X_NORM = 1, X_DIRECT = 2 };
+enum { X_PLAIN = 0, X_NORM = 1, X_DIRECT = 2, X_PREPARED = 3 };
 enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUM = 2, EPI_GATED = 3 };
 
 struct GemvArgs {
@@ -23,6 +23,14 @@ struct GemvArgs {
   void* out;                // STORE: [M, N]; ACCUM: float residual [M, N]; GATED: bf16 [M, N / 2]
   int M, N, K;
   int x_stride;             // shared-memory row stride of x, in elements
+  // ACCUM may prepare the norm that follows it: for the completed residual r it also stores bfloat16(r * prepare_weight)
+  // and, per row and 16-column tile, the sum of r^2 (what X_NORM would work out again in every CTA of the next product)
+  const float* prepare_weight;   // [N], or nullptr
+  __nv_bfloat16* prepare_x;      // [M, N]
+  float* prepare_squares;        // [M, tiles of 16 columns]
+  // X_PREPARED: x is such a bfloat16 [M, K]; squares [M, square_tiles] are summed into the row's scale with eps
+  const float* squares;
+  int square_tiles;
 };
 
 __device__ __forceinline__ uint4 load_stream_16(const void* p) {
@@ -42,7 +50,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* x
   // --- stage x in shared memory as bfloat16, once per CTA ----------------------------------------
   // Shared memory is kept small on purpose: the weight loads in flight are tracked in L1, which shrinks as
   // shared memory grows, and with it the bandwidth a CTA can pull.
-  if (XMODE == X_PLAIN) {
+  if (XMODE == X_PLAIN || XMODE == X_PREPARED) {
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
     const int chunks = K / 8;
     for (int idx = threadIdx.x; idx < MT * 8 * chunks; idx += kGemvWarps * 32) {
@@ -51,6 +59,15 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* x
       cp_async_16(xs + (size_t)m * a.x_stride + c * 8, x + (size_t)(m < a.M ? m : 0) * a.ldx + c * 8, m < a.M);
     }
     cp_async_commit();
+    if (XMODE == X_PREPARED) {   // the rows' scales from the sums of squares the previous product left, while the copies fly
+      for (int m = warp; m < MT * 8; m += kGemvWarps) {
+        float sum = 0.0f;
+        if (m < a.M)
+          for (int t = lane; t < a.square_tiles; t += 32) sum += __ldcg(a.squares + (size_t)m * a.square_tiles + t);
+        sum = warp_sum(sum);
+        if (lane == 0) row_scale[m] = 1.0f / sqrtf(sum / (float)K + a.eps);
+      }
+    }
     cp_async_wait<0>();
     __syncthreads();
   } else if (XMODE == X_NORM) {
@@ -107,28 +124,39 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
     base[(g + 8) * kRedRow + mt * 8 + 2 * t + 1] = acc[mt][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < kTileRows * MT * 8; idx += kGemvWarps * 32) {
+  for (int idx = threadIdx.x; idx < kTileRows * MT * 8; idx += kGemvWarps * 32) {   // whole warps: 16 * MT * 8 is 128 or 256
     const int m = idx / kTileRows;
     const int r = idx - m * kTileRows;
-    if (m >= a.M || n0 + r >= n_rows) continue;
+    const bool live = m < a.M && n0 + r < n_rows;
     float sum = 0.0f, second = 0.0f;
 #pragma unroll
     for (int wi = 0; wi < kGemvWarps; ++wi) {
       sum += red[(size_t)wi * 16 * kRedRow + r * kRedRow + m];
       if (EPI == EPI_GATED) second += red[(size_t)wi * 16 * kRedRow + (r + 8) * kRedRow + m];
     }
-    if (XMODE == X_NORM) {
+    if (XMODE == X_NORM || XMODE == X_PREPARED) {
       sum *= row_scale[m];
       second *= row_scale[m];
     }
     const size_t o = (size_t)m * n_rows + n0 + r;
     if (EPI == EPI_STORE_BF16) {
-      reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(sum);
+      if (live) reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(sum);
     } else if (EPI == EPI_STORE_F32) {
-      reinterpret_cast<float*>(a.out)[o] = sum;
+      if (live) reinterpret_cast<float*>(a.out)[o] = sum;
     } else if (EPI == EPI_ACCUM) {
-      reinterpret_cast<float*>(a.out)[o] = __ldcg(reinterpret_cast<const float*>(a.out) + o) + sum;
-    } else {
+      float value = 0.0f;
+      if (live) {
+        value = __ldcg(reinterpret_cast<const float*>(a.out) + o) + sum;
+        reinterpret_cast<float*>(a.out)[o] = value;
+      }
+      if (a.prepare_weight != nullptr) {   // the same for the whole block
+        if (live) a.prepare_x[o] = __float2bfloat16_rn(value * a.prepare_weight[n0 + r]);
+        float squares = value * value;     // zero where nothing lives; the 16 columns of a row are 16 neighbouring lanes
+#pragma unroll
+        for (int offset = 8; offset > 0; offset >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, offset);
+        if (r == 0 && m < a.M) a.prepare_squares[(size_t)m * ((n_rows + 15) / 16) + n0 / 16] = squares;
+      }
+    } else if (live) {
       // gate and up are rounded to bfloat16 first, as when the product is stored and read back
       const float gate = __bfloat162float(__float2bfloat16_rn(sum));
       const float up = __bfloat162float(__float2bfloat16_rn(second));

@@ -14,6 +14,9 @@
 //                    result, which is the same product because the scale is one number per row;
 //           X_DIRECT x is bfloat16 [M, K] and is not staged in shared memory at all (a CTA that
 //                    computes a single tile uses every element of x once);
+//           X_PREPARED x is bfloat16(residual * norm_weight) as the product that completed the residual left it
+//                    (ACCUM with prepare_*), with the rows' sums of squares per 16-column tile: the CTAs copy half
+//                    the bytes X_NORM reads and none of them squares anything;
 //   output  STORE    bfloat16 or 32-bit [M, N];
 //           ACCUM    residual[m, n] += result in 32-bit (each element owned by one thread, so the
 //                    sum is deterministic): the reference's add kernel (src/cuda/kernels.cu:208-215);
@@ -97,13 +100,19 @@ using namespace tlie;
 TLIE_EXPORT int tlie_gemv_max_rows() { return 16; }
 
 // x_mode 0: x bf16 [M, K] with row stride ldx.  x_mode 1: x is the 32-bit residual [*, K]; rows (optional) gathers,
-// norm_weight [K] and eps give the RMSNorm.  epilogue 0: bf16 out [M, N]; 1: 32-bit out; 2: out (32-bit [M, N]) += result;
+// norm_weight [K] and eps give the RMSNorm.  x_mode 3: x is bf16(residual * norm weight) [M, K] and `squares`
+// [M, square_tiles] the rows' sums of squares, as an earlier call with epilogue 2 and prepare_* left them.
+// prepare_weight (epilogue 2 only, else null): also store bf16(out * prepare_weight) in prepare_x [M, N] and the rows' sums of
+// squares per 16 columns in prepare_squares [M, ceil(N / 16)].  epilogue 0: bf16 out [M, N]; 1: 32-bit out; 2: out (32-bit [M, N]) += result;
 // 3: w holds [gate rows | up rows] (N even), out = silu(gate) * up as bf16 [M, N / 2].
 // Needs K % 8 == 0 (K % 4 == 0 suffices for x_mode 1 is NOT enough: weights are read 8 at a time), M <= 16.
 TLIE_EXPORT int tlie_gemv_fused(int x_mode, const void* x, int ldx, const int* rows, const float* norm_weight, float eps,
-                                const void* w, void* out, int M, int N, int K, int epilogue, cudaStream_t stream) {
+                                const void* w, void* out, int M, int N, int K, int epilogue, const float* squares, int square_tiles,
+                                const float* prepare_weight, void* prepare_x, float* prepare_squares, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || M > 16 || (x_mode == X_PLAIN && ldx % 8 != 0) || (epilogue == EPI_GATED && (N & 1)))
+  if (K <= 0 || K % 8 != 0 || M > 16 || ((x_mode == X_PLAIN || x_mode == X_PREPARED) && ldx % 8 != 0) || (epilogue == EPI_GATED && (N & 1)) ||
+      (x_mode == X_PREPARED && (squares == nullptr || square_tiles <= 0)) ||
+      (prepare_weight != nullptr && (epilogue != EPI_ACCUM || prepare_x == nullptr || prepare_squares == nullptr)))
     return (int)cudaErrorInvalidValue;
   GemvArgs a;
   a.x = x;
@@ -117,7 +126,13 @@ TLIE_EXPORT int tlie_gemv_fused(int x_mode, const void* x, int ldx, const int* r
   a.N = N;
   a.K = K;
   a.x_stride = gemv_x_stride(K);
+  a.squares = squares;
+  a.square_tiles = square_tiles;
+  a.prepare_weight = prepare_weight;
+  a.prepare_x = (__nv_bfloat16*)prepare_x;
+  a.prepare_squares = prepare_squares;
   if (x_mode == X_PLAIN) return launch_epilogue<X_PLAIN>(a, epilogue, stream);
   if (x_mode == X_NORM) return launch_epilogue<X_NORM>(a, epilogue, stream);
+  if (x_mode == X_PREPARED) return launch_epilogue<X_PREPARED>(a, epilogue, stream);
   return (int)cudaErrorInvalidValue;
 }

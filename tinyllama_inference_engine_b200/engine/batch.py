@@ -83,6 +83,7 @@ class StepContext:
     max_q_len: int
     max_seq_len: int
     attn_tiles: torch.Tensor | None = None
+    wants_every_row_in_order: bool = False      # want_rows is 0, 1, ..., num_tokens - 1
     attn_tiles_tc: torch.Tensor | None = None   # work items of the tensor-memory kernel: pairs of 128-row runs (int32 [n, 4])
 
     @property
@@ -138,5 +139,5 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=q_lens,
         host_first_positions=list(first_positions), host_state_slots=list(slots),
         max_q_len=max(q_lens), max_seq_len=max(seq_lens), attn_tiles=views[8].view(-1, 2),
-        attn_tiles_tc=views[9].view(-1, 4),
+        attn_tiles_tc=views[9].view(-1, 4), wants_every_row_in_order=want_rows == list(range(num_tokens)),
     )

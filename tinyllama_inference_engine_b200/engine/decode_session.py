@@ -60,7 +60,7 @@ class DecodeSession:
             num_tokens=count, num_seqs=count, token_ids=d[0], positions=d[1], token_seq=d[2], seq_starts=d[3], seq_lens=d[4],
             first_positions=d[5], state_slots=d[6], want_rows=d[7], block_tables=self.d_tables, request_ids=self.request_ids,
             host_q_lens=[1] * count, host_first_positions=[0] * count, host_state_slots=[0] * count, max_q_len=1,
-            max_seq_len=runner.spec.max_positions,
+            max_seq_len=runner.spec.max_positions, wants_every_row_in_order=True,
         )
         self.positions = [0] * count      # host mirror: position of the token each request runs next
         self.use_graph = use_graph

@@ -40,28 +40,46 @@ class DecoderModel:
 
     def forward(self, ctx, caches: dict[int, LayerCache]):
         """Logits (32-bit, [len(want_rows), vocab]) of the rows ``ctx.want_rows``."""
-        hidden = self.forward_hidden(ctx, caches)
-        return self.logits(hidden, ctx.want_rows)
+        hidden, pending = self._run_blocks(ctx, caches)
+        return self.logits(hidden, ctx.want_rows, pending if ctx.wants_every_row_in_order else None)
 
     def forward_hidden(self, ctx, caches: dict[int, LayerCache]):
+        return self._run_blocks(ctx, caches)[0]
+
+    def _run_blocks(self, ctx, caches: dict[int, LayerCache]):
+        """The complete residual stream of the step's rows, and a lazy final norm of it if the last block left one prepared."""
+        from .. import ops
+
         residual = self.embedding.forward(ctx.token_ids)
-        delta = None
-        for entry in self.spec.order:
+        pending = None
+        order = self.spec.order
+        for index, entry in enumerate(order):
             cache = caches[entry.cache]
             if cache.writes != entry.writes_cache:
                 cache = LayerCache(cache.need, entry.writes_cache, cache.pages, cache.block_table, cache.page_size, cache.state)
-            residual, delta = self.blocks[entry.layer].forward(residual, delta, ctx, cache)
-        if delta is not None:
-            from .. import ops
+            block = self.blocks[entry.layer]
+            if block.accepts_next_norm:
+                # the norm that reads this block's result: the next block's first one (if it names one), or the final norm
+                following = getattr(self.blocks[order[index + 1].layer], "mixer_norm", None) if index + 1 < len(order) else self.final_norm
+                residual, pending = block.forward(residual, pending, ctx, cache, next_norm=following)
+            else:
+                if isinstance(pending, ops.LazyNorm):
+                    pending = None   # the residual is complete; this block does not know prepared norms
+                residual, pending = block.forward(residual, pending, ctx, cache)
+        if isinstance(pending, ops.LazyNorm):
+            return residual, pending
+        if pending is not None:
+            ops.add_(residual, pending)
+        return residual, None
 
-            ops.add_(residual, delta)
-        return residual
-
-    def logits(self, residual, want_rows):
+    def logits(self, residual, want_rows, prepared=None):
+        """``prepared``: a lazy final norm of all rows that the last block left ready, usable when every row is wanted in order."""
         if want_rows is None or want_rows.shape[0] == 0:
             return None
         from .. import ops
 
         if self.final_norm.supports_lazy and want_rows.shape[0] <= ops.fused_rows_limit(self.runtime.dtype, residual.device):
+            if prepared is not None and prepared.weight is self.final_norm.weight and prepared.shape[0] == want_rows.shape[0]:
+                return self.head.forward(prepared)
             return self.head.forward(self.final_norm.forward(residual, None, rows=want_rows, lazy=True))
         return self.head.forward(self.final_norm.forward(residual, None, rows=want_rows))

@@ -34,7 +34,11 @@ def _ops():
     return ops
 
 
-FUSED_MAX_ROWS = 16     # the fused decode kernels (norm + product, product + residual add, gate) take up to this many rows
+GEMV_KERNEL_MAX_ROWS = 16   # what gemv_fused.cu can take
+# Up to this many rows a step uses the fused decode kernels (norm + product, product + residual add, gate).  Measured on the
+# 1.1B shapes: with 9 to 16 rows (two groups of eight per warp) a decode step takes 1.34 to 1.49 ms on them and 1.14 to 1.23 ms
+# on the library's product with separate norm and activation kernels, so they stop at eight.
+FUSED_MAX_ROWS = 8
 _EPILOGUES = {"store": None, "accumulate": 2, "gated": 3}
 
 
@@ -53,19 +57,29 @@ def gemv_fits(rows: int, K: int, norm: bool, gated: bool = False) -> bool:
     return need <= 200 * 1024
 
 
-def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store") -> None:
+def prepared_norm_buffers(rows: int, width: int, device) -> tuple:
+    """Where a product that completes the residual leaves the next norm's input: bfloat16(residual * norm weight) [rows, width]
+    and the rows' sums of squares per 16 columns, 32-bit [rows, ceil(width / 16)]."""
+    return (torch.empty((rows, width), dtype=torch.bfloat16, device=device), torch.empty((rows, -(-width // 16)), dtype=torch.float32, device=device))
+
+
+def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=None, prepare=None) -> None:
     """out (+)= f(x) . weight^T for up to 16 rows, one kernel.
 
     norm      None: ``x`` is bfloat16 [M, K].  (norm_weight, eps, rows): ``x`` is the 32-bit residual stream and
               the operand is rmsnorm(x[rows]) * norm_weight (rows None: the first M rows).
+    prepared  (squares, eps): ``x`` is bfloat16(residual * norm weight) [M, K] and ``squares`` [M, tiles] the rows' sums of
+              squares, as an earlier "accumulate" with ``prepare`` left them; the operand is the same rmsnorm.
     epilogue  "store": out [M, N] bfloat16 or 32-bit;  "accumulate": out is the 32-bit residual, out += result;
               "gated": weight is [gate rows | up rows], out [M, N / 2] = silu(gate) * up.
+    prepare   ("accumulate" only) (norm_weight [N], x_out bfloat16 [M, N], squares_out [M, ceil(N / 16)]): also store
+              bfloat16(out * norm_weight) and the rows' sums of squares per 16 columns, for a later call with ``prepared``.
     """
     ops = _ops()
     N, K = weight.shape
     M = out.shape[0]
-    if weight.dtype != torch.bfloat16 or M > FUSED_MAX_ROWS or K % 8 != 0:
-        raise KernelError(f"gemv_fused takes bfloat16 weights with K % 8 == 0 and at most {FUSED_MAX_ROWS} rows", code="invalid_shape")
+    if weight.dtype != torch.bfloat16 or M > GEMV_KERNEL_MAX_ROWS or K % 8 != 0:
+        raise KernelError(f"gemv_fused takes bfloat16 weights with K % 8 == 0 and at most {GEMV_KERNEL_MAX_ROWS} rows", code="invalid_shape")
     code = _EPILOGUES[epilogue]
     if epilogue == "store":
         code = 1 if out.dtype == torch.float32 else 0
@@ -73,7 +87,14 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store") -> None:
         raise KernelError("gemv_fused accumulates into the 32-bit residual only", code="invalid_dtype")
     if out.shape[1] != (N // 2 if epilogue == "gated" else N):
         raise KernelError("gemv_fused: the output's width does not fit the weight", code="invalid_shape")
-    if norm is None:
+    consume = (c_void_p(0), c_int(0))
+    if prepared is not None:
+        squares, eps = prepared
+        if x.dtype != torch.bfloat16 or x.shape != (M, K) or not x.is_contiguous() or squares.dtype != torch.float32 or squares.shape[0] != M or not squares.is_contiguous():
+            raise KernelError("gemv_fused: a prepared norm is bfloat16 [M, K] with 32-bit sums of squares [M, tiles]", code="invalid_shape")
+        args = (c_int(3), ops._ptr(x), c_int(K), c_void_p(0), c_void_p(0), c_float(eps))
+        consume = (ops._ptr(squares), c_int(squares.shape[1]))
+    elif norm is None:
         if x.dtype != torch.bfloat16 or x.shape != (M, K) or x.stride(1) != 1 or x.stride(0) % 8 != 0:
             raise KernelError("gemv_fused: x must be bfloat16 [M, K] with rows 16-byte aligned", code="invalid_shape")
         args = (c_int(0), c_void_p(x.data_ptr()), c_int(x.stride(0)), c_void_p(0), c_void_p(0), c_float(0.0))
@@ -84,7 +105,15 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store") -> None:
         args = (c_int(1), ops._ptr(x), c_int(K), ops._i32(rows, "rows"), ops._ptr(norm_weight), c_float(eps))
     if not out.is_cuda:
         raise KernelError("this engine has no CPU path: a kernel was given a tensor that is not on a CUDA device")
-    ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), ops._stream()), "gemv_fused")
+    emit = (c_void_p(0), c_void_p(0), c_void_p(0))
+    if prepare is not None:
+        norm_weight, x_out, squares_out = prepare
+        if (epilogue != "accumulate" or norm_weight.dtype != torch.float32 or norm_weight.numel() != N or x_out.dtype != torch.bfloat16 or x_out.shape != (M, N)
+                or squares_out.dtype != torch.float32 or squares_out.shape != (M, -(-N // 16)) or not x_out.is_contiguous() or not squares_out.is_contiguous()):
+            raise KernelError("gemv_fused: prepare takes a 32-bit norm weight [N], bfloat16 [M, N] and 32-bit [M, ceil(N / 16)], with accumulate", code="invalid_shape")
+        emit = (ops._ptr(norm_weight), ops._ptr(x_out), ops._ptr(squares_out))
+    ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), *consume, *emit, ops._stream()),
+               "gemv_fused")
 
 
 # --- tensor-core product for many rows (tcgen05, TMA, tensor memory) -------------------------------------

@@ -24,6 +24,7 @@ class Attention(Mixer):
 
     accepts_lazy_norm = True
     fuses_residual_add = True
+    prepares_next_norm = True
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
@@ -55,7 +56,7 @@ class Attention(Mixer):
         self.position = build_part("position", spec["position"], prefix, weights, runtime)
         self.qkv_width = (self.q_heads + 2 * self.kv_heads) * self.head_dim
 
-    def forward(self, x, ctx, cache: LayerCache, accumulate_into=None):
+    def forward(self, x, ctx, cache: LayerCache, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         qkv = ws.get("qkv", tokens, self.qkv_width, dtype)
         if isinstance(x, ops.LazyNorm):
@@ -73,7 +74,7 @@ class Attention(Mixer):
                            self.q_heads, self.kv_heads, self.head_dim, cache.page_size, self.window, self.scale,
                            write_cache=cache.writes, batch=ctx)
         if accumulate_into is not None:
-            ops.linear_accumulate(mixed, self.w_o, accumulate_into)
+            ops.linear_accumulate(mixed, self.w_o, accumulate_into, prepare)
             return None
         out = ws.get("mixer_out", tokens, self.hidden, dtype)
         ops.linear(mixed, self.w_o, out)

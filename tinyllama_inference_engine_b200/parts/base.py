@@ -20,9 +20,14 @@ What each category must offer:
                ``forward(x, ctx, cache) -> y`` for the step's tokens ``x [T, hidden]``.
   feed_forward ``forward(x, ctx) -> y``.
                (A mixer or feed-forward may set ``accepts_lazy_norm`` / ``fuses_residual_add``
-               to take the norm before it and the residual add after it into its own kernels.)
-  block        ``forward(residual, delta, ctx, cache) -> (residual, delta)``: the
-               hidden state is the pair (32-bit residual, last output not yet added).
+               to take the norm before it and the residual add after it into its own kernels, and
+               ``prepares_next_norm`` to take ``prepare=<the lazy norm that follows>`` along with
+               ``accumulate_into`` and leave that norm's input for the next product.)
+  block        ``forward(residual, pending, ctx, cache) -> (residual, pending)``: the hidden state
+               is the pair (32-bit residual, what is pending on it): None, the last output not
+               yet added, or (residual complete) a lazy norm already prepared for whoever
+               normalises next.  A block with ``accepts_next_norm`` is also given
+               ``next_norm=<the norm part that will read its result>``.
 """
 from __future__ import annotations
 
@@ -130,6 +135,7 @@ class Mixer(Part):
     # A mixer (or feed-forward) that sets these takes more work into its own kernels when the block offers it:
     accepts_lazy_norm = False      # forward may receive an ops.LazyNorm in the place of the normalised tensor
     fuses_residual_add = False     # forward(..., accumulate_into=residual) adds its output there and returns None
+    prepares_next_norm = False     # with accumulate_into it also takes prepare=<ops.LazyNorm of the norm that follows>
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
@@ -143,6 +149,7 @@ class FeedForward(Part):
     category = "feed_forward"
     accepts_lazy_norm = False
     fuses_residual_add = False
+    prepares_next_norm = False
 
     def forward(self, x, ctx):
         raise NotImplementedError
@@ -150,6 +157,7 @@ class FeedForward(Part):
 
 class Block(Part):
     category = "block"
+    accepts_next_norm = False      # forward(..., next_norm=<Norm>) : the norm that will read this block's result, if known
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:

@@ -35,22 +35,36 @@ class PreNormResidualBlock(Block):
         for slot, category in self._SLOTS:
             setattr(self, slot, build_part(category, spec[slot], f"{prefix}.{spec[slot + '_name']}", weights, runtime))
 
-    def forward(self, residual, delta, ctx, cache: LayerCache):
+    accepts_next_norm = True
+
+    def forward(self, residual, pending, ctx, cache: LayerCache, next_norm=None):
         from .. import ops
 
         fused = residual.shape[0] <= ops.fused_rows_limit(self.runtime.dtype, residual.device)
-        delta = self._run(self.mixer_norm, self.mixer, residual, delta, fused, ctx, cache)
-        delta = self._run(self.feed_forward_norm, self.feed_forward, residual, delta, fused, ctx)
-        return residual, delta
+        pending = self._run(self.mixer_norm, self.mixer, residual, pending, fused, self.feed_forward_norm, ctx, cache)
+        pending = self._run(self.feed_forward_norm, self.feed_forward, residual, pending, fused, next_norm, ctx)
+        return residual, pending
 
     @staticmethod
-    def _run(norm, part, residual, delta, fused, *args):
-        """norm -> part, letting the part take the norm and the residual add into its kernels where it can (few rows)."""
-        if fused and part.accepts_lazy_norm and norm.supports_lazy:
-            x = norm.forward(residual, delta, lazy=True)
+    def _run(norm, part, residual, pending, fused, next_norm, *args):
+        """norm -> part, letting the part take the norm and the residual add into its kernels where it can (few rows).
+
+        ``pending``: None, the output not yet added to the residual, or a lazy norm that the product before left prepared
+        (the residual is complete then).  Returns what is pending after the part."""
+        from .. import ops
+
+        if isinstance(pending, ops.LazyNorm):
+            usable = fused and part.accepts_lazy_norm and pending.weight is norm.weight and pending.eps == norm.eps
+            x = pending if usable else norm.forward(residual, None, lazy=fused and part.accepts_lazy_norm and norm.supports_lazy)
+        elif fused and part.accepts_lazy_norm and norm.supports_lazy:
+            x = norm.forward(residual, pending, lazy=True)
         else:
-            x = norm.forward(residual, delta)
+            x = norm.forward(residual, pending)
         if fused and part.fuses_residual_add:
+            if part.prepares_next_norm and next_norm is not None and next_norm.supports_lazy:
+                following = next_norm.forward(residual, None, lazy=True)   # of the residual as it will be when the part is done
+                part.forward(x, *args, accumulate_into=residual, prepare=following)
+                return following
             return part.forward(x, *args, accumulate_into=residual)
         return part.forward(x, *args)
 

@@ -21,6 +21,7 @@ class GatedMLP(FeedForward):
 
     accepts_lazy_norm = True
     fuses_residual_add = True
+    prepares_next_norm = True
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
@@ -41,7 +42,7 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat([weights.get(f"{prefix}.gate_proj.weight", dtype), weights.get(f"{prefix}.up_proj.weight", dtype)], dim=0).contiguous()
         self.w_down = weights.get(f"{prefix}.down_proj.weight", dtype).contiguous()
 
-    def forward(self, x, ctx, accumulate_into=None):
+    def forward(self, x, ctx, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         act = ws.get("activated", tokens, self.inter, dtype)
         if tokens <= ops.fused_rows_limit(dtype, act.device):
@@ -59,7 +60,7 @@ class GatedMLP(FeedForward):
             ops.linear(x, self.w_gate_up, gate_up)
             ops.silu_mul(gate_up, act)
         if accumulate_into is not None:
-            ops.linear_accumulate(act, self.w_down, accumulate_into)
+            ops.linear_accumulate(act, self.w_down, accumulate_into, prepare)
             return None
         out = ws.get("ff_out", tokens, self.hidden, dtype)
         ops.linear(act, self.w_down, out)

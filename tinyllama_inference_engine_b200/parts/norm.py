@@ -31,7 +31,13 @@ class RMSNorm(Norm):
     def forward(self, residual, delta=None, rows=None, lazy: bool = False):
         """``lazy`` (and nothing to add): hand the norm on to the product that consumes it (ops.LazyNorm)."""
         if lazy and delta is None:
-            return ops.LazyNorm(residual, self.weight, self.eps, rows, lambda: self.forward(residual, None, rows))
+            handle = ops.LazyNorm(residual, self.weight, self.eps, rows, lambda: self.forward(residual, None, rows))
+            if rows is None and self.runtime.dtype == torch.bfloat16:
+                # where a product that completes the residual may leave this norm's input (ops.linear_accumulate(..., prepare=handle))
+                ws = self.runtime.workspace
+                handle.buffers = (ws.get("prepared_norm", residual.shape[0], self.size, torch.bfloat16),
+                                  ws.get("prepared_squares", residual.shape[0], -(-self.size // 16), torch.float32))
+            return handle
         count = residual.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.workspace.get("normed" if rows is None else "normed_rows", count, self.size, self.runtime.dtype)
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
