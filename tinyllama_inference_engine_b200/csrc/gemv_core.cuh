@@ -172,7 +172,7 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
 template <int MT, int XMODE, int EPI>
 struct GemvPhase {
   static constexpr int kTileRows = (EPI == EPI_GATED) ? 8 : 16;
-  static constexpr int UNROLL = (XMODE == X_DIRECT && MT > 1) ? 4 : 8;
+  static constexpr int UNROLL = 8;   // k blocks of 32 a thread holds in flight per round (four were tried for the 16-row direct kernels: slower)
   static constexpr int kRedRow = MT * 8 + 1;
   uint4 wreg[UNROLL][2];
 

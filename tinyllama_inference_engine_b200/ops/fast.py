@@ -36,9 +36,10 @@ def _ops():
 
 GEMV_KERNEL_MAX_ROWS = 16   # what gemv_fused.cu can take
 # Up to this many rows a step uses the fused decode kernels (norm + product, product + residual add, gate).  Measured on the
-# 1.1B shapes: with 9 to 16 rows (two groups of eight per warp) a decode step takes 1.34 to 1.49 ms on them and 1.14 to 1.23 ms
-# on the library's product with separate norm and activation kernels, so they stop at eight.
-FUSED_MAX_ROWS = 8
+# 1.1B shapes, a decode step of 9 / 12 / 16 requests: 1.10 / 1.15 / 1.20 ms on them, 1.14 / 1.20 / 1.23 to 1.30 ms on the
+# library's product with separate norm and activation kernels.  (With four weight blocks in flight per thread instead of
+# eight in the 16-row kernels that read x directly, the fused step took 1.34 to 1.49 ms and lost.)
+FUSED_MAX_ROWS = 16
 _EPILOGUES = {"store": None, "accumulate": 2, "gated": 3}
 
 
