@@ -156,3 +156,13 @@ def test_batches_that_pass_through_a_size_are_not_captured(model_folders):
     assert sessions[4].graph is not None and sessions[1].graph is not None   # eleven and sixteen steps
     assert sessions[3].graph is None and sessions[2].graph is None           # one step each
     engine.runner.cache.check()
+
+
+def test_one_token_prompts(model_folders):
+    """A prompt of one token is a step of one token that samples, but of a request the cache does not know yet: it must not
+    go the way of decode steps (which continue live requests), and what follows it must."""
+    config, weights = plain_llama.load_model(model_folders["b"])
+    prompts = [[7], [11], [3]]
+    engine = _engine(model_folders["b"], use_cuda_graphs=True)
+    got = [r.generated_tokens for r in engine.generate(prompts, SamplingParams(max_tokens=6))]
+    assert got == [plain_llama.generate_greedy(config, weights, p, 6) for p in prompts]
