@@ -308,6 +308,15 @@ def test_gemv_fused(ops, M, N, K):
     got = residual.clone().cuda()
     fast.gemv_fused(x.cuda(), w.cuda(), got, epilogue="accumulate")
     assert torch.allclose(got.cpu(), residual + want, atol=1e-4 * scale + 1e-5)
+    # long rows and few tiles take sixteen warps per CTA (K split sixteen ways): the same sums with the eight-warp kernel
+    library = fast.gemv_library()
+    library.tlie_gemv_set_wide_ctas(0)
+    try:
+        narrow = residual.clone().cuda()
+        fast.gemv_fused(x.cuda(), w.cuda(), narrow, epilogue="accumulate")
+    finally:
+        library.tlie_gemv_set_wide_ctas(1)
+    assert torch.allclose(narrow, got, atol=1e-4 * scale + 1e-5)
     # gated: silu of the first half of the rows times the second half, both rounded to bfloat16 first
     half = N // 2
     g, u = want[:, :half].bfloat16().float(), want[:, half:].bfloat16().float()

@@ -9,7 +9,7 @@
 
 namespace tlie {
 
-constexpr int kGemvWarps = 8;
+constexpr int kGemvWarps = 8;       // warps of a CTA; the kernels that stream long rows without staging x take 16 (template parameter WARPS)
 enum { X_PLAIN = 0, X_NORM = 1, X_DIRECT = 2, X_PREPARED = 3 };
 enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUM = 2, EPI_GATED = 3 };
 
@@ -43,7 +43,7 @@ __device__ __forceinline__ uint4 load_stream_16(const void* p) {
 // x into shared memory as bfloat16 (nothing for X_DIRECT); ends with a block-wide barrier.  X_NORM stores
 // bf16(residual * norm_weight) and leaves 1 / rms of each row in row_scale: the epilogue applies it.
 // kBatch: 16-byte loads of the residual a lane has in flight (more: fewer dependent round trips, more registers).
-template <int MT, int XMODE, int kBatch = 8>
+template <int MT, int XMODE, int kBatch = 8, int WARPS = kGemvWarps>
 __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* xs, float* row_scale) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = a.K;
@@ -53,14 +53,14 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* x
   if (XMODE == X_PLAIN || XMODE == X_PREPARED) {
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
     const int chunks = K / 8;
-    for (int idx = threadIdx.x; idx < MT * 8 * chunks; idx += kGemvWarps * 32) {
+    for (int idx = threadIdx.x; idx < MT * 8 * chunks; idx += WARPS * 32) {
       const int m = idx / chunks;
       const int c = idx - m * chunks;
       cp_async_16(xs + (size_t)m * a.x_stride + c * 8, x + (size_t)(m < a.M ? m : 0) * a.ldx + c * 8, m < a.M);
     }
     cp_async_commit();
     if (XMODE == X_PREPARED) {   // the rows' scales from the sums of squares the previous product left, while the copies fly
-      for (int m = warp; m < MT * 8; m += kGemvWarps) {
+      for (int m = warp; m < MT * 8; m += WARPS) {
         float sum = 0.0f;
         if (m < a.M)
           for (int t = lane; t < a.square_tiles; t += 32) sum += __ldcg(a.squares + (size_t)m * a.square_tiles + t);
@@ -73,7 +73,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* x
   } else if (XMODE == X_NORM) {
     const float* residual = reinterpret_cast<const float*>(a.x);
     const int chunks = K / 4;
-    for (int m = warp; m < MT * 8; m += kGemvWarps) {
+    for (int m = warp; m < MT * 8; m += WARPS) {
       __nv_bfloat16* dst = xs + (size_t)m * a.x_stride;
       float sum = 0.0f;
       if (m < a.M) {
@@ -108,7 +108,7 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* x
 // The end of a tile: the warps' partial tiles are summed through `red` ([warp][16][MT * 8 + 1] floats) and stored by the
 // variant's epilogue.  acc[mt] is a warp's m16n8 accumulator (weight rows x activation rows).  A gated tile holds 8 gate
 // rows in the upper half of the accumulator's rows and the 8 up rows of the same outputs in the lower half.
-template <int MT, int XMODE, int EPI>
+template <int MT, int XMODE, int EPI, int WARPS = kGemvWarps>
 __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float (&acc)[MT][4], float* red, const float* row_scale, int n0) {
   constexpr int kRedRow = MT * 8 + 1;
   constexpr int kTileRows = (EPI == EPI_GATED) ? 8 : 16;      // outputs of a tile
@@ -124,13 +124,13 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
     base[(g + 8) * kRedRow + mt * 8 + 2 * t + 1] = acc[mt][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < kTileRows * MT * 8; idx += kGemvWarps * 32) {   // whole warps: 16 * MT * 8 is 128 or 256
+  for (int idx = threadIdx.x; idx < kTileRows * MT * 8; idx += WARPS * 32) {   // whole warps: 16 * MT * 8 is 128 or 256
     const int m = idx / kTileRows;
     const int r = idx - m * kTileRows;
     const bool live = m < a.M && n0 + r < n_rows;
     float sum = 0.0f, second = 0.0f;
 #pragma unroll
-    for (int wi = 0; wi < kGemvWarps; ++wi) {
+    for (int wi = 0; wi < WARPS; ++wi) {
       sum += red[(size_t)wi * 16 * kRedRow + r * kRedRow + m];
       if (EPI == EPI_GATED) second += red[(size_t)wi * 16 * kRedRow + (r + 8) * kRedRow + m];
     }
@@ -169,7 +169,7 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
 // A tile is 16 weight rows (the A operand of the MMA), or for GATED 8 gate rows and the 8 up rows N / 2 below them: the
 // outputs of a gated tile are 8, so that the tiles of the widest product can be dealt evenly to the CTAs.  (Tiles of 8 rows
 // with the other half of the MMA empty were tried for the down projection, 128 tiles of 16 x 5632: 11.1 us against 7.9 us.)
-template <int MT, int XMODE, int EPI>
+template <int MT, int XMODE, int EPI, int WARPS = kGemvWarps>
 struct GemvPhase {
   static constexpr int kTileRows = (EPI == EPI_GATED) ? 8 : 16;
   static constexpr int UNROLL = 8;   // k blocks of 32 a thread holds in flight per round (four were tried for the 16-row direct kernels: slower)
@@ -178,7 +178,7 @@ struct GemvPhase {
 
   // Shared memory this variant needs: x as bfloat16 (unless read directly) and the warps' partial tiles.
   static __host__ __device__ size_t smem_bytes(int x_stride) {
-    return (XMODE == X_DIRECT ? 0 : (size_t)MT * 8 * x_stride * 2) + (size_t)kGemvWarps * 16 * kRedRow * sizeof(float);
+    return (XMODE == X_DIRECT ? 0 : (size_t)MT * 8 * x_stride * 2) + (size_t)WARPS * 16 * kRedRow * sizeof(float);
   }
   static __device__ __forceinline__ float* red_of(unsigned char* smem, int x_stride) {
     return reinterpret_cast<float*>(smem + (XMODE == X_DIRECT ? 0 : (size_t)MT * 8 * x_stride * 2));
@@ -195,14 +195,14 @@ struct GemvPhase {
     const __nv_bfloat16* r1 = a.w + (size_t)(EPI == EPI_GATED ? n_rows + min(n0 + g, n_rows - 1) : min(n0 + g + 8, n_rows - 1)) * K + t * 8;
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const int kb = kb0 + u * kGemvWarps;
+      const int kb = kb0 + u * WARPS;
       const bool valid = kb * 32 + t * 8 < K;
       wreg[u][0] = valid ? load_stream_16(r0 + (size_t)kb * 32) : make_uint4(0, 0, 0, 0);
       wreg[u][1] = valid ? load_stream_16(r1 + (size_t)kb * 32) : make_uint4(0, 0, 0, 0);
     }
   }
 
-  __device__ __forceinline__ void stage_x(const GemvArgs& a, __nv_bfloat16* xs, float* row_scale) { gemv_stage_x<MT, XMODE>(a, xs, row_scale); }
+  __device__ __forceinline__ void stage_x(const GemvArgs& a, __nv_bfloat16* xs, float* row_scale) { gemv_stage_x<MT, XMODE, 8, WARPS>(a, xs, row_scale); }
 
   // tiles first_tile, first_tile + tile_step, ...; the first round of the first tile is in wreg already if first_round_issued
   __device__ __forceinline__ void run(const GemvArgs& a, __nv_bfloat16* xs, float* red, const float* row_scale, int first_tile, int tile_step,
@@ -220,14 +220,14 @@ struct GemvPhase {
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
 
-      for (int kb0 = warp; kb0 < blocks; kb0 += kGemvWarps * UNROLL) {
+      for (int kb0 = warp; kb0 < blocks; kb0 += WARPS * UNROLL) {
         if (kb0 != warp || !issued) issue(a, n0, kb0);
         uint4 xdirect[XMODE == X_DIRECT ? UNROLL : 1][MT];
         if (XMODE == X_DIRECT) {
           const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
 #pragma unroll
           for (int u = 0; u < UNROLL; ++u) {
-            const int k = (kb0 + u * kGemvWarps) * 32 + t * 8;
+            const int k = (kb0 + u * WARPS) * 32 + t * 8;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               const int m = mt * 8 + g;
@@ -237,7 +237,7 @@ struct GemvPhase {
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-          const int kb = kb0 + u * kGemvWarps;
+          const int kb = kb0 + u * WARPS;
           if (kb >= blocks) continue;          // the same for every lane: mma.sync needs the whole warp
           const int k = kb * 32 + t * 8;
           const unsigned lo[4] = {wreg[u][0].x, wreg[u][1].x, wreg[u][0].y, wreg[u][1].y};
@@ -259,7 +259,7 @@ struct GemvPhase {
       // the weights of the next tile's first round go out before this tile is summed and stored
       issued = tile_index + tile_step < tiles;
       if (issued) issue(a, (tile_index + tile_step) * kTileRows, warp);
-      gemv_reduce_store<MT, XMODE, EPI>(a, acc, red, row_scale, n0);
+      gemv_reduce_store<MT, XMODE, EPI, WARPS>(a, acc, red, row_scale, n0);
     }
   }
 };

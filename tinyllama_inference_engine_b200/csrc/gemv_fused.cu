@@ -33,11 +33,11 @@
 
 namespace tlie {
 
-template <int MT, int XMODE, int EPI>
-__global__ void __launch_bounds__(kGemvWarps * 32) gemv_fused_kernel(const GemvArgs a) {
+template <int MT, int XMODE, int EPI, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) gemv_fused_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float row_scale[MT * 8];
-  GemvPhase<MT, XMODE, EPI> phase;
+  GemvPhase<MT, XMODE, EPI, WARPS> phase;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [MT * 8][x_stride]
   float* red = phase.red_of(smem_raw, a.x_stride);                  // [warps][16][MT * 8 + 1]
   // weights of the first round, before anything that depends on the previous kernel
@@ -48,19 +48,20 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_fused_kernel(const GemvA
   phase.run(a, xs, red, row_scale, blockIdx.x, gridDim.x, true);
 }
 
-template <int MT, int XMODE, int EPI>
+template <int MT, int XMODE, int EPI, int WARPS = kGemvWarps>
 static int launch_one(const GemvArgs& a, int grid, cudaStream_t stream) {
-  const size_t smem = GemvPhase<MT, XMODE, EPI>::smem_bytes(a.x_stride);
+  const size_t smem = GemvPhase<MT, XMODE, EPI, WARPS>::smem_bytes(a.x_stride);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<MT, XMODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<MT, XMODE, EPI, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  return (int)launch_pdl(gemv_fused_kernel<MT, XMODE, EPI>, dim3(grid), dim3(kGemvWarps * 32), smem, stream, a);
+  return (int)launch_pdl(gemv_fused_kernel<MT, XMODE, EPI, WARPS>, dim3(grid), dim3(WARPS * 32), smem, stream, a);
 }
 
+static int gemv_wide_ctas = 1;      // tlie_gemv_set_wide_ctas
 constexpr int kGemvCtasPerSm = 2;   // how many CTAs of a product an SM is dealt at most (measured: 1 and 3 are slower for the wide products)
 
 template <int XMODE, int EPI>
@@ -73,6 +74,8 @@ static int launch_rows(const GemvArgs& a, cudaStream_t stream) {
   const int per_cta = (tiles + slots - 1) / slots;
   const int grid = (tiles + per_cta - 1) / per_cta;
   if (XMODE == X_PLAIN && per_cta == 1) {   // every element of x is used once per CTA: no point in staging it
+    // long rows and no more tiles than SMs: sixteen warps split K, so that a CTA has twice the bytes in flight and half the rounds
+    if (a.M <= 8 && gemv_wide_ctas && tiles <= 148 && a.K > kGemvWarps * 8 * 32) return launch_one<1, X_DIRECT, EPI, 16>(a, grid, stream);
     if (a.M <= 8) return launch_one<1, X_DIRECT, EPI>(a, grid, stream);
     if (a.M <= 16) return launch_one<2, X_DIRECT, EPI>(a, grid, stream);
     return (int)cudaErrorInvalidValue;
@@ -98,6 +101,8 @@ static int launch_epilogue(const GemvArgs& a, int epilogue, cudaStream_t stream)
 using namespace tlie;
 
 TLIE_EXPORT int tlie_gemv_max_rows() { return 16; }
+// 0: products of long rows never take sixteen warps per CTA (for comparison)
+TLIE_EXPORT void tlie_gemv_set_wide_ctas(int on) { gemv_wide_ctas = on; }
 
 // x_mode 0: x bf16 [M, K] with row stride ldx.  x_mode 1: x is the 32-bit residual [*, K]; rows (optional) gathers,
 // norm_weight [K] and eps give the RMSNorm.  x_mode 3: x is bf16(residual * norm weight) [M, K] and `squares`
