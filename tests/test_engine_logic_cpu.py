@@ -89,3 +89,16 @@ def test_gemm_tile_width_prefers_full_waves():
     for rows in (128, 300, 5000):
         for cols in (64, 1000, 32000):
             assert fast.gemm_tile_width(rows, cols) in fast.GEMM_TILE_WIDTHS
+
+
+def test_decode_attention_parts_fit_one_wave():
+    """requests x kv heads x parts never exceeds the SMs while a (request, kv head) has a CTA to itself: no second wave."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    for requests in (1, 2, 3, 7, 8, 9, 16, 33, 37, 64):
+        for kv_heads in (1, 2, 4, 8):
+            parts = fast.decode_splits(requests, kv_heads, 4096)
+            assert 1 <= parts <= 32
+            if requests * kv_heads <= fast.SM_COUNT:
+                assert requests * kv_heads * parts <= fast.SM_COUNT
+    assert fast.decode_splits(8, 4, 2048) == 4 and fast.decode_splits(1, 4, 2048) == 8 and fast.decode_splits(1, 4, 100) == 1

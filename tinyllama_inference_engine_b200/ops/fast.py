@@ -231,8 +231,8 @@ def decode_attention_library(head_dim: int, narrow: bool = False):
 
 
 def decode_splits(requests: int, kv_heads: int, max_context: int) -> int:
-    """Parts the key range is cut into: about one CTA (eight warps) per SM, at least 256 keys per part, at most 32 parts."""
-    by_occupancy = -(-SM_COUNT // max(1, requests * kv_heads))
+    """Parts the key range is cut into: at most one CTA (eight warps) per SM, at least 256 keys per part, at most 32 parts."""
+    by_occupancy = max(1, SM_COUNT // max(1, requests * kv_heads))   # rounded down: one CTA too many is a second wave
     by_length = max(1, -(-max_context // 256))
     return max(1, min(by_occupancy, by_length, 32))
 
