@@ -256,7 +256,9 @@ struct GemvPhase {
           }
         }
       }
-      // the weights of the next tile's first round go out before this tile is summed and stored
+      // the weights of the next tile's first round go out before this tile is summed and stored.  (Refilling every slot of
+      // wreg right after the MMAs that read it was tried: a warp then waits for its newest loads whenever it waits for an
+      // old one, and the widest products took half as long again.)
       issued = tile_index + tile_step < tiles;
       if (issued) issue(a, (tile_index + tile_step) * kTileRows, warp);
       gemv_reduce_store<MT, XMODE, EPI, WARPS>(a, acc, red, row_scale, n0);
