@@ -166,3 +166,17 @@ def test_one_token_prompts(model_folders):
     engine = _engine(model_folders["b"], use_cuda_graphs=True)
     got = [r.generated_tokens for r in engine.generate(prompts, SamplingParams(max_tokens=6))]
     assert got == [plain_llama.generate_greedy(config, weights, p, 6) for p in prompts]
+
+
+@pytest.mark.parametrize("count", [12, 20])
+def test_wider_decode_batches(model_folders, count):
+    """Twelve requests decode on the 16-row fused kernels, twenty on the library's product with separate norm kernels."""
+    config, weights = plain_llama.load_model(model_folders["e"])
+    prompts = _prompts(config["vocab_size"], [3 + (5 * i) % 23 for i in range(count)], seed=12)
+    want = [plain_llama.generate_greedy(config, weights, p, 10) for p in prompts]
+    engine = _engine(model_folders["e"], dtype="bfloat16", use_cuda_graphs=True, max_requests=32, max_cache_tokens=4096, max_batch_tokens=256)
+    got = [r.generated_tokens for r in engine.generate(prompts, SamplingParams(max_tokens=10))]
+    for prompt, g, w in zip(prompts, got, want):
+        assert _agrees_up_to_near_ties(config, weights, prompt, g, w, 0.03)
+    assert count in engine._sessions
+    engine.runner.cache.check()
