@@ -26,7 +26,11 @@ template <int BN>
 struct GemmShape {
   static constexpr int kStageBytes = (kBM + BN) * kBK * 2;
   static constexpr int kStages = (220 * 1024 / kStageBytes) < 6 ? (220 * 1024 / kStageBytes) : 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  // staging boxes of the epilogue's bulk stores: two per warp where they fit beside the ring, else one
+  static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kStoreBoxBytes + 1280 <= 227 * 1024) ? 2 : 1;
+  static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kStoreBoxBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
   static constexpr int kAccStride = BN <= 128 ? 128 : 256;   // tensor memory is allocated in powers of two
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "the N of a tcgen05.mma with M = 128");
   static_assert(2 * kAccStride <= 512, "two accumulators must fit the 512 columns of tensor memory");
@@ -38,13 +42,15 @@ struct GemmShape {
 // [M, 2N] intermediate through memory disappear.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads)
-    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ out, int M,
-                        int N, int K, int* __restrict__ error_flag) {
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const __grid_constant__ CUtensorMap map_out, int staged, void* __restrict__ out, int M, int N, int K,
+                        int* __restrict__ error_flag) {
   using Shape = GemmShape<BN>;
   constexpr int kStages = Shape::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles need 1024-byte alignment
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kStages * Shape::kStageBytes);
+  uint8_t* staging = tiles + kStages * Shape::kStageBytes;   // [4 warps][kStoreBuffers] boxes of the epilogue's bulk stores
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + Shape::kStoreBytes);
   uint64_t* empty = full + kStages;
   uint64_t* accum_full = empty + kStages;     // [2]: the MMAs of a tile are done
   uint64_t* accum_empty = accum_full + 2;      // [2]: the epilogue has read the accumulator
@@ -82,24 +88,23 @@ __global__ void __launch_bounds__(kGemmThreads)
 
   if (warp == 0) {
     if (lane == 0) {   // TMA producer: one ring of stages across all of this CTA's tiles
-      int it = 0;
+      RingPosition<kStages> ring;
+      const uint32_t tiles_addr = smem_u32(tiles), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % m_blocks) * kBM, n0 = (tile / m_blocks) * kTileN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
-          ok = mbar_wait(&empty[s], phase ^ 1, abort_flag);
+        for (int kb = 0; kb < k_blocks; ++kb, ring.advance()) {
+          ok = mbar_wait(empty_addr + 8 * ring.stage, ring.phase ^ 1, abort_flag);
           if (!ok) break;
-          uint8_t* a_tile = tiles + s * Shape::kStageBytes;
-          uint8_t* b_tile = a_tile + kBM * kBK * 2;
-          mbar_expect_tx(&full[s], Shape::kStageBytes);
-          tma_load_2d(a_tile, &map_a, kb * kBK, m0, &full[s]);
+          const uint32_t a_tile = tiles_addr + ring.stage * Shape::kStageBytes, b_tile = a_tile + kBM * kBK * 2;
+          const uint32_t bar = full_addr + 8 * ring.stage;
+          mbar_expect_tx(bar, Shape::kStageBytes);
+          tma_load_2d(a_tile, &map_a, kb * kBK, m0, bar);
           if (EPI == 2) {
-            tma_load_2d(b_tile, &map_b, kb * kBK, n0, &full[s]);                                  // gate rows
-            tma_load_2d(b_tile + (BN / 2) * kBK * 2, &map_b, kb * kBK, N + n0, &full[s]);        // up rows
+            tma_load_2d(b_tile, &map_b, kb * kBK, n0, bar);                                  // gate rows
+            tma_load_2d(b_tile + (BN / 2) * kBK * 2, &map_b, kb * kBK, N + n0, bar);        // up rows
           } else {
-            tma_load_2d(b_tile, &map_b, kb * kBK, n0, &full[s]);
+            tma_load_2d(b_tile, &map_b, kb * kBK, n0, bar);
           }
         }
       }
@@ -107,7 +112,9 @@ __global__ void __launch_bounds__(kGemmThreads)
   } else if (warp == 1) {
     if (lane == 0) {   // MMA issuer
       constexpr uint32_t idesc = umma_instr_desc(kBM, BN);
-      int it = 0, local = 0;
+      RingPosition<kStages> ring;
+      const uint32_t tiles_low = umma_desc_low(smem_u32(tiles)), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
+      int local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
@@ -115,20 +122,18 @@ __global__ void __launch_bounds__(kGemmThreads)
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
-          ok = mbar_wait(&full[s], phase, abort_flag);
+        for (int kb = 0; kb < k_blocks; ++kb, ring.advance()) {
+          ok = mbar_wait(full_addr + 8 * ring.stage, ring.phase, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint32_t a_addr = smem_u32(tiles + s * Shape::kStageBytes);
-          const uint32_t b_addr = a_addr + kBM * kBK * 2;
+          // descriptors by their lower words, in 16-byte units: a stage further, then B behind A
+          const uint32_t a_low = tiles_low + ring.stage * (Shape::kStageBytes >> 4), b_low = a_low + ((kBM * kBK * 2) >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             // 16 k = 32 bytes further inside the 128-byte swizzle span
-            umma_bf16(tmem_acc, umma_smem_desc(a_addr + k * kUmmaK * 2), umma_smem_desc(b_addr + k * kUmmaK * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_acc, a_low + k * ((kUmmaK * 2) >> 4), b_low + k * ((kUmmaK * 2) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&empty[s]);   // the stage is free once these MMAs have read it
+          umma_commit(empty_addr + 8 * ring.stage);   // the stage is free once these MMAs have read it
         }
         if (ok) umma_commit(&accum_full[acc]);
       }
@@ -136,7 +141,7 @@ __global__ void __launch_bounds__(kGemmThreads)
   }
   if (warp >= 2) {   // epilogue: warp w reads tensor-memory lanes 32 * (w % 4) ... + 31
     const int sub = warp & 3;
-    int local = 0;
+    int local = 0, boxes = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       const int m0 = (tile % m_blocks) * kBM, n0 = (tile / m_blocks) * kTileN;
@@ -144,72 +149,18 @@ __global__ void __launch_bounds__(kGemmThreads)
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
-      if (EPI == 2) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t gate[16], up[16];
-          tmem_load_16(tmem_acc + c * 16, gate);
-          tmem_load_16(tmem_acc + BN / 2 + c * 16, up);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          const int col = n0 + c * 16;
-          if (row < M && col < N) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
-            float act[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              // gate and up are rounded to bfloat16 first, as when the product is stored and read back
-              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[i])));
-              const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[i])));
-              act[i] = (g / (1.0f + expf(-g))) * u;
-            }
-            if (col + 16 <= N && (N % 8) == 0) {
-              uint32_t packed[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                __nv_bfloat162 p = __floats2bfloat162_rn(act[2 * i], act[2 * i + 1]);
-                packed[i] = *reinterpret_cast<uint32_t*>(&p);
-              }
-              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-            } else {
-              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(act[i]);
-            }
-          }
-        }
+      if (EPI != 1 && staged) {
+        store_tile_staged<BN, EPI, Shape::kStoreBuffers>(tmem_acc, m0 + sub * 32, n0, M, N, &map_out,
+                                                         staging + sub * Shape::kStoreBuffers * kStoreBoxBytes, lane, boxes);
       } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 16; ++c) {
-          uint32_t r[16];
-          tmem_load_16(tmem_acc + c * 16, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          const int col = n0 + c * 16;
-          if (row < M && col < N) {
-            if (EPI == 0) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
-              if (col + 16 <= N && (N % 8) == 0) {
-                uint32_t packed[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                  packed[i] = *reinterpret_cast<uint32_t*>(&p);
-                }
-                *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-              } else {
-                for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
-              }
-            } else {
-              float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
-              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __uint_as_float(r[i]);
-            }
-          }
-        }
+        store_tile_direct<BN, EPI>(tmem_acc, row, n0, out, M, N);
       }
       // this warp is done with the accumulator: hand it back to the MMA issuer
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&accum_empty[acc])) : "memory");
     }
+    if (lane == 0) bulk_wait_all();   // this warp's staging boxes have been read and written out
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
   if (*abort_flag) {
@@ -225,9 +176,11 @@ __global__ void __launch_bounds__(kGemmThreads)
 
 template <int BN, int EPI>
 static int launch_gemm(const void* x, const void* w, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_out;
   // EPI 2: w has 2 N rows, fetched as two boxes of BN / 2 rows; N is the width of the output
   if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, EPI == 2 ? BN / 2 : BN)) return (int)cudaErrorInvalidValue;
+  const int staged = (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
+  if (!staged) map_out = map_a;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmShape<BN>::kSmemBytes);
@@ -243,7 +196,7 @@ static int launch_gemm(const void* x, const void* w, void* out, int M, int N, in
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
-  gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, GemmShape<BN>::kSmemBytes, stream>>>(map_a, map_b, out, M, N, K, error_flag);
+  gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, GemmShape<BN>::kSmemBytes, stream>>>(map_a, map_b, map_out, staged, out, M, N, K, error_flag);
   return (int)cudaGetLastError();
 }
 

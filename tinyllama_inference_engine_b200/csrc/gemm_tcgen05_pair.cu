@@ -28,28 +28,33 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 // a tile load of this CTA into its own shared memory whose bytes are counted on the leader's barrier
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(map), "r"(smem_u32(bar) & kLeaderWindow), "r"(x), "r"(y)
+// (shared-memory and barrier addresses are 32-bit addresses of this CTA's window)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(smem_dst),
+               "l"(map), "r"(bar & kLeaderWindow), "r"(x), "r"(y)
                : "memory");
 }
-__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// descriptors given by their lower words (umma_desc_low)
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint32_t a_low, uint32_t b_low, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
       "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "mov.b64 da, {%1, %5};\n"
+      "mov.b64 db, {%2, %5};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n"
       "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      "r"(a_low), "r"(b_low), "r"(idesc), "r"(accumulate), "r"(kUmmaDescHigh)
       : "memory");
 }
 // arrives on the barrier at this offset in both CTAs of the pair when the MMAs issued so far are done
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   const uint16_t both = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "h"(both)
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(bar), "h"(both)
                : "memory");
 }
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) { umma_commit_pair(smem_u32(bar)); }
 __device__ __forceinline__ void arrive_at_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & kLeaderWindow) : "memory");
 }
@@ -58,7 +63,11 @@ template <int BN>
 struct PairShape {
   static constexpr int kStageBytes = (kBM + BN / 2) * kBK * 2;   // per CTA: its rows of x and its half of the rows of w
   static constexpr int kStages = (220 * 1024 / kStageBytes) < 8 ? (220 * 1024 / kStageBytes) : 8;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  // staging boxes of the epilogue's bulk stores: two per warp where they fit beside the ring, else one
+  static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kStoreBoxBytes + 1280 <= 227 * 1024) ? 2 : 1;
+  static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kStoreBoxBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
   static constexpr int kAccStride = BN <= 128 ? 128 : 256;       // tensor memory is allocated in powers of two
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "each CTA holds BN / 2 rows of w, in groups of 8");
 };
@@ -66,13 +75,15 @@ struct PairShape {
 // EPI as in gemm_tcgen05.cu: 0 bfloat16 out, 1 32-bit out, 2 (BN = 256) w = [gate rows | up rows] and out = silu(gate) * up.
 template <int BN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
-    gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ out, int M, int N, int K,
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_out, int staged, void* __restrict__ out, int M, int N, int K,
                      int* __restrict__ error_flag) {
   using Shape = PairShape<BN>;
   constexpr int kStages = Shape::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles need 1024-byte alignment
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + kStages * Shape::kStageBytes);   // used in the leader only
+  uint8_t* staging = tiles + kStages * Shape::kStageBytes;   // [4 warps][kStoreBuffers] boxes of the epilogue's bulk stores
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + Shape::kStoreBytes);   // used in the leader only
   uint64_t* empty = full + kStages;
   uint64_t* accum_full = empty + kStages;      // [2]: the MMAs of a tile are done
   uint64_t* accum_empty = accum_full + 2;      // [2], used in the leader only: both CTAs' epilogues have read the accumulator
@@ -113,29 +124,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 
   if (warp == 0) {
     if (lane == 0) {   // TMA producer of this CTA: one ring of stages across all of the pair's tiles
-      int it = 0;
+      RingPosition<kStages> ring;
+      const uint32_t tiles_addr = smem_u32(tiles), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
         const int m0 = (tile % m_blocks) * 2 * kBM + rank * kBM, n0 = (tile / m_blocks) * kTileN;
         // this CTA's half of the tile's rows of w: rank 0 the first BN / 2 (the gate rows if gated), rank 1 the rest (the up rows)
         const int w_row = EPI == 2 ? rank * N + n0 : n0 + rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
-          ok = mbar_wait(&empty[s], phase ^ 1, abort_flag);
+        for (int kb = 0; kb < k_blocks; ++kb, ring.advance()) {
+          ok = mbar_wait(empty_addr + 8 * ring.stage, ring.phase ^ 1, abort_flag);
           if (!ok) break;
-          uint8_t* a_tile = tiles + s * Shape::kStageBytes;
-          uint8_t* b_tile = a_tile + kBM * kBK * 2;
-          if (rank == 0) mbar_expect_tx(&full[s], 2 * Shape::kStageBytes);   // this CTA's bytes and the peer's
-          tma_load_2d_pair(a_tile, &map_a, kb * kBK, m0, &full[s]);
-          tma_load_2d_pair(b_tile, &map_b, kb * kBK, w_row, &full[s]);
+          const uint32_t a_tile = tiles_addr + ring.stage * Shape::kStageBytes, b_tile = a_tile + kBM * kBK * 2;
+          const uint32_t bar = full_addr + 8 * ring.stage;
+          if (rank == 0) mbar_expect_tx(bar, 2 * Shape::kStageBytes);   // this CTA's bytes and the peer's
+          tma_load_2d_pair(a_tile, &map_a, kb * kBK, m0, bar);
+          tma_load_2d_pair(b_tile, &map_b, kb * kBK, w_row, bar);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {   // MMA issuer of the pair
       constexpr uint32_t idesc = umma_instr_desc(2 * kBM, BN);
-      int it = 0, local = 0;
+      RingPosition<kStages> ring;
+      const uint32_t tiles_low = umma_desc_low(smem_u32(tiles)), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
+      int local = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++local) {
         const int acc = local & 1;
@@ -143,19 +155,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
-          ok = mbar_wait(&full[s], phase, abort_flag);
+        for (int kb = 0; kb < k_blocks; ++kb, ring.advance()) {
+          ok = mbar_wait(full_addr + 8 * ring.stage, ring.phase, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint32_t a_addr = smem_u32(tiles + s * Shape::kStageBytes);
-          const uint32_t b_addr = a_addr + kBM * kBK * 2;
+          // descriptors by their lower words, in 16-byte units: a stage further, then B behind A
+          const uint32_t a_low = tiles_low + ring.stage * (Shape::kStageBytes >> 4), b_low = a_low + ((kBM * kBK * 2) >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
-            umma_bf16_pair(tmem_acc, umma_smem_desc(a_addr + k * kUmmaK * 2), umma_smem_desc(b_addr + k * kUmmaK * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_pair(tmem_acc, a_low + k * ((kUmmaK * 2) >> 4), b_low + k * ((kUmmaK * 2) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit_pair(&empty[s]);   // the stage is free in both CTAs once these MMAs have read it
+          umma_commit_pair(empty_addr + 8 * ring.stage);   // the stage is free in both CTAs once these MMAs have read it
         }
         if (ok) umma_commit_pair(&accum_full[acc]);
       }
@@ -163,7 +173,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
   }
   if (warp >= 2) {   // epilogue: warp w reads tensor-memory lanes 32 * (w % 4) ... + 31 of this CTA's 128 rows
     const int sub = warp & 3;
-    int local = 0;
+    int local = 0, boxes = 0;
     for (int tile = pair; tile < num_tiles; tile += pairs, ++local) {
       const int acc = local & 1;
       const int m0 = (tile % m_blocks) * 2 * kBM + rank * kBM, n0 = (tile / m_blocks) * kTileN;
@@ -171,72 +181,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
-      if (EPI == 2) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t gate[16], up[16];
-          tmem_load_16(tmem_acc + c * 16, gate);
-          tmem_load_16(tmem_acc + BN / 2 + c * 16, up);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          const int col = n0 + c * 16;
-          if (row < M && col < N) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
-            float act[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              // gate and up are rounded to bfloat16 first, as when the product is stored and read back
-              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[i])));
-              const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[i])));
-              act[i] = (g / (1.0f + expf(-g))) * u;
-            }
-            if (col + 16 <= N && (N % 8) == 0) {
-              uint32_t packed[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                __nv_bfloat162 p = __floats2bfloat162_rn(act[2 * i], act[2 * i + 1]);
-                packed[i] = *reinterpret_cast<uint32_t*>(&p);
-              }
-              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-            } else {
-              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(act[i]);
-            }
-          }
-        }
+      if (EPI != 1 && staged) {
+        store_tile_staged<BN, EPI, Shape::kStoreBuffers>(tmem_acc, m0 + sub * 32, n0, M, N, &map_out,
+                                                         staging + sub * Shape::kStoreBuffers * kStoreBoxBytes, lane, boxes);
       } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 16; ++c) {
-          uint32_t r[16];
-          tmem_load_16(tmem_acc + c * 16, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          const int col = n0 + c * 16;
-          if (row < M && col < N) {
-            if (EPI == 0) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
-              if (col + 16 <= N && (N % 8) == 0) {
-                uint32_t packed[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                  packed[i] = *reinterpret_cast<uint32_t*>(&p);
-                }
-                *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-              } else {
-                for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
-              }
-            } else {
-              float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
-              for (int i = 0; i < 16 && col + i < N; ++i) dst[i] = __uint_as_float(r[i]);
-            }
-          }
-        }
+        store_tile_direct<BN, EPI>(tmem_acc, row, n0, out, M, N);
       }
       // this warp is done with the accumulator: tell the pair's MMA issuer
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) arrive_at_leader(&accum_empty[acc]);
     }
+    if (lane == 0) bulk_wait_all();   // this warp's staging boxes have been read and written out
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
   if (*abort_flag) {
@@ -253,9 +209,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
 
 template <int BN, int EPI>
 static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_out;
   // each CTA fetches boxes of 128 rows of x and BN / 2 rows of w (gated: w has 2 N rows, one CTA takes gate rows, the other up rows)
   if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, BN / 2)) return (int)cudaErrorInvalidValue;
+  const int staged = (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
+  if (!staged) map_out = map_a;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairShape<BN>::kSmemBytes);
@@ -271,7 +229,7 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   const int pairs = num_tiles < sm_count / 2 ? num_tiles : sm_count / 2;
-  gemm_pair_kernel<BN, EPI><<<dim3(2 * pairs), kGemmThreads, PairShape<BN>::kSmemBytes, stream>>>(map_a, map_b, out, M, N, K, error_flag);
+  gemm_pair_kernel<BN, EPI><<<dim3(2 * pairs), kGemmThreads, PairShape<BN>::kSmemBytes, stream>>>(map_a, map_b, map_out, staged, out, M, N, K, error_flag);
   return (int)cudaGetLastError();
 }
 

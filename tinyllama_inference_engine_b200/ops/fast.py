@@ -148,11 +148,13 @@ use_sm_pairs = True
 
 
 def gemm_tile_width(M: int, N: int, pair: bool = False) -> int:
-    """The tile width whose waves of persistent CTAs (or pairs of them) cost least: waves x width, the wider tile on a tie
-    (it reads x less often)."""
+    """The tile width whose waves of persistent CTAs (or pairs of them) cost least.
+
+    A tile costs its width plus a fixed part about as large as 300 columns (measured: a 128 x 160 tile takes 0.8 of the time
+    of a 128 x 256 one), so the widest tile wins unless a narrower one saves a whole wave; the wider tile on a tie."""
     workers = SM_COUNT // 2 if pair else SM_COUNT
     row_blocks = -(-M // (256 if pair else 128))
-    return min(GEMM_TILE_WIDTHS, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * width, -width))
+    return min(GEMM_TILE_WIDTHS, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * (width + 300), -width))
 
 
 def gemm_tcgen05(x, weight, out, tile_n: int | None = None, pair: bool | None = None) -> None:
