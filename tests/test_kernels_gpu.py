@@ -440,6 +440,13 @@ def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, wind
     for h in range(q_heads):
         qv = qkv.view(qkv.shape[0], -1, head_dim)[row, h].float()
         pages[page, 0, h // (q_heads // kv_heads), slot] = (qv * (6.0 * head_dim ** 0.5 / float(qv.norm()) ** 2)).bfloat16()
+    # A score far above everything before it, many key tiles into a row (request 9, position 588, key 568): the kernel keeps its
+    # running output in tensor memory against a reference maximum and must rescale it there when the maximum jumps.
+    late_row = sum(q_lens[:9]) + 100
+    page, slot = int(table[9, 568 // page_size]), 568 % page_size
+    for h in range(q_heads):
+        qv = qkv.view(qkv.shape[0], -1, head_dim)[late_row, h].float()
+        pages[page, 0, h // (q_heads // kv_heads), slot] = (qv * (16.0 * head_dim ** 0.5 / float(qv.norm()) ** 2)).bfloat16()
     tokens = qkv.shape[0]
     want = torch.empty(tokens, q_heads * head_dim, dtype=torch.bfloat16)
     plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)

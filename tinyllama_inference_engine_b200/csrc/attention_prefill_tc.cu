@@ -15,9 +15,7 @@
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and tensor-memory owner, warps 2..5 softmax (128 threads).
 // Every mbarrier wait is bounded; on a timeout the CTA raises `error_flag`, stops, lets copies land, frees its tensor
 // memory and returns.  Needs page_size % 64 == 0; other shapes use the mma.sync kernel.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05_utils.cuh"
 
 namespace tlie {
 
@@ -26,72 +24,15 @@ constexpr int kRowsTC = 128;      // query rows per CTA
 constexpr int kKeysTC = 64;       // keys per tile (one box)
 constexpr int kKvStages = 3;
 constexpr int kThreadsTC = 192;
-constexpr long long kWaitLimitTC = 1ll << 20;
 constexpr float kLog2eTC = 1.4426950408889634f;
+// The running output stays in tensor memory and is rescaled only when a row's maximum has grown by more than this many
+// powers of two since its reference was set: until then the probabilities are taken against the old reference and are at
+// most 2^kLazyRescale, which bfloat16 and the 32-bit sum hold without loss.
+constexpr float kLazyRescale = 8.0f;
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void bar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ bool bar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(done)
-      : "r"(smem_addr(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (long long i = 0; i < kWaitLimitTC; ++i) {
-    if (bar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-__device__ __forceinline__ void tma_box_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(smem_addr(smem_dst)),
-               "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
-               : "memory");
-}
-// 128-byte-swizzled tile of 128-byte rows, 8-row groups 1024 bytes apart (both the K-major and the MN-major use).
-__device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
-  uint64_t desc = 0;
-  desc |= (uint64_t)((addr >> 4) & 0x3FFF);
-  desc |= (uint64_t)1 << 16;
-  desc |= (uint64_t)(1024 >> 4) << 32;
-  desc |= (uint64_t)1 << 46;
-  desc |= (uint64_t)2 << 61;
-  return desc;
-}
-// bf16 x bf16 -> f32, A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), tile m x n.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n, int b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
+// bf16 x bf16 -> f32, A K-major, B MN-major (V stays [key][dim], as the cache stores it), tile m x n.
+__host__ __device__ constexpr uint32_t instr_desc_b_mn(int m, int n) { return umma_instr_desc(m, n) | (1u << 16); }
+
 // 64 consecutive 32-bit columns of this thread's lane: four loads in flight, one wait.
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
   uint32_t r[64];
@@ -109,13 +50,28 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
   for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The reverse: 64 columns of this thread's lane written from registers (and waited for).
+__device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[64]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr + c * 16),
+        "r"(__float_as_uint(v[c * 16 + 0])), "r"(__float_as_uint(v[c * 16 + 1])), "r"(__float_as_uint(v[c * 16 + 2])), "r"(__float_as_uint(v[c * 16 + 3])),
+        "r"(__float_as_uint(v[c * 16 + 4])), "r"(__float_as_uint(v[c * 16 + 5])), "r"(__float_as_uint(v[c * 16 + 6])), "r"(__float_as_uint(v[c * 16 + 7])),
+        "r"(__float_as_uint(v[c * 16 + 8])), "r"(__float_as_uint(v[c * 16 + 9])), "r"(__float_as_uint(v[c * 16 + 10])), "r"(__float_as_uint(v[c * 16 + 11])),
+        "r"(__float_as_uint(v[c * 16 + 12])), "r"(__float_as_uint(v[c * 16 + 13])), "r"(__float_as_uint(v[c * 16 + 14])), "r"(__float_as_uint(v[c * 16 + 15]))
+        : "memory");
+  }
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+
 struct SmemTC {
   // all tiles are 1024-byte aligned (the struct is placed on a 1024-byte boundary)
   __nv_bfloat16 q[kRowsTC * kD];                     // 16 KB
   __nv_bfloat16 k[kKvStages][kKeysTC * kD];          // 8 KB each
   __nv_bfloat16 v[kKvStages][kKeysTC * kD];          // 8 KB each
   __nv_bfloat16 p[2][kRowsTC * kKeysTC];             // 16 KB each
-  uint64_t q_full, q_empty, kv_full[kKvStages], kv_empty[kKvStages], s_full[2], s_empty[2], p_full[2], pv_full, pv_empty;
+  uint64_t q_full, q_empty, kv_full[kKvStages], kv_empty[kKvStages], s_full[2], s_empty[2], p_full[2], pv_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -136,7 +92,7 @@ __global__ void __launch_bounds__(kThreadsTC)
   const int* item = tiles + (size_t)blockIdx.x * 4;
   const int head = blockIdx.y;
   const int kvh = head / (q_heads / kv_heads);
-  constexpr int kTmemCols = 256;   // S0 [0,64), S1 [64,128), PV [128,192)
+  constexpr int kTmemCols = 256;   // S0 [0,64), S1 [64,128), O of the first row tile [128,192), of the second [192,256)
 
   struct RowTile {
     int row0, rows_here, pos0, n_keys, first_kt, num_kt;
@@ -163,25 +119,24 @@ __global__ void __launch_bounds__(kThreadsTC)
   };
 
   if (threadIdx.x == 0) {
-    bar_init(&sm.q_full, 1);
-    bar_init(&sm.q_empty, 1);
+    mbar_init(&sm.q_full, 1);
+    mbar_init(&sm.q_empty, 1);
     for (int s = 0; s < kKvStages; ++s) {
-      bar_init(&sm.kv_full[s], 1);
-      bar_init(&sm.kv_empty[s], 1);
+      mbar_init(&sm.kv_full[s], 1);
+      mbar_init(&sm.kv_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
-      bar_init(&sm.s_full[b], 1);
-      bar_init(&sm.s_empty[b], 4);   // one arrival per softmax warp
-      bar_init(&sm.p_full[b], 4);
+      mbar_init(&sm.s_full[b], 1);
+      mbar_init(&sm.s_empty[b], 4);   // one arrival per softmax warp
+      mbar_init(&sm.p_full[b], 4);
     }
-    bar_init(&sm.pv_full, 1);
-    bar_init(&sm.pv_empty, 4);
+    mbar_init(&sm.pv_full, 1);
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&sm.tmem_base)), "r"(kTmemCols));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -192,44 +147,51 @@ __global__ void __launch_bounds__(kThreadsTC)
   // g counts key tiles over both row tiles: every ring (kv stages, the two S / P buffers, the P.V buffer) is indexed by it.
   if (warp == 0) {
     if (lane == 0) {   // TMA producer: per row tile Q once, then one K box and one V box per key tile
-      int g = 0;
+      RingPosition<kKvStages> ring;
+      const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), full_addr = smem_u32(sm.kv_full), empty_addr = smem_u32(sm.kv_empty);
       bool ok = true;
       for (int u = 0; u < 2 && ok; ++u) {
         const RowTile t = row_tile(u);
         if (t.num_kt == 0) continue;
-        if (u > 0) ok = bar_wait(&sm.q_empty, 0, abort_flag);   // the first row tile's score products have read Q
+        if (u > 0) ok = mbar_wait(&sm.q_empty, 0, abort_flag);   // the first row tile's score products have read Q
         if (!ok) break;
-        bar_expect_tx(&sm.q_full, kRowsTC * kD * 2);
-        tma_box_2d(sm.q, &map_q, head * kD, t.row0, &sm.q_full);
-        for (int j = 0; j < t.num_kt; ++j, ++g) {
-          const int s = g % kKvStages;
-          ok = bar_wait(&sm.kv_empty[s], ((g / kKvStages) & 1) ^ 1, abort_flag);
+        mbar_expect_tx(&sm.q_full, kRowsTC * kD * 2);
+        tma_load_2d(sm.q, &map_q, head * kD, t.row0, &sm.q_full);
+        for (int j = 0; j < t.num_kt; ++j, ring.advance()) {
+          ok = mbar_wait(empty_addr + 8 * ring.stage, ring.phase ^ 1, abort_flag);
           if (!ok) break;
           const int key0 = (t.first_kt + j) * kKeysTC;
           const int page = t.table[key0 / page_size];
           const int in_page = key0 % page_size;
           const int k_row = ((page * 2 + 0) * kv_heads + kvh) * page_size + in_page;   // row of the [rows, 64] view of the pool
           const int v_row = ((page * 2 + 1) * kv_heads + kvh) * page_size + in_page;
-          bar_expect_tx(&sm.kv_full[s], 2 * kKeysTC * kD * 2);
-          tma_box_2d(sm.k[s], &map_kv, 0, k_row, &sm.kv_full[s]);
-          tma_box_2d(sm.v[s], &map_kv, 0, v_row, &sm.kv_full[s]);
+          const uint32_t bar = full_addr + 8 * ring.stage;
+          mbar_expect_tx(bar, 2 * kKeysTC * kD * 2);
+          tma_load_2d(k_addr + ring.stage * (kKeysTC * kD * 2), &map_kv, 0, k_row, bar);
+          tma_load_2d(v_addr + ring.stage * (kKeysTC * kD * 2), &map_kv, 0, v_row, bar);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {   // MMA issuer
-      constexpr uint32_t idesc_s = instr_desc(kRowsTC, kKeysTC, 0);    // S = Q . K^T   (B = K tile, K-major)
-      constexpr uint32_t idesc_pv = instr_desc(kRowsTC, kD, 1);        // PV = P . V    (B = V tile, MN-major)
-      const uint32_t q_addr = smem_addr(sm.q);
+      constexpr uint32_t idesc_s = umma_instr_desc(kRowsTC, kKeysTC);      // S = Q . K^T   (B = K tile, K-major)
+      constexpr uint32_t idesc_pv = instr_desc_b_mn(kRowsTC, kD);          // O += P . V    (B = V tile, MN-major)
+      constexpr uint32_t kTileLow = (kKeysTC * kD * 2) >> 4;               // one K or V tile further, in descriptor units
+      const uint32_t q_low = umma_desc_low(smem_u32(sm.q)), k_low = umma_desc_low(smem_u32(sm.k)), v_low = umma_desc_low(smem_u32(sm.v));
+      const uint32_t p_low = umma_desc_low(smem_u32(sm.p));
+      const uint32_t kv_full = smem_u32(sm.kv_full), kv_empty = smem_u32(sm.kv_empty), s_full = smem_u32(sm.s_full), s_empty = smem_u32(sm.s_empty);
+      const uint32_t p_full = smem_u32(sm.p_full), pv_full = smem_u32(&sm.pv_full);
+      RingPosition<kKvStages> s_ring, pv_ring;   // the stage whose scores are issued next / whose P . V is issued next
       auto issue_s = [&](int g) {   // scores of key tile g into S buffer g & 1
-        const int s = g % kKvStages, b = g & 1;
-        if (!bar_wait(&sm.kv_full[s], (g / kKvStages) & 1, abort_flag)) return false;
-        if (!bar_wait(&sm.s_empty[b], ((g >> 1) & 1) ^ 1, abort_flag)) return false;
+        const uint32_t b = g & 1;
+        if (!mbar_wait(kv_full + 8 * s_ring.stage, s_ring.phase, abort_flag)) return false;
+        if (!mbar_wait(s_empty + 8 * b, ((g >> 1) & 1) ^ 1, abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t k_addr = smem_addr(sm.k[s]);
+        const uint32_t k_tile = k_low + s_ring.stage * kTileLow;
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) mma_ss(tmem + b * kKeysTC, tile_desc(q_addr + kk * 32), tile_desc(k_addr + kk * 32), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(&sm.s_full[b]);
+        for (int kk = 0; kk < kD / 16; ++kk) umma_bf16(tmem + b * kKeysTC, q_low + kk * 2, k_tile + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+        umma_commit(s_full + 8 * b);
+        s_ring.advance();
         return true;
       };
       int g = 0, q_phase = 0;
@@ -237,26 +199,27 @@ __global__ void __launch_bounds__(kThreadsTC)
       for (int u = 0; u < 2 && ok; ++u) {
         const RowTile t = row_tile(u);
         if (t.num_kt == 0) continue;
-        ok = bar_wait(&sm.q_full, q_phase, abort_flag);
+        ok = mbar_wait(&sm.q_full, q_phase, abort_flag);
         q_phase ^= 1;
         if (ok) ok = issue_s(g);
-        for (int j = 0; j < t.num_kt && ok; ++j, ++g) {
+        const uint32_t tmem_o = tmem + (2 + u) * kKeysTC;   // this row tile's running output
+        for (int j = 0; j < t.num_kt && ok; ++j, ++g, pv_ring.advance()) {
           if (j + 1 < t.num_kt) {
             ok = issue_s(g + 1);   // the next tile's scores run under this tile's softmax
           } else {
-            mma_commit(&sm.q_empty);   // all score products of this row tile are issued: Q may be replaced when they are done
+            umma_commit(&sm.q_empty);   // all score products of this row tile are issued: Q may be replaced when they are done
           }
           if (!ok) break;
-          const int s = g % kKvStages, b = g & 1;
-          ok = bar_wait(&sm.p_full[b], (g >> 1) & 1, abort_flag) && bar_wait(&sm.pv_empty, (g & 1) ^ 1, abort_flag);
+          const uint32_t b = g & 1;
+          ok = mbar_wait(p_full + 8 * b, (g >> 1) & 1, abort_flag);   // P is written (and O rescaled, if it had to be)
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint32_t p_addr = smem_addr(sm.p[b]), v_addr = smem_addr(sm.v[s]);
+          const uint32_t p_tile = p_low + b * ((kRowsTC * kKeysTC * 2) >> 4), v_tile = v_low + pv_ring.stage * kTileLow;
 #pragma unroll
           for (int kk = 0; kk < kKeysTC / 16; ++kk)   // 16 keys further: 32 bytes inside P's rows, 16 rows (2048 bytes) down in V
-            mma_ss(tmem + 2 * kKeysTC, tile_desc(p_addr + kk * 32), tile_desc(v_addr + kk * 16 * kD * 2), idesc_pv, kk > 0 ? 1u : 0u);
-          mma_commit(&sm.pv_full);
-          mma_commit(&sm.kv_empty[s]);   // both products of this stage are done when this fires
+            umma_bf16(tmem_o, p_tile + kk * 2, v_tile + kk * ((16 * kD * 2) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(pv_full);
+          umma_commit(kv_empty + 8 * pv_ring.stage);   // both products of this stage are done when this fires
         }
       }
     }
@@ -272,28 +235,13 @@ __global__ void __launch_bounds__(kThreadsTC)
       if (t.num_kt == 0) continue;
       const int my_pos = t.pos0 + min(row, t.rows_here - 1);   // rows past the end behave like the last row; never stored
       const int my_lo = (window > 0 && my_pos - window + 1 > 0) ? my_pos - window + 1 : 0;
-      float o[kD];
-#pragma unroll
-      for (int i = 0; i < kD; ++i) o[i] = 0.0f;
-      float row_max = -INFINITY, row_sum = 0.0f;
-      float pending_alpha = 1.0f;   // the factor that belongs to the product P . V still in flight
-      // O = O * alpha + (P . V of key tile gg): read one tile late, so that the product runs under the next tile's softmax
-      auto absorb_pv = [&](int gg) {
-        if (!bar_wait(&sm.pv_full, gg & 1, abort_flag)) return false;
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        float pv[kD];
-        tmem_ld64(tmem + lane_base + 2 * kKeysTC, pv);
-#pragma unroll
-        for (int i = 0; i < kD; ++i) o[i] = fmaf(o[i], pending_alpha, pv[i]);
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        __syncwarp();
-        if (lane == 0) bar_arrive(&sm.pv_empty);
-        return true;
-      };
+      const uint32_t tmem_o = tmem + lane_base + (2 + u) * kKeysTC;
+      // The row's reference maximum (times scale * log2 e) that the exponents are taken against, and the sum against it.
+      float reference = -INFINITY, row_sum = 0.0f;
       for (int j = 0; j < t.num_kt && ok; ++j, ++g) {
-        const int b = g & 1, s = g % kKvStages;
+        const int b = g & 1;
         const int key0 = (t.first_kt + j) * kKeysTC;
-        ok = bar_wait(&sm.s_full[b], (g >> 1) & 1, abort_flag);
+        ok = mbar_wait(&sm.s_full[b], (g >> 1) & 1, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         float sc[kKeysTC];
@@ -301,7 +249,7 @@ __global__ void __launch_bounds__(kThreadsTC)
         // S_b has been read: the issuer may overwrite it with key tile g + 2
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
         __syncwarp();
-        if (lane == 0) bar_arrive(&sm.s_empty[b]);
+        if (lane == 0) mbar_arrive(&sm.s_empty[b]);
         const bool need_mask = key0 + kKeysTC - 1 > t.pos0 || (window > 0 && key0 < t.pos0 + t.rows_here - window);
         float tile_max = -INFINITY;
         if (need_mask) {
@@ -315,11 +263,28 @@ __global__ void __launch_bounds__(kThreadsTC)
 #pragma unroll
           for (int i = 0; i < kKeysTC; ++i) tile_max = fmaxf(tile_max, sc[i]);
         }
-        const float new_max = fmaxf(row_max, tile_max);
-        const float finite_max = (new_max == -INFINITY) ? 0.0f : new_max;
-        const float base = finite_max * sl2;
-        const float alpha = exp2f((row_max - finite_max) * sl2);
-        row_max = new_max;
+        const float scaled_max = tile_max * sl2;
+        if (j == 0) {
+          reference = scaled_max;   // nothing accumulated yet: the first product overwrites O
+        } else {
+          // O (in tensor memory) and the sum are taken against `reference`.  They are brought to a new one only when this
+          // tile's maximum is far above it; the loads and stores are warp-wide, rows that need nothing multiply by one.
+          const bool grown = scaled_max > reference + kLazyRescale;
+          if (__any_sync(0xffffffffu, grown)) {
+            ok = mbar_wait(&sm.pv_full, (g - 1) & 1, abort_flag);   // the product that last added to O is done
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const float alpha = grown ? exp2f(reference - scaled_max) : 1.0f;
+            float o[kD];
+            tmem_ld64(tmem_o, o);
+#pragma unroll
+            for (int i = 0; i < kD; ++i) o[i] *= alpha;
+            tmem_st64(tmem_o, o);
+            row_sum *= alpha;
+            if (grown) reference = scaled_max;
+          }
+        }
+        const float base = (reference == -INFINITY) ? 0.0f : reference;   // a row that has seen no key yet: every p is 0
         uint32_t packed[kKeysTC / 2];
         float sum = 0.0f;
 #pragma unroll
@@ -327,16 +292,9 @@ __global__ void __launch_bounds__(kThreadsTC)
           const float p0 = exp2_approx(fmaf(sc[2 * i], sl2, -base));
           const float p1 = exp2_approx(fmaf(sc[2 * i + 1], sl2, -base));
           sum += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          packed[i] = *reinterpret_cast<uint32_t*>(&h);
+          packed[i] = pack_bf16(p0, p1);
         }
-        row_sum = row_sum * alpha + sum;
-        // the previous tile's product has had this tile's softmax to finish: take it in before its buffer is reused
-        if (j > 0) {
-          ok = absorb_pv(g - 1);
-          if (!ok) break;
-        }
-        pending_alpha = alpha;
+        row_sum += sum;
         // P as bfloat16 into the swizzled K-major tile: row r at (r / 8) * 1024 + (r % 8) * 128, 16-byte chunk c at c ^ (r % 8)
         uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p[b]) + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
@@ -346,28 +304,27 @@ __global__ void __launch_bounds__(kThreadsTC)
         // so that 0 * (whatever is there) stays 0.  A V row is 128 contiguous bytes whatever the swizzle.
         if (key0 + kKeysTC > t.n_keys) {
           const int first_bad = t.n_keys - key0;
-          for (int r = first_bad + (row >> 3); r < kKeysTC; r += kRowsTC / 8) {
-            uint8_t* v_row = reinterpret_cast<uint8_t*>(sm.v[s]) + (r >> 3) * 1024 + (r & 7) * 128;
-            *reinterpret_cast<uint4*>(v_row + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
-          }
+          uint8_t* v_tile = reinterpret_cast<uint8_t*>(sm.v[g % kKvStages]);
+          for (int r = first_bad + (row >> 3); r < kKeysTC; r += kRowsTC / 8)
+            *reinterpret_cast<uint4*>(v_tile + (r >> 3) * 1024 + (r & 7) * 128 + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");   // and a rescaled O before the product that adds to it
         __syncwarp();
-        if (lane == 0) bar_arrive(&sm.p_full[b]);
+        if (lane == 0) mbar_arrive(&sm.p_full[b]);
       }
-      if (ok) ok = absorb_pv(g - 1);
-      if (ok && row < t.rows_here) {
-        const float inv = 1.0f / row_sum;
-        __nv_bfloat16* dst = out + ((size_t)(t.row0 + row) * q_heads + head) * kD;
+      if (ok) ok = mbar_wait(&sm.pv_full, (g - 1) & 1, abort_flag);   // the row tile's last product
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        float o[kD];
+        tmem_ld64(tmem_o, o);
+        if (row < t.rows_here) {
+          const float inv = 1.0f / row_sum;
+          __nv_bfloat16* dst = out + ((size_t)(t.row0 + row) * q_heads + head) * kD;
 #pragma unroll
-        for (int c = 0; c < kD / 8; ++c) {
-          uint32_t packed[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
-            packed[i] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          for (int c = 0; c < kD / 8; ++c)
+            *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv), pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                                               pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
         }
       }
     }
@@ -383,21 +340,9 @@ __global__ void __launch_bounds__(kThreadsTC)
   }
 }
 
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                             const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeFn encoder() {
-  static EncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* found = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &status) == cudaSuccess && status == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeFn>(found);
-  }
-  return fn;
-}
 // [rows, width] bfloat16 with a row stride in elements, boxes of box_rows x 64, 128-byte swizzle.
 static bool make_map_2d(CUtensorMap* map, const void* base, long long rows, long long width, long long row_stride, int box_rows) {
-  EncodeFn fn = encoder();
+  EncodeTiledFn fn = encode_tiled();
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
