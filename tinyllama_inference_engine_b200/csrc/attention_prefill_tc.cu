@@ -143,6 +143,10 @@ __global__ void __launch_bounds__(kThreadsTC)
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem = sm.tmem_base;
+  // Programmatic dependent launch: the CTA is set up (barriers, tensor memory) while the kernel before it in the stream still
+  // runs; nothing of global memory is touched before the wait, which returns when that kernel has completed.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   // g counts key tiles over both row tiles: every ring (kv stages, the two S / P buffers, the P.V buffer) is indexed by it.
   if (warp == 0) {
@@ -379,7 +383,6 @@ TLIE_EXPORT int tlie_prefill_attention_tc(const void* q, int q_row_stride, int t
     configured = true;
   }
   dim3 grid(n_tiles, q_heads);
-  prefill_attention_tc_kernel<<<grid, kThreadsTC, smem, stream>>>(map_q, map_kv, tiles, seq_starts, first_positions, block_table, table_stride,
-                                                                  (__nv_bfloat16*)out, q_heads, kv_heads, page_size, window, scale, error_flag);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(prefill_attention_tc_kernel, grid, dim3(kThreadsTC), (size_t)smem, stream, map_q, map_kv, tiles, seq_starts, first_positions,
+                         block_table, table_stride, (__nv_bfloat16*)out, q_heads, kv_heads, page_size, window, scale, error_flag);
 }

@@ -82,6 +82,8 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_vec_kernel(float* __
                                                                      const int* __restrict__ rows, const float* __restrict__ weight,
                                                                      float eps, T* __restrict__ out, int hidden) {
   __shared__ float scratch[32];
+  grid_launch_dependents();   // launched as a programmatic dependent: the kernel before it has completed when the wait returns
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* x = residual + (size_t)src * hidden;
@@ -183,11 +185,10 @@ TLIE_EXPORT int tlie_add_rmsnorm(int dtype, float* residual, const void* delta, 
   if (hidden % 4 == 0 && hidden <= kNormThreads * kNormChunks * 4) {
     // The order of a row's sum differs from the scalar kernel's but is still a function of the row alone.
     if (dtype == TLIE_F32)
-      add_rmsnorm_vec_kernel<float><<<out_rows, kNormThreads, 0, stream>>>(residual, (const float*)delta, rows, weight, eps, (float*)out, hidden);
-    else
-      add_rmsnorm_vec_kernel<__nv_bfloat16><<<out_rows, kNormThreads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, rows, weight, eps,
-                                                                                (__nv_bfloat16*)out, hidden);
-    return (int)cudaGetLastError();
+      return (int)launch_pdl(add_rmsnorm_vec_kernel<float>, dim3(out_rows), dim3(kNormThreads), 0, stream, residual, (const float*)delta, rows, weight, eps,
+                             (float*)out, hidden);
+    return (int)launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(out_rows), dim3(kNormThreads), 0, stream, residual, (const __nv_bfloat16*)delta, rows,
+                           weight, eps, (__nv_bfloat16*)out, hidden);
   }
   const int block = hidden >= 1024 ? 256 : 128;
   if (dtype == TLIE_F32)

@@ -85,6 +85,10 @@ __global__ void __launch_bounds__(kGemmThreads)
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
+  // Programmatic dependent launch: the CTA is set up (barriers, tensor memory) while the kernel before it in the stream still
+  // runs; nothing of global memory is touched before the wait, which returns when that kernel has completed.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {   // TMA producer: one ring of stages across all of this CTA's tiles
@@ -196,8 +200,8 @@ static int launch_gemm(const void* x, const void* w, void* out, int M, int N, in
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
-  gemm_tcgen05_kernel<BN, EPI><<<grid, kGemmThreads, GemmShape<BN>::kSmemBytes, stream>>>(map_a, map_b, map_out, staged, out, M, N, K, error_flag);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(gemm_tcgen05_kernel<BN, EPI>, grid, dim3(kGemmThreads), GemmShape<BN>::kSmemBytes, stream, map_a, map_b, map_out, staged, out, M, N, K,
+                         error_flag);
 }
 
 }  // namespace tlie

@@ -121,6 +121,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
   cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
+  // Programmatic dependent launch: the CTA is set up (barriers, tensor memory) while the kernel before it in the stream still
+  // runs; nothing of global memory is touched before the wait, which returns when that kernel has completed.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {   // TMA producer of this CTA: one ring of stages across all of the pair's tiles
@@ -229,8 +233,8 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   const int pairs = num_tiles < sm_count / 2 ? num_tiles : sm_count / 2;
-  gemm_pair_kernel<BN, EPI><<<dim3(2 * pairs), kGemmThreads, PairShape<BN>::kSmemBytes, stream>>>(map_a, map_b, map_out, staged, out, M, N, K, error_flag);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(gemm_pair_kernel<BN, EPI>, dim3(2 * pairs), dim3(kGemmThreads), PairShape<BN>::kSmemBytes, stream, map_a, map_b, map_out, staged, out,
+                         M, N, K, error_flag);
 }
 
 }  // namespace tlie

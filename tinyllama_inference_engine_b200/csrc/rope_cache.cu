@@ -121,6 +121,8 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int
                                       const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq, int rotary_dim,
                                       __nv_bfloat16* __restrict__ pages, int q_heads, int kv_heads, int head_dim, int page_size, int write_cache) {
   __shared__ float cos_s[kMaxRotaryHalf], sin_s[kMaxRotaryHalf];
+  grid_launch_dependents();   // launched as a programmatic dependent: the kernel before it has completed when the wait returns
+  grid_dependency_wait();
   const int t = blockIdx.x;
   const int row_width = (q_heads + 2 * kv_heads) * head_dim;
   __nv_bfloat16* row = qkv + (size_t)t * row_width;
@@ -209,9 +211,8 @@ TLIE_EXPORT int tlie_rope_store(int dtype, void* qkv, const int* positions, cons
   const int block = 256;
   const int half = rotary_dim / 2;
   if (dtype != TLIE_F32 && half % 8 == 0 && head_dim % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)pages & 15) == 0) {
-    rope_store_vec_kernel<<<tokens, block, 0, stream>>>((__nv_bfloat16*)qkv, positions, token_seq, block_table, table_stride, inv_freq, rotary_dim,
-                                                        (__nv_bfloat16*)pages, q_heads, kv_heads, head_dim, page_size, write_cache);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(rope_store_vec_kernel, dim3(tokens), dim3(block), 0, stream, (__nv_bfloat16*)qkv, positions, token_seq, block_table, table_stride,
+                           inv_freq, rotary_dim, (__nv_bfloat16*)pages, q_heads, kv_heads, head_dim, page_size, write_cache);
   }
   if (dtype == TLIE_F32)
     rope_store_kernel<float><<<tokens, block, 0, stream>>>((float*)qkv, positions, token_seq, block_table,
