@@ -79,14 +79,15 @@ def test_step_refuses_bad_batches(model_folders, monkeypatch):
     runner.cache.check()
 
 
-def test_plain_products_with_few_tiles_go_to_the_library():
+def test_plain_products_with_few_tiles_and_a_long_k_go_to_the_library():
     from tinyllama_inference_engine_b200.ops import fast
 
-    assert fast.tcgen05_fills_the_sms(2048, 2048) and fast.tcgen05_fills_the_sms(2048, 2560) and fast.tcgen05_fills_the_sms(1280, 2048)
-    assert not fast.tcgen05_fills_the_sms(512, 2048)      # 32 tiles for 148 SMs
-    assert not fast.tcgen05_fills_the_sms(1024, 2048)     # 64 tiles
-    assert not fast.tcgen05_fills_the_sms(64, 32000)      # below the kernel's smallest row count
-    assert fast.tcgen05_fills_the_sms(128, 32000)         # one row block, 125 tiles
+    assert fast.tcgen05_takes(2048, 2048, 5632) and fast.tcgen05_takes(2048, 2560, 2048) and fast.tcgen05_takes(1280, 2048, 5632)
+    assert not fast.tcgen05_takes(512, 2048, 5632)      # 32 tiles for 148 SMs, 88 k blocks each
+    assert not fast.tcgen05_takes(1024, 2048, 5632)     # 64 tiles
+    assert fast.tcgen05_takes(512, 2048, 2048)          # few tiles, short K: level with the library and cheaper to launch
+    assert not fast.tcgen05_takes(64, 32000, 2048)      # below the kernel's smallest row count
+    assert fast.tcgen05_takes(128, 32000, 8192)         # one row block, 125 tiles
 
 
 def test_gemm_tile_width_prefers_full_waves():

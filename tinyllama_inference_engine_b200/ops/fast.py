@@ -126,15 +126,19 @@ use_tcgen05 = True
 TCGEN05_SOURCES = ["gemm_tcgen05.cu", "gemm_tcgen05_pair.cu"]
 
 
-def tcgen05_fills_the_sms(M: int, N: int) -> bool:
-    """Whether a plain product has tiles for at least half of the SMs.
+def tcgen05_takes(M: int, N: int, K: int) -> bool:
+    """Whether a plain product runs on this engine's tcgen05 kernel (else on the library's).
 
-    The kernel gives a CTA whole 128 x 256 tiles, all of K each.  With fewer tiles than that the library's product, which also
-    splits K, is ahead: measured at 512 rows on the 1.1B shapes, o 16.6 against 15.5 us and down (K = 5,632) 32 against 16 us;
-    from about half of the SMs on the two are level or this kernel is ahead.  (Sharing a tile's k blocks among CTAs was tried
-    in this kernel: the owner of a tile collects the others' partial accumulators at the very end of its share, eight trips to
-    the L2 per partial tile with nothing left to hide them behind, and that cost more than the even shares saved.)"""
-    return M >= TCGEN05_MIN_ROWS and -(-M // 128) * -(-N // 256) >= SM_COUNT // 2
+    The kernel gives a CTA whole 128 x 256 tiles, all of K each.  With tiles for fewer than half of the SMs and a long K the
+    library's product, which also splits K, is ahead by a factor: measured at 512 rows on the 1.1B shapes, down (K = 5,632)
+    32 against 16 us.  With a short K the two are within 10 % of each other and this kernel is the cheaper one to launch, which
+    is what counts for short prompt portions (their steps wait for the host, not for the GPU).  (Sharing a tile's k blocks
+    among CTAs was tried in this kernel: the owner of a tile collects the others' partial accumulators at the very end of its
+    share, eight trips to the L2 per partial tile with nothing left to hide them behind, and that cost more than even shares
+    saved.)"""
+    if M < TCGEN05_MIN_ROWS:
+        return False
+    return -(-M // 128) * -(-N // 256) >= SM_COUNT // 2 or K < 4096
 
 
 def tcgen05_library():
@@ -215,7 +219,7 @@ def linear_bf16(x, weight, out) -> None:
     if x.stride(0) % 8 == 0 and gemv_fits(x.shape[0], weight.shape[1], norm=False):
         gemv_fused(x, weight, out)
         return
-    if use_tcgen05 and tcgen05_fills_the_sms(x.shape[0], weight.shape[0]) and weight.shape[1] % 8 == 0 and x.is_contiguous():
+    if use_tcgen05 and tcgen05_takes(x.shape[0], weight.shape[0], weight.shape[1]) and weight.shape[1] % 8 == 0 and x.is_contiguous():
         gemm_tcgen05(x, weight, out)
         return
     library_gemm_calls += 1
