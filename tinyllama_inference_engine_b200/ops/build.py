@@ -125,7 +125,10 @@ def build_library(name: str, sources: list[str], defines: dict[str, object] | No
 
 
 def load_library(name: str, sources: list[str], defines: dict[str, object] | None = None, extra_link: list[str] | None = None) -> ctypes.CDLL:
-    key = name + repr(sorted((defines or {}).items()))
+    key = name if not defines else name + repr(sorted(defines.items()))
+    found = _loaded.get(key)   # every kernel launch comes through here: no lock and no string building once it is loaded
+    if found is not None:
+        return found
     with _lock:
         if key not in _loaded:
             path = build_library(name, sources, defines, extra_link)

@@ -5,6 +5,7 @@ and compiled only for what a model needs.
 """
 from __future__ import annotations
 
+import functools
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -162,6 +163,7 @@ PAIR_MIN_ROWS = 1024
 use_sm_pairs = True
 
 
+@functools.lru_cache(maxsize=4096)
 def gemm_tile_width(M: int, N: int, pair: bool = False) -> int:
     """The tile width whose waves of persistent CTAs (or pairs of them) cost least.
 
