@@ -405,6 +405,30 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n, pair):
         assert float(error.max()) <= tol * scale, (float(error.max()), scale, int(error.argmax()) // N, int(error.argmax()) % N)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (2048, 2048, 5632), (300, 200, 136), (1000, 132, 80), (129, 1000, 2048)])
+def test_gemm_tcgen05_accumulate(ops, M, N, K):
+    """residual += product in the product's epilogue (bulk tensor reductions, each element once): twice in a row, tails included."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    torch.manual_seed(17)
+    x = torch.randn(M, K).bfloat16()
+    w = (torch.randn(N, K) * 0.05).bfloat16()
+    start = torch.randn(M, N)
+    product = x.float() @ w.float().T
+    residual = start.clone().cuda()
+    guard = torch.full((M + 1, N), 7.0, device="cuda")   # the rows behind the residual must stay as they are
+    view = guard[:M]
+    view.copy_(residual)
+    for times in (1, 2):
+        fast.gemm_tcgen05_accumulate(x.cuda(), w.cuda(), view)
+        torch.cuda.synchronize()
+        assert int(fast.tcgen05_error_flag(view.device)) == 0, "a bounded wait inside the kernel gave up"
+        want = start + times * product
+        error = (view.cpu() - want).abs()
+        assert float(error.max()) <= 1e-4 * float(want.abs().max()), (times, float(error.max()), int(error.argmax()) // N, int(error.argmax()) % N)
+        assert float((guard[M] - 7.0).abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (2048, 5632, 2048), (300, 176, 136), (1000, 200, 80)])
 def test_gemm_tcgen05_gated(ops, M, inter, K, pair):

@@ -22,30 +22,35 @@ namespace tlie {
 
 // BN: any multiple of 16 up to 256 (the N of one tcgen05.mma with M = 128).  Widths between 128 and 256 exist for products
 // whose tiles would otherwise fill one wave of CTAs and a sliver of a second one.
-template <int BN>
+template <int BN, int EPI = 0>
 struct GemmShape {
   static constexpr int kStageBytes = (kBM + BN) * kBK * 2;
-  static constexpr int kStages = (220 * 1024 / kStageBytes) < 6 ? (220 * 1024 / kStageBytes) : 6;
-  // staging boxes of the epilogue's bulk stores: two per warp where they fit beside the ring, else one
-  static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kStoreBoxBytes + 1280 <= 227 * 1024) ? 2 : 1;
-  static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kStoreBoxBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /* alignment slack */ + 256 /* barriers */;
-  static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
+  // staging boxes of the epilogue's bulk stores (EPI 3: 32-bit boxes for bulk reductions): one per warp at least, two where
+  // they fit beside the ring
+  static constexpr int kBoxBytes = EPI == 3 ? kAddBoxBytes : kStoreBoxBytes;
+  static constexpr int kRoom = 227 * 1024 - 1024 /* alignment slack */ - 256 /* barriers */;
+  static constexpr int kFit = (kRoom - kStoreWarps * kBoxBytes) / kStageBytes;
+  static constexpr int kStages = kFit < 6 ? kFit : 6;
+  static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kBoxBytes <= kRoom) ? 2 : 1;
+  static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kBoxBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
   static constexpr int kAccStride = BN <= 128 ? 128 : 256;   // tensor memory is allocated in powers of two
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "the N of a tcgen05.mma with M = 128");
   static_assert(2 * kAccStride <= 512, "two accumulators must fit the 512 columns of tensor memory");
+  static_assert(kStages >= 2 && kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 };
 
 // EPI 0: bfloat16 out; EPI 1: 32-bit out; EPI 2 (BN = 256): w holds [gate rows | up rows] (`N` = rows of one half);
 // the tile's B operand is 128 gate rows and the 128 up rows at the same offset, and the epilogue stores
 // silu(gate) * up (src/operators.cpp:148-164) as bfloat16 [M, N]: the activation kernel and the round trip of the
-// [M, 2N] intermediate through memory disappear.
+// [M, 2N] intermediate through memory disappear.  EPI 3: out is the 32-bit residual stream and the tile is added to it by bulk
+// tensor reductions (the add kernel and the round trip of the product through memory disappear).
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_out, int staged, void* __restrict__ out, int M, int N, int K,
                         int* __restrict__ error_flag) {
-  using Shape = GemmShape<BN>;
+  using Shape = GemmShape<BN, EPI>;
   constexpr int kStages = Shape::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles need 1024-byte alignment
@@ -153,7 +158,9 @@ __global__ void __launch_bounds__(kGemmThreads)
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
-      if (EPI != 1 && staged) {
+      if (EPI == 3) {
+        add_tile_staged<BN, Shape::kStoreBuffers>(tmem_acc, m0 + sub * 32, n0, M, N, &map_out, staging + sub * Shape::kStoreBuffers * kAddBoxBytes, lane, boxes);
+      } else if (EPI != 1 && staged) {
         store_tile_staged<BN, EPI, Shape::kStoreBuffers>(tmem_acc, m0 + sub * 32, n0, M, N, &map_out,
                                                          staging + sub * Shape::kStoreBuffers * kStoreBoxBytes, lane, boxes);
       } else {
@@ -183,11 +190,12 @@ static int launch_gemm(const void* x, const void* w, void* out, int M, int N, in
   CUtensorMap map_a, map_b, map_out;
   // EPI 2: w has 2 N rows, fetched as two boxes of BN / 2 rows; N is the width of the output
   if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, EPI == 2 ? BN / 2 : BN)) return (int)cudaErrorInvalidValue;
-  const int staged = (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
+  if (EPI == 3 && !make_add_map(&map_out, out, M, N)) return (int)cudaErrorInvalidValue;
+  const int staged = EPI == 3 || (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
   if (!staged) map_out = map_a;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmShape<BN>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmShape<BN, EPI>::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -200,7 +208,7 @@ static int launch_gemm(const void* x, const void* w, void* out, int M, int N, in
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
-  return (int)launch_pdl(gemm_tcgen05_kernel<BN, EPI>, grid, dim3(kGemmThreads), GemmShape<BN>::kSmemBytes, stream, map_a, map_b, map_out, staged, out, M, N, K,
+  return (int)launch_pdl(gemm_tcgen05_kernel<BN, EPI>, grid, dim3(kGemmThreads), GemmShape<BN, EPI>::kSmemBytes, stream, map_a, map_b, map_out, staged, out, M, N, K,
                          error_flag);
 }
 
@@ -209,13 +217,15 @@ static int launch_gemm(const void* x, const void* w, void* out, int M, int N, in
 using namespace tlie;
 
 // out[M, N] = x[M, K] . w[N, K]^T.  x and w bfloat16 row-major with 16-byte aligned bases and K % 8 == 0 (TMA strides);
-// out bfloat16 (out_f32 = 0), 32-bit (1), or out_f32 = 2: w is [gate rows | up rows] of N rows each and out [M, N] = silu(gate) * up.
+// out bfloat16 (out_f32 = 0), 32-bit (1), out_f32 = 2: w is [gate rows | up rows] of N rows each and out [M, N] = silu(gate) * up,
+// or out_f32 = 3: out is 32-bit (16-byte aligned, N % 4 == 0) and the product is added to it.
 // tile_n is 128, 160, 192 or 256.  `error_flag` (device int, zero) becomes 1 if a wait gave up.
 TLIE_EXPORT int tlie_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int tile_n, int* error_flag,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || error_flag == nullptr || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   if (out_f32 == 2) return launch_gemm<256, 2>(x, w, out, M, N, K, error_flag, stream);   // gated: N = rows of one half of w
+  if (out_f32 == 3) return launch_gemm<256, 3>(x, w, out, M, N, K, error_flag, stream);   // out (32-bit) += the product
   if (tile_n == 256) {
     return out_f32 ? launch_gemm<256, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<256, 0>(x, w, out, M, N, K, error_flag, stream);
   }

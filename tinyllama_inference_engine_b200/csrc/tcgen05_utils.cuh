@@ -162,8 +162,11 @@ __device__ __forceinline__ void store_tile_staged(uint32_t tmem_acc, int row0, i
                                                   int lane, int& boxes) {
   constexpr int kOutCols = EPI == 2 ? BN / 2 : BN;
   const int swizzle = (lane >> 1) & 3;   // 64-byte swizzle: 16-byte chunk j of row r lies at chunk j ^ ((r / 2) % 4)
+  if (row0 >= M) return;   // nothing of this warp's rows is inside the matrix
+  // Only boxes that reach into the matrix are staged: a box is handed over with every pass, which is what the wait before
+  // the next pass over the same buffer counts on.
 #pragma unroll 1
-  for (int c = 0; c < kOutCols / kStoreCols; ++c) {
+  for (int c = 0; c < kOutCols / kStoreCols && n0 + c * kStoreCols < N; ++c) {
     uint32_t packed[kStoreCols / 2];
     if (EPI == 2) {
       uint32_t gate[32], up[32];
@@ -189,8 +192,42 @@ __device__ __forceinline__ void store_tile_staged(uint32_t tmem_acc, int row0, i
       *reinterpret_cast<uint4*>(my_row + ((j ^ swizzle) << 4)) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the bulk store
     __syncwarp();
-    if (lane == 0 && row0 < M && n0 + c * kStoreCols < N) {
+    if (lane == 0) {
       tma_store_2d(map_out, box, n0 + c * kStoreCols, row0);
+      asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+    }
+  }
+}
+
+// out (32-bit) += the tile: 32 columns of the warp's 32 rows as 32-bit values into shared memory (128-byte rows, 128-byte swizzle)
+// and one bulk tensor reduction (add) per box.  Every element of out belongs to one tile, so it is added to exactly once: the
+// sum does not depend on any order.  This is the reference's add kernel (src/cuda/kernels.cu:208-215) inside the product.
+constexpr int kAddBoxBytes = 32 * kStoreCols * 4;
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+template <int BN, int BUFFERS>
+__device__ __forceinline__ void add_tile_staged(uint32_t tmem_acc, int row0, int n0, int M, int N, const CUtensorMap* map_out, uint8_t* staging, int lane,
+                                                int& boxes) {
+  const int swizzle = lane & 7;   // 128-byte swizzle: 16-byte chunk j of row r lies at chunk j ^ (r % 8)
+  if (row0 >= M) return;
+#pragma unroll 1
+  for (int c = 0; c < BN / kStoreCols && n0 + c * kStoreCols < N; ++c) {   // as above: every pass hands a box over
+    uint32_t r[32];
+    tmem_load_32(tmem_acc + c * kStoreCols, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+    uint8_t* box = staging + (boxes % BUFFERS) * kAddBoxBytes;
+    ++boxes;
+    if (lane == 0) bulk_wait_read<BUFFERS - 1>();   // the reduction that last read this box is done with it
+    __syncwarp();
+    uint8_t* my_row = box + lane * (kStoreCols * 4);
+#pragma unroll
+    for (int j = 0; j < kStoreCols / 4; ++j) *reinterpret_cast<uint4*>(my_row + ((j ^ swizzle) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      tma_reduce_add_2d(map_out, box, n0 + c * kStoreCols, row0);
       asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
     }
   }
@@ -275,6 +312,19 @@ static bool make_store_map(CUtensorMap* map, const void* base, int M, int N) {
   const cuuint32_t elem[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// out [M, N] 32-bit row-major with boxes of 32 rows x 32 columns (128 bytes) and 128-byte swizzle, for reductions into it.
+// Needs a 16-byte aligned base and N % 4 == 0.
+static bool make_add_map(CUtensorMap* map, const void* base, int M, int N) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr || ((uintptr_t)base & 15) || N % 4 != 0) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+  const cuuint32_t box[2] = {(cuuint32_t)kStoreCols, 32};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace tlie

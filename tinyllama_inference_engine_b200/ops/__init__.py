@@ -189,8 +189,16 @@ def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
         linear(x.tensor(), weight, out)
 
 
+def can_accumulate(rows: int, weight) -> bool:
+    """Whether ``linear_accumulate`` is one kernel for a step of this many rows beyond the fused row limit."""
+    from . import fast
+
+    return fast.can_accumulate(rows, weight)
+
+
 def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) -> None:
-    """residual += x . weight^T, the sum in 32-bit, in one kernel (bfloat16 x, up to the fused row limit).
+    """residual += x . weight^T, the sum in 32-bit, in one kernel (bfloat16 x; up to the fused row limit in the weight-streaming
+    kernel, for prompt portions in the tensor-core product's epilogue).
 
     ``prepare``: the lazy norm of this residual (all rows) that the next product will consume; the kernel then leaves that
     norm's input beside the residual (``prepare.prepared``), written by the threads that hold the finished sums."""
@@ -203,6 +211,8 @@ def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) ->
             prepare.prepared = buffers
         else:
             fast.gemv_fused(x, weight, residual, epilogue="accumulate")
+    elif x.dtype == torch.bfloat16 and fast.can_accumulate(x.shape[0], weight) and x.is_contiguous() and residual.is_contiguous():
+        fast.gemm_tcgen05_accumulate(x, weight, residual)
     else:
         delta = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
         linear(x, weight, delta)

@@ -196,6 +196,30 @@ def gemm_tcgen05(x, weight, out, tile_n: int | None = None, pair: bool | None = 
     )
 
 
+use_accumulate_epilogue = True   # o-proj and down-proj of prompt portions add into the residual from the product's epilogue
+
+
+def can_accumulate(rows: int, weight) -> bool:
+    """Whether ``gemm_tcgen05_accumulate`` takes residual += x . weight^T for this many rows."""
+    N, K = weight.shape
+    return (use_tcgen05 and use_accumulate_epilogue and weight.dtype == torch.bfloat16 and N % 4 == 0 and K % 8 == 0 and tcgen05_takes(rows, N, K))
+
+
+def gemm_tcgen05_accumulate(x, weight, residual) -> None:
+    """residual[M, N] (32-bit) += x[M, K] . weight[N, K]^T: the product's tiles are added by bulk tensor reductions, each element once."""
+    ops = _ops()
+    M, K = x.shape
+    N = weight.shape[0]
+    if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or residual.dtype != torch.float32 or residual.shape != (M, N) or K % 8 != 0 or N % 4 != 0
+            or not x.is_contiguous() or not residual.is_contiguous()):
+        raise KernelError("gemm_tcgen05_accumulate takes contiguous bfloat16 operands (K % 8 == 0) and a contiguous 32-bit residual [M, N] with N % 4 == 0", code="invalid_shape")
+    ops._check(
+        tcgen05_library().tlie_gemm_tcgen05(ops._ptr(x), ops._ptr(weight), ops._ptr(residual), c_int(M), c_int(N), c_int(K), c_int(3), c_int(256),
+                                            ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
+        "gemm_tcgen05_accumulate",
+    )
+
+
 def gemm_tcgen05_gated(x, weight, out, pair: bool | None = None) -> None:
     """out[M, I] = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows] ([2 I, K]), one kernel."""
     ops = _ops()

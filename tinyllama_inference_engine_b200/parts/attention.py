@@ -56,6 +56,9 @@ class Attention(Mixer):
         self.position = build_part("position", spec["position"], prefix, weights, runtime)
         self.qkv_width = (self.q_heads + 2 * self.kv_heads) * self.head_dim
 
+    def adds_to_residual(self, rows: int) -> bool:
+        return ops.can_accumulate(rows, self.w_o)
+
     def forward(self, x, ctx, cache: LayerCache, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         qkv = ws.get("qkv", tokens, self.qkv_width, dtype)

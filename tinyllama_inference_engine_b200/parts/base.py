@@ -137,6 +137,10 @@ class Mixer(Part):
     fuses_residual_add = False     # forward(..., accumulate_into=residual) adds its output there and returns None
     prepares_next_norm = False     # with accumulate_into it also takes prepare=<ops.LazyNorm of the norm that follows>
 
+    def adds_to_residual(self, rows: int) -> bool:
+        """Whether, with ``fuses_residual_add``, a step of this many rows beyond the fused row limit can still add in its last kernel."""
+        return False
+
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
         return CacheNeed()
@@ -150,6 +154,9 @@ class FeedForward(Part):
     accepts_lazy_norm = False
     fuses_residual_add = False
     prepares_next_norm = False
+
+    def adds_to_residual(self, rows: int) -> bool:
+        return False
 
     def forward(self, x, ctx):
         raise NotImplementedError

@@ -60,6 +60,8 @@ class PreNormResidualBlock(Block):
             x = norm.forward(residual, pending, lazy=True)
         else:
             x = norm.forward(residual, pending)
+        if not fused and part.fuses_residual_add and part.adds_to_residual(residual.shape[0]):
+            return part.forward(x, *args, accumulate_into=residual)   # many rows: the add happens in the last product's epilogue
         if fused and part.fuses_residual_add:
             if part.prepares_next_norm and next_norm is not None and next_norm.supports_lazy:
                 following = next_norm.forward(residual, None, lazy=True)   # of the residual as it will be when the part is done

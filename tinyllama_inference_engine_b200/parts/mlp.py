@@ -42,6 +42,9 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat([weights.get(f"{prefix}.gate_proj.weight", dtype), weights.get(f"{prefix}.up_proj.weight", dtype)], dim=0).contiguous()
         self.w_down = weights.get(f"{prefix}.down_proj.weight", dtype).contiguous()
 
+    def adds_to_residual(self, rows: int) -> bool:
+        return ops.can_accumulate(rows, self.w_down)
+
     def forward(self, x, ctx, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         act = ws.get("activated", tokens, self.inter, dtype)
