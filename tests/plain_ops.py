@@ -121,7 +121,12 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
         out[r] = plain_llama.sample_top_p(logits[r].float(), float(temperature[r]), float(top_p[r]), u)
 
 
-_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample"]
+def can_accumulate(rows: int, weight) -> bool:
+    return False   # no product adds into the residual here: the block adds the part's output in the norm that follows
+
+
+_NAMES = ["embedding", "add_rmsnorm", "add_", "silu_mul", "linear", "fused_rows_limit", "rope_store", "paged_attention", "attention_step", "argmax", "sample",
+          "can_accumulate"]
 
 
 def install(monkeypatch) -> None:
