@@ -113,3 +113,45 @@ def test_decode_attention_parts_fit_one_wave():
             if requests * kv_heads <= fast.SM_COUNT:
                 assert requests * kv_heads * parts <= fast.SM_COUNT
     assert fast.decode_splits(8, 4, 2048) == 4 and fast.decode_splits(1, 4, 2048) == 8 and fast.decode_splits(1, 4, 100) == 1
+
+
+def test_block_lets_a_part_add_to_the_residual_in_steps_of_many_rows(monkeypatch):
+    """The block's choice, with stand-in parts: few rows -> norm and add go into the part's kernels (lazy norm, accumulate_into);
+    many rows -> a materialised norm, and accumulate_into only if the part says it can add for that many rows."""
+    from tinyllama_inference_engine_b200 import ops
+    from tinyllama_inference_engine_b200.parts.block import PreNormResidualBlock
+
+    monkeypatch.setattr(ops, "fused_rows_limit", lambda dtype, device: 16)
+    calls = []
+
+    class Norm:
+        supports_lazy = True
+        weight, eps = object(), 1e-5
+
+        def forward(self, residual, delta, lazy=False):
+            calls.append(("norm", delta is not None, lazy))
+            return "lazy" if lazy else "normed"
+
+    class Part:
+        accepts_lazy_norm = fuses_residual_add = True
+        prepares_next_norm = False
+
+        def __init__(self, adds):
+            self.adds = adds
+
+        def adds_to_residual(self, rows):
+            return self.adds
+
+        def forward(self, x, accumulate_into=None):
+            calls.append(("part", x, accumulate_into is not None))
+            return None if accumulate_into is not None else "out"
+
+    few, many = torch.zeros(8, 4), torch.zeros(200, 4)
+    assert PreNormResidualBlock._run(Norm(), Part(False), few, None, True, None) is None
+    assert calls == [("norm", False, True), ("part", "lazy", True)]
+    calls.clear()
+    assert PreNormResidualBlock._run(Norm(), Part(False), many, "pending", False, None) == "out"
+    assert calls == [("norm", True, False), ("part", "normed", False)]
+    calls.clear()
+    assert PreNormResidualBlock._run(Norm(), Part(True), many, "pending", False, None) is None
+    assert calls == [("norm", True, False), ("part", "normed", True)]
