@@ -11,7 +11,12 @@
 //   * the softmax warps read S with tcgen05.ld, mask, exponentiate (scale folded into the exponent), write P as
 //     bfloat16 into shared memory in the swizzled K-major layout, and a second tcgen05.mma group computes P . V with
 //     V as an MN-major operand (V stays [key][dim], as the cache stores it);
-//   * the running output lives in registers: O = O * 2^(old max - new max) + (P . V), read back from tensor memory.
+//   * the running output lives in tensor memory: every P . V accumulates onto it, against a reference maximum per row;
+//     when a tile's maximum is more than 2^8 above the reference, the row's thread multiplies its lane of the output
+//     and its sum by 2^(old reference - new one) (a warp-wide load, multiply and store; rows that need nothing use 1)
+//     before P of that tile is handed over, and the output is read once, after the last tile, and divided by the sum;
+//   * the kernel is launched as a programmatic dependent: barriers and tensor memory are set up while the kernel before
+//     it drains, global memory is touched only after the dependency wait.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and tensor-memory owner, warps 2..5 softmax (128 threads).
 // Every mbarrier wait is bounded; on a timeout the CTA raises `error_flag`, stops, lets copies land, frees its tensor
 // memory and returns.  Needs page_size % 64 == 0; other shapes use the mma.sync kernel.

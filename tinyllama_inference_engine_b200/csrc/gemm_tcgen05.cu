@@ -8,7 +8,11 @@
 //     (128 lanes x BN 32-bit columns) lives in tensor memory, not in registers;
 //   * tcgen05.commit hands a stage back to the TMA producer when its MMAs have read it, and signals the
 //     epilogue when the last MMA is done;
-//   * four epilogue warps read the accumulator with tcgen05.ld (each warp its 32 lanes), convert and store.
+//   * four epilogue warps read the accumulator with tcgen05.ld (each warp its 32 lanes), convert, pack 32 columns of their
+//     32 rows into shared memory and let one thread write the 32 x 32 box with a bulk tensor store (or add it into a
+//     32-bit matrix with a bulk tensor reduction); where the output's shape rules that out, rows go straight from registers;
+//   * the kernel is launched as a programmatic dependent: barriers and tensor memory are set up while the kernel before
+//     it drains, global memory is touched only after the dependency wait.
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer, warp 2 = tensor-memory allocation (and epilogue),
 // warps 2..5 = epilogue.  CTAs are persistent: one per SM walks the 128 x BN output tiles blockIdx.x, + gridDim.x, ...
 // (m fastest, so the CTAs running together share a few column blocks of w in L2).  Two accumulators in tensor memory
