@@ -76,7 +76,7 @@ struct SmemTC {
   __nv_bfloat16 k[kKvStages][kKeysTC * kD];          // 8 KB each
   __nv_bfloat16 v[kKvStages][kKeysTC * kD];          // 8 KB each
   __nv_bfloat16 p[2][kRowsTC * kKeysTC];             // 16 KB each
-  uint64_t q_full, q_empty, kv_full[kKvStages], kv_empty[kKvStages], s_full[2], s_empty[2], p_full[2], pv_full;
+  uint64_t q_full, q_empty, kv_full[kKvStages], kv_empty[kKvStages], s_full[2], s_empty[2], p_full[2], pv_full, o_full[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -136,6 +136,8 @@ __global__ void __launch_bounds__(kThreadsTC)
       mbar_init(&sm.p_full[b], 4);
     }
     mbar_init(&sm.pv_full, 1);
+    mbar_init(&sm.o_full[0], 1);   // used once each: all products of a row tile are done
+    mbar_init(&sm.o_full[1], 1);
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -230,6 +232,7 @@ __global__ void __launch_bounds__(kThreadsTC)
           umma_commit(pv_full);
           umma_commit(kv_empty + 8 * pv_ring.stage);   // both products of this stage are done when this fires
         }
+        if (ok) umma_commit(&sm.o_full[u]);   // the row tile's output is complete when this fires
       }
     }
   } else {   // softmax: thread = one query row = one lane of tensor memory
@@ -287,7 +290,9 @@ __global__ void __launch_bounds__(kThreadsTC)
           // tile's maximum is far above it; the loads and stores are warp-wide, rows that need nothing multiply by one.
           const bool grown = scaled_max > reference + kLazyRescale;
           if (__any_sync(0xffffffffu, grown)) {
-            ok = mbar_wait(&sm.pv_full, (g - 1) & 1, abort_flag);   // the product that last added to O is done
+            // The product that last added to O must be done.  The parity is enough here: the scores of this tile were issued
+            // after the product two tiles back and are complete, so that product is, and the one of this tile waits for this P.
+            ok = mbar_wait(&sm.pv_full, (g - 1) & 1, abort_flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float alpha = grown ? exp2f(reference - scaled_max) : 1.0f;
@@ -331,7 +336,10 @@ __global__ void __launch_bounds__(kThreadsTC)
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.p_full[b]);
       }
-      if (ok) ok = mbar_wait(&sm.pv_full, (g - 1) & 1, abort_flag);   // the row tile's last product
+      // The row tile's output is read when all its products are done.  This waits on a barrier of its own that completes once:
+      // pv_full's parity tells only the last phase from the one before, and a warp that is a tile ahead of the slowest one
+      // (whose P the product before last still waits for) would take the phase two back for the one it asked about.
+      if (ok) ok = mbar_wait(&sm.o_full[u], 0, abort_flag);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         float o[kD];
