@@ -130,13 +130,12 @@ class ClockSampler:
 
 def model_folder(layers: int) -> Path:
     """A random-weights model folder at the benchmark shapes (kept in the temporary folder between runs)."""
-    from tinyllama_inference_engine_b200 import LlamaConfig
     from tinyllama_inference_engine_b200.weights import write_random_model
 
     folder = Path(tempfile.gettempdir()) / f"tlie_b200_bench_{os.getuid()}_L{layers}"
     if not (folder / "model.safetensors").exists():
         staging = Path(tempfile.mkdtemp(prefix="tlie_b200_bench_", dir=tempfile.gettempdir()))
-        write_random_model(staging, LlamaConfig.from_dict(dict(SHAPES, num_hidden_layers=layers)), seed=0)
+        write_random_model(staging, dict(SHAPES, num_hidden_layers=layers), seed=0)
         try:
             os.replace(staging, folder)
         except OSError:

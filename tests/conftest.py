@@ -19,8 +19,7 @@ def pytest_configure(config):
 def model_folders(tmp_path_factory):
     """Random tiny checkpoints (config.json + model.safetensors) in a temporary folder, by name."""
     from tiny_configs import ALL
-    from tinyllama_inference_engine_b200 import LlamaConfig
     from tinyllama_inference_engine_b200.weights import write_random_model
 
     base = tmp_path_factory.mktemp("models")
-    return {key: write_random_model(base / key, LlamaConfig.from_dict(config), seed) for key, (config, seed) in ALL.items()}
+    return {key: write_random_model(base / key, config, seed) for key, (config, seed) in ALL.items()}

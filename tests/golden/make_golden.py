@@ -97,7 +97,6 @@ def main() -> None:
 
     import plain_llama
     from tiny_configs import ALL
-    from tinyllama_inference_engine_b200 import LlamaConfig
     from tinyllama_inference_engine_b200.weights import write_random_model
 
     with tempfile.TemporaryDirectory() as tmp:
@@ -109,7 +108,7 @@ def main() -> None:
         result = {}
         for key in ("a", "b"):
             config, seed = ALL[key]
-            folder = write_random_model(tmp / key, LlamaConfig.from_dict(config), seed)
+            folder = write_random_model(tmp / key, config, seed)
             _, weights = plain_llama.load_model(folder)
             if "lm_head.weight" not in weights:
                 weights["lm_head.weight"] = weights["model.embed_tokens.weight"]

@@ -8,7 +8,8 @@ import pytest
 import torch
 
 from tiny_configs import TINY_A, TINY_B, TINY_C
-from tinyllama_inference_engine_b200 import EngineConfig, LlamaConfig
+from tinyllama_inference_engine_b200 import EngineConfig
+from tinyllama_inference_engine_b200.models.llama_config import LlamaConfig
 from tinyllama_inference_engine_b200.config import architecture_for, load_model_config, registered_architectures
 from tinyllama_inference_engine_b200.errors import ConfigError, EngineError, FormatError, WeightError
 from tinyllama_inference_engine_b200.models import expected_tensors
@@ -34,7 +35,9 @@ def test_config_reads_its_own_keys_and_derives_sizes():
     ({"model_type": "mistral"}, "model_type must be llama"),
     ({"num_key_value_heads": 3}, "not a multiple"),
     ({"hidden_size": 66}, "no head_dim"),
-    ({"head_dim": 15}, "even"),
+    ({"head_dim": 15}, "multiple of 16"),
+    ({"head_dim": 40}, "multiple of 16"),
+    ({"head_dim": 272}, "up to 256"),
     ({"hidden_act": "gelu"}, "silu"),
     ({"attention_bias": True}, "biases"),
     ({"rope_scaling": {"type": "linear", "factor": 2.0}}, "rope_scaling"),
@@ -101,8 +104,38 @@ def test_storage_rule_32_bit_stays_and_integers_become_int32(tmp_path):
         "single": torch.ones(4, dtype=torch.float32), "table": torch.arange(5, dtype=torch.int64),
     })
     store = WeightStore.load(tmp_path, [TensorSpec("half", (2, 3)), TensorSpec("brain", (2, 3)), TensorSpec("single", (4,)), TensorSpec("table", (5,), integer=True)])
-    assert store.get("half").dtype == store.get("brain").dtype == torch.bfloat16
+    assert store.get("half").dtype == torch.float16 and store.get("brain").dtype == torch.bfloat16   # each as the file has it
+    assert store.get("half", torch.float32).dtype == torch.float32
     assert store.get("single").dtype == torch.float32 and store.get("table").dtype == torch.int32
+
+
+def test_a_float16_checkpoint_widens_exactly_for_the_32_bit_engine(tmp_path):
+    """A float16 value has three more mantissa bits than bfloat16 keeps: the store must hand the 32-bit path the value itself
+    (the reference's GPU checkpoints are float16, scripts/convert_model_fp16.py:23-67)."""
+    folder = write_random_model(tmp_path / "half", TINY_A, seed=0, storage_dtype="float16")
+    architecture, loaded = load_model_config(folder)
+    store = WeightStore.load(folder, expected_tensors(architecture.build_spec(loaded)))
+    file = SafetensorsFile(folder / "model.safetensors")
+    name = "model.layers.0.self_attn.q_proj.weight"
+    raw = file.tensor(name).clone()
+    file.close()
+    assert raw.dtype == torch.float16
+    assert torch.equal(store.get(name, torch.float32), raw.float())
+    assert not torch.equal(raw.float(), raw.bfloat16().float())          # so rounding to bfloat16 would have been visible
+    assert torch.equal(store.get(name, torch.bfloat16), raw.bfloat16())  # the bfloat16 engine rounds, once
+
+
+def test_a_tied_checkpoint_may_store_the_head_as_well(tmp_path):
+    folder = write_random_model(tmp_path / "tied", TINY_B, seed=2)
+    file = SafetensorsFile(folder / "model.safetensors")
+    tensors = {name: file.tensor(name).clone() for name in file.names()}
+    file.close()
+    assert "lm_head.weight" not in tensors
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    write_safetensors(folder / "model.safetensors", tensors)
+    architecture, loaded = load_model_config(folder)
+    store = WeightStore.load(folder, expected_tensors(architecture.build_spec(loaded)))   # not "unexpected"
+    assert store.has("lm_head.weight")
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):

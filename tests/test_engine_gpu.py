@@ -180,3 +180,28 @@ def test_wider_decode_batches(model_folders, count):
         assert _agrees_up_to_near_ties(config, weights, prompt, g, w, 0.03)
     assert count in engine._sessions
     engine.runner.cache.check()
+
+
+def test_a_fault_recorded_on_the_device_fails_the_step(model_folders):
+    """Kernels that give up a bounded wait, or meet a token id outside the vocabulary, set a bit in the device's error word.
+    The engine reads the word where it waits for the device anyway, raises, and clears it; the failure is made on the host
+    here (the word is written by the test), no kernel is driven into a fault."""
+    from tinyllama_inference_engine_b200 import ops
+    from tinyllama_inference_engine_b200.engine.replay import replay_step
+    from tinyllama_inference_engine_b200.errors import KernelError
+
+    engine = _engine(model_folders["a"], dtype="bfloat16", use_cuda_graphs=True)
+    word = ops.error_flag(engine.runner.device)
+    engine.add_request([5, 6, 7], SamplingParams(max_tokens=6))
+    engine.step()                      # the prompt
+    engine.step()                      # first decode steps, through a decode session
+    word.fill_(1)
+    with pytest.raises(KernelError, match="bounded wait"):
+        for _ in range(3):
+            engine.step()
+    assert int(word.item()) == 0
+    runner = ModelRunner(model_folders["a"], EngineConfig(dtype="float32", page_size=16, max_cache_tokens=64, max_requests=2, max_batch_tokens=16))
+    word.fill_(2)
+    with pytest.raises(KernelError, match="outside the vocabulary"):
+        replay_step(runner, {"step": 0, "entries": [{"id": "x", "tokens": [1, 2], "want": [1]}], "end": ["x"]})
+    assert replay_step(runner, {"step": 1, "entries": [{"id": "y", "tokens": [1, 2], "want": [1]}], "end": ["y"]}) is not None

@@ -17,8 +17,8 @@ from tinyllama_inference_engine_b200.engine.runner import ModelRunner
 from tinyllama_inference_engine_b200.errors import BatchError, KernelError, OutOfPages
 
 
-def _runner(folder, max_tokens=1024, page_size=16, dtype="float32"):
-    config = EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8, max_batch_tokens=64, device="cpu", poison_freed_pages=True)
+def _runner(folder, max_tokens=1024, page_size=16, dtype="float32", max_batch_tokens=2048):
+    config = EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8, max_batch_tokens=max_batch_tokens, device="cpu", poison_freed_pages=True)
     return ModelRunner(folder, config)
 
 
@@ -77,6 +77,14 @@ def test_step_refuses_bad_batches(model_folders, monkeypatch):
     assert list(runner.cache.records) == ["x"]
     runner.finish("x")
     runner.cache.check()
+    # the workspace's buffers have fixed addresses (captured graphs point at them): a step beyond the token budget is refused
+    small = _runner(model_folders["a"], max_batch_tokens=8)
+    with pytest.raises(BatchError, match="max_batch_tokens"):
+        small.step([StepEntry("x", [1] * 5, []), StepEntry("y", [1] * 4, [])])
+    assert not small.cache.records
+    small.step([StepEntry("x", [1] * 5, []), StepEntry("y", [1] * 3, [2])])
+    with pytest.raises(BatchError, match="workspace"):
+        small.runtime.workspace.get("anything", 9, 4, torch.float32)
 
 
 def test_plain_products_with_few_tiles_and_a_long_k_go_to_the_library():
@@ -110,8 +118,8 @@ def test_decode_attention_parts_fit_one_wave():
         for kv_heads in (1, 2, 4, 8):
             parts = fast.decode_splits(requests, kv_heads, 4096)
             assert 1 <= parts <= 32
-            if requests * kv_heads <= fast.SM_COUNT:
-                assert requests * kv_heads * parts <= fast.SM_COUNT
+            if requests * kv_heads <= fast.sm_count():
+                assert requests * kv_heads * parts <= fast.sm_count()
     assert fast.decode_splits(8, 4, 2048) == 4 and fast.decode_splits(1, 4, 2048) == 8 and fast.decode_splits(1, 4, 100) == 1
 
 

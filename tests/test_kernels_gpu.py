@@ -166,6 +166,43 @@ def test_paged_attention(ops, dtype, q_heads, kv_heads, head_dim, page_size, win
     assert torch.allclose(got.cpu().float(), want.float(), atol=_tol(dtype, 2) + (2e-6 if dtype == torch.float32 else 0)), float((got.cpu().float() - want.float()).abs().max())
 
 
+def test_embedding_survives_an_id_outside_the_table_and_reports_it(ops):
+    """An id the host never saw (a token sampled on the device from non-finite logits) must not be used as an address:
+    row 0 is read instead and the device's error word says so; reading the word raises and clears it."""
+    from tinyllama_inference_engine_b200.errors import KernelError
+
+    table = torch.randn(50, 64).bfloat16().cuda()
+    ids = torch.tensor([3, 50, -1, 0x7FFFFFFF, 49], dtype=torch.int32).cuda()
+    got = torch.empty(5, 64, device="cuda")
+    ops.check_device_errors(got.device)   # nothing is pending
+    ops.embedding(table, ids, got)
+    with pytest.raises(KernelError, match="outside the vocabulary"):
+        ops.check_device_errors(got.device)
+    ops.check_device_errors(got.device)   # cleared by the read that raised
+    want = table.float()[[3, 0, 0, 0, 49]]
+    assert torch.equal(got, want)
+
+
+def test_sampling_non_finite_logits_still_gives_a_token_of_the_vocabulary(ops):
+    vocab = 131
+    logits = torch.randn(6, vocab)
+    logits[0] = float("nan")
+    logits[1] = float("-inf")
+    logits[2, ::2] = float("nan")
+    logits[3] = float("inf")
+    logits[4, 5] = float("nan")
+    cuda = lambda t: t.cuda()  # noqa: E731
+    for temperature, top_p in ((0.0, 1.0), (0.9, 1.0), (0.9, 0.5)):
+        out = torch.full((6,), -7, dtype=torch.int32, device="cuda")
+        ops.sample(cuda(logits), cuda(torch.full((6,), temperature)), cuda(torch.full((6,), top_p)), cuda(torch.arange(6, dtype=torch.int64)),
+                   cuda(torch.zeros(6, dtype=torch.int64)), out)
+        tokens = out.cpu().tolist()
+        assert all(0 <= t < vocab for t in tokens), (temperature, top_p, tokens)
+    out = torch.full((6,), -7, dtype=torch.int32, device="cuda")
+    ops.argmax(cuda(logits), out)
+    assert all(0 <= t < vocab for t in out.cpu().tolist())
+
+
 def test_argmax_and_sampling(ops):
     torch.manual_seed(7)
     logits = torch.randn(6, 1000)

@@ -30,7 +30,7 @@ def cases(model_folders):
 
 
 def _runner(folder, dtype, max_tokens=2048, page_size=64):
-    return ModelRunner(folder, EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8, max_batch_tokens=128, poison_freed_pages=True))
+    return ModelRunner(folder, EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8, max_batch_tokens=2048, poison_freed_pages=True))
 
 
 def test_far_key_decides_the_logits(model_folders):
@@ -60,6 +60,22 @@ def test_far_key_decides_the_logits(model_folders):
         for steps in (trace_tools.tail_decode(requests), trace_tools.portions(requests), trace_tools.mixed(requests, seed=9, page_size=16)[0]):
             runner = _runner(folder, dtype, max_tokens=1024, page_size=16)
             trace_tools.run_and_compare(runner, steps, full, atol=TOLERANCE[dtype] * scale)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_float16_checkpoint(tmp_path, dtype):
+    """A checkpoint stored in float16 (the reference's GPU format, scripts/convert_model_fp16.py:23-67): the 32-bit engine sees
+    every value exactly, so its logits meet the 32-bit bound; rounding the weights to bfloat16 first would miss it a hundredfold."""
+    from tiny_configs import TINY_A
+    from tinyllama_inference_engine_b200.weights import write_random_model
+
+    folder = write_random_model(tmp_path / "half", TINY_A, seed=4, storage_dtype="float16")
+    config, weights = plain_llama.load_model(folder)
+    requests = trace_tools.make_requests(config["vocab_size"], [33, 100, 7], seed=12)
+    full = {rid: plain_llama.forward(config, weights, tokens) for rid, tokens in requests.items()}
+    scale = max(float(v.abs().max()) for v in full.values())
+    for steps in (trace_tools.whole(requests), trace_tools.tail_decode(requests, tail=8)):
+        trace_tools.run_and_compare(_runner(folder, dtype), steps, full, atol=TOLERANCE[dtype] * scale)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

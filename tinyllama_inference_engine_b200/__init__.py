@@ -6,10 +6,10 @@ together from parts, a paged cache manager, one step function for mixed batches,
 a continuous-batching scheduler, sampling, and hand-written CUDA kernels.
 """
 from . import models  # noqa: F401  (registers the built-in architecture and parts)
-from .config import EngineConfig, LlamaConfig
+from .config import EngineConfig
 from .errors import EngineError
 
-__all__ = ["EngineConfig", "EngineError", "LlamaConfig", "Engine", "SamplingParams"]
+__all__ = ["EngineConfig", "EngineError", "Engine", "SamplingParams", "generate"]
 __version__ = "0.1.0"
 
 

@@ -1,5 +1,5 @@
 from .engine_config import EngineConfig
-from .model_config import LlamaConfig, read_config_json
+from .model_config import read_config_json
 from .registry import (
     Architecture,
     architecture_for,
@@ -12,7 +12,6 @@ from .registry import (
 __all__ = [
     "Architecture",
     "EngineConfig",
-    "LlamaConfig",
     "architecture_for",
     "load_model_config",
     "read_config_json",

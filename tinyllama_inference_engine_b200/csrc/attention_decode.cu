@@ -27,6 +27,8 @@
 // captured graph serves every later step.
 //
 // Compile-time: HEAD_DIM (multiple of 16, <= 256).
+#include <mutex>
+
 #include "attention_decode.h"
 #include "attention_decode_core.cuh"
 
@@ -111,6 +113,8 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 // use is looked up once per device, with that device current.
 static float* static_scratch_address(cudaError_t* error) {
   static float* address[64] = {};
+  static std::mutex guard;   // first calls on several devices may come from several host threads
+  std::lock_guard<std::mutex> lock(guard);
   int device = 0;
   *error = cudaGetDevice(&device);
   if (*error != cudaSuccess) return nullptr;
@@ -132,8 +136,11 @@ TLIE_EXPORT int tlie_decode_attention_static(const void* q, int q_row_stride, vo
                                              int q_heads, int kv_heads, int page_size, int window, float scale, int splits,
                                              int fuse_rope, const float* inv_freq, int write_cache, cudaStream_t stream) {
   if (requests <= 0) return 0;
-  if (splits < 1 || q_heads <= 0 || (long long)requests * q_heads * splits > kStaticMaxSlots ||
-      (long long)requests * kv_heads > kMaxTickets)
+  // every shape rule of tlie_decode_attention is applied here first, so that nothing at all is enqueued for a refused shape
+  if (kv_heads <= 0 || q_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || splits < 1 || splits > 32 ||
+      (fuse_rope && inv_freq != nullptr && kD % 32 != 0))
+    return (int)cudaErrorInvalidValue;
+  if ((long long)requests * q_heads * splits > kStaticMaxSlots || (long long)requests * kv_heads > kMaxTickets)
     return (int)cudaErrorInvalidValue;   // beyond the built-in scratch: nothing is launched
   cudaError_t error = cudaSuccess;
   float* scratch = static_scratch_address(&error);

@@ -1,8 +1,7 @@
 // The split-KV decode attention of attention_decode.cu as two steps a kernel strings together: `prologue` works out this
 // CTA's key range and starts fetching its cache tiles (nothing it touches depends on the current step's q, k, v), `main`
-// reads q, rotates, attends, and merges the parts.  The stand-alone kernel puts its programmatic-dependency wait between
-// the two; the fused decode step puts a grid barrier there.  What another CTA may have written this step (q, k, v of the
-// new token, the parts) is read through L2.
+// reads q, rotates, attends, and merges the parts.  The kernel puts its programmatic-dependency wait between the two.
+// What another CTA may have written this step (q, k, v of the new token, the parts) is read through L2.
 #pragma once
 
 #include "common.cuh"

@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(kThreadsTC)
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
   if (*abort_flag) {
-    if (threadIdx.x == 0) atomicExch(error_flag, 1);
+    if (threadIdx.x == 0) atomicOr(error_flag, 1);
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // copies that were issued may still be landing
   }
   __syncthreads();

@@ -93,6 +93,19 @@ __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddep
 #ifdef __CUDACC__
 #include <cstdlib>
 namespace tlie {
+// Streaming multiprocessors of the current device (asked once; 148 on a B200).  Grids of persistent CTAs are sized from it.
+static inline int device_sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0, found = 0;
+    if (cudaGetDevice(&device) == cudaSuccess && cudaDeviceGetAttribute(&found, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && found > 0)
+      count = found;
+    else
+      count = 148;
+  }
+  return count;
+}
+
 // Launch with programmatic dependent launch unless TLIE_PDL=0 is set in the environment.
 template <typename... KernelArgs, typename... Args>
 static inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

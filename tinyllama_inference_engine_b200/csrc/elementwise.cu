@@ -8,12 +8,18 @@
 
 namespace tlie {
 
-// residual[t, :] = float(table[ids[t], :])
+// residual[t, :] = float(table[ids[t], :]).  An id outside [0, vocab) (a sampler fed non-finite logits can produce one on
+// the device, where no host check sees it) reads row 0 instead and sets bit 1 of *error_flag, if one is given.
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ residual, int hidden) {
+                                 float* __restrict__ residual, int hidden, int vocab, int* __restrict__ error_flag) {
   const int row = blockIdx.x;
-  const T* src = table + (size_t)ids[row] * hidden;
+  int id = ids[row];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && error_flag != nullptr) atomicOr(error_flag, 2);
+    id = 0;
+  }
+  const T* src = table + (size_t)id * hidden;
   float* dst = residual + (size_t)row * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
 }
@@ -164,18 +170,20 @@ using namespace tlie;
 
 static inline int grid_for(size_t total, int block) {
   size_t blocks = (total + block - 1) / block;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const size_t most = (size_t)device_sm_count() * 16;
+  if (blocks > most) blocks = most;
   if (blocks < 1) blocks = 1;
   return (int)blocks;
 }
 
-TLIE_EXPORT int tlie_embedding(int dtype, const void* table, const int* ids, float* residual, int rows, int hidden,
-                               cudaStream_t stream) {
+TLIE_EXPORT int tlie_embedding(int dtype, const void* table, const int* ids, float* residual, int rows, int hidden, int vocab,
+                               int* error_flag, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (vocab <= 0) return (int)cudaErrorInvalidValue;
   if (dtype == TLIE_F32)
-    embedding_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, residual, hidden);
+    embedding_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, residual, hidden, vocab, error_flag);
   else
-    embedding_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, residual, hidden);
+    embedding_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, residual, hidden, vocab, error_flag);
   return (int)cudaGetLastError();
 }
 
@@ -215,7 +223,8 @@ TLIE_EXPORT int tlie_silu_mul(int dtype, const void* gate_up, void* out, int row
   if (total == 0) return 0;
   if (inter % 4 == 0) {
     const size_t total4 = total / 4;
-    const int blocks = (int)((total4 + 255) / 256 < 148 * 32 ? (total4 + 255) / 256 : 148 * 32);
+    const size_t most = (size_t)device_sm_count() * 32;
+    const int blocks = (int)((total4 + 255) / 256 < most ? (total4 + 255) / 256 : most);
     if (dtype == TLIE_F32)
       silu_mul_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total4);
     else

@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(kGemmThreads)
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
   if (*abort_flag) {
-    if (threadIdx.x == 0) atomicExch(error_flag, 1);
+    if (threadIdx.x == 0) atomicOr(error_flag, 1);
     // copies that were issued may still be landing in this CTA's shared memory: give them time before it is released
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
@@ -205,12 +205,7 @@ static int launch_gemm(const void* x, const void* w, void* out, int M, int N, in
   }
   constexpr int kTileN = EPI == 2 ? BN / 2 : BN;
   const int num_tiles = ((N + kTileN - 1) / kTileN) * ((M + kBM - 1) / kBM);
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = device_sm_count();
   dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
   return (int)launch_pdl(gemm_tcgen05_kernel<BN, EPI>, grid, dim3(kGemmThreads), GemmShape<BN, EPI>::kSmemBytes, stream, map_a, map_b, map_out, staged, out, M, N, K,
                          error_flag);

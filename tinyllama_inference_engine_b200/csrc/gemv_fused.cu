@@ -70,14 +70,14 @@ static int launch_rows(const GemvArgs& a, cudaStream_t stream) {
   const int tile_rows = (EPI == EPI_GATED) ? 8 : 16;
   const int tiles = (n_rows + tile_rows - 1) / tile_rows;
   // x is staged once per CTA, so a CTA takes several tiles when there are more than `slots` of them; equal shares
-  const int slots = kGemvCtasPerSm * 148;
+  const int slots = kGemvCtasPerSm * device_sm_count();
   const int per_cta = (tiles + slots - 1) / slots;
   // All slots are filled and a CTA walks tiles blockIdx.x, + gridDim.x, ...: an SM's CTAs then hold tile counts that differ
   // by one at most.  (Equal shares per CTA in fewer CTAs left some SMs with two CTAs and some with one: twice the work.)
   const int grid = tiles < slots ? tiles : slots;
   if (XMODE == X_PLAIN && per_cta == 1) {   // every element of x is used once per CTA: no point in staging it
     // long rows and no more tiles than SMs: sixteen warps split K, so that a CTA has twice the bytes in flight and half the rounds
-    if (a.M <= 8 && gemv_wide_ctas && tiles <= 148 && a.K > kGemvWarps * 8 * 32) return launch_one<1, X_DIRECT, EPI, 16>(a, grid, stream);
+    if (a.M <= 8 && gemv_wide_ctas && tiles <= device_sm_count() && a.K > kGemvWarps * 8 * 32) return launch_one<1, X_DIRECT, EPI, 16>(a, grid, stream);
     if (a.M <= 8) return launch_one<1, X_DIRECT, EPI>(a, grid, stream);
     if (a.M <= 16) return launch_one<2, X_DIRECT, EPI>(a, grid, stream);
     return (int)cudaErrorInvalidValue;

@@ -119,7 +119,8 @@ __global__ void __launch_bounds__(kSampleThreads)
     __syncthreads();
     if (local_max == row_max) atomicMin(&arg_smem, local_arg);
     __syncthreads();
-    if (threadIdx.x == 0) out[blockIdx.x] = arg_smem;
+    // a row without any comparable value (all NaN) leaves no maximum: token 0, as argmax_kernel answers
+    if (threadIdx.x == 0) out[blockIdx.x] = (arg_smem < 0 || arg_smem >= vocab) ? 0 : arg_smem;
     return;
   }
   const float inv_temp = 1.0f / temp;
@@ -194,7 +195,8 @@ __global__ void __launch_bounds__(kSampleThreads)
       for (int i = vocab - 1; i >= 0 && pick < 0; --i)
         if (expf((row[i] - row_max) * inv_temp) >= tau) pick = i;
     }
-    out[blockIdx.x] = pick;
+    // non-finite logits can leave nothing kept at all; the answer must still be a token of the vocabulary
+    out[blockIdx.x] = (pick < 0 || pick >= vocab) ? 0 : pick;
   }
 }
 

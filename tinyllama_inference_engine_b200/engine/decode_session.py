@@ -44,6 +44,8 @@ class DecodeSession:
         self.h_tokens, self.h_positions = view(self._host, 0), view(self._host, 1)
         self._np = self._host.numpy()                       # the same pinned memory, for cheap host writes
         self._sampled_host = torch.zeros(count, dtype=torch.int32).pin_memory()
+        self._error_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._error_word = ops.error_flag(device)            # what kernels of this device report without a host in the loop
         self._capacity = [0] * count                        # tokens each request's pages hold (least over the groups)
         self.h_tables = [view(self._host, 8 + g).view(count, width) for g in range(groups)]
         view(self._host, 2).copy_(torch.arange(count))
@@ -139,7 +141,9 @@ class DecodeSession:
     def read_tokens(self) -> list[int]:
         """Host tokens out: the tokens the last step sampled, through pinned host memory."""
         self._sampled_host.copy_(self.sampled, non_blocking=True)
+        self._error_host.copy_(self._error_word, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        ops.raise_for_error_word(int(self._error_host[0]), self._error_word.device)
         return self._sampled_host.tolist()
 
     def step(self) -> torch.Tensor:

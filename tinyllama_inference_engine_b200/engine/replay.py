@@ -17,6 +17,7 @@ import json
 import sys
 from pathlib import Path
 
+from .. import ops
 from ..config import EngineConfig
 from ..errors import EngineError
 from .batch import StepEntry
@@ -27,8 +28,9 @@ REPLAY_LIVE_REQUESTS = 8
 def replay_engine_config(dtype: str, max_tokens: int, page_size: int = 64, device: str = "cuda:0") -> EngineConfig:
     """The engine options of a replay: a pool of exactly ``max_tokens`` (rounded up to whole pages)."""
     pages = max(1, -(-max_tokens // page_size))
+    # a step can bring at most what the pool holds, so that is the step's token budget too
     return EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=pages * page_size,
-                        max_requests=REPLAY_LIVE_REQUESTS, max_batch_tokens=256, device=device, use_cuda_graphs=False)
+                        max_requests=REPLAY_LIVE_REQUESTS, max_batch_tokens=max(256, pages * page_size), device=device, use_cuda_graphs=False)
 
 
 def replay_step(runner, step: dict):
@@ -37,7 +39,11 @@ def replay_step(runner, step: dict):
     logits = runner.step(entries) if entries else None
     for request_id in step.get("end", []):
         runner.finish(request_id)
-    return None if logits is None else logits.float().cpu()
+    if logits is None:
+        return None
+    host = logits.float().cpu()
+    ops.check_device_errors(runner.device)   # a fault a kernel recorded on the device makes the step fail, not its logits wrong
+    return host
 
 
 def main(argv: list[str] | None = None) -> int:

@@ -73,6 +73,9 @@ class ModelRunner:
                     f"request {entry.request_id!r} would reach {first + len(entry.tokens)} tokens; the model's context is {self.spec.max_positions}"
                 )
             firsts.append(first)
+        total = sum(len(entry.tokens) for entry in entries)
+        if total > self.engine_config.max_batch_tokens:
+            raise BatchError(f"the step brings {total} tokens; max_batch_tokens is {self.engine_config.max_batch_tokens}")
         if len(self.cache.records) + new_requests > self.cache.max_requests:
             raise BatchError(f"more than {self.cache.max_requests} live requests")
         return firsts

@@ -7,7 +7,7 @@ names parts and sizes; every formula lives in the parts.
 """
 from __future__ import annotations
 
-from ..config.model_config import LlamaConfig
+from .llama_config import LlamaConfig
 from ..config.registry import Architecture, register_architecture
 from ..parts.spec import LayerSpec, ModelSpec, OrderEntry, PartSpec
 

@@ -84,11 +84,46 @@ def _i32(tensor: torch.Tensor | None, what: str) -> c_void_p:
     return _ptr(tensor)
 
 
+# --- the device's error word -------------------------------------------------------------
+# Kernels that can notice a fault without a host in the loop record it in one int32 per device: bit 0, a bounded wait
+# inside a tensor-core kernel gave up (its results are garbage); bit 1, a token id outside the vocabulary reached the
+# embedding (row 0 was read instead).  The engine reads the word wherever it synchronises with the device anyway.
+_error_flags: dict[torch.device, torch.Tensor] = {}
+DEVICE_ERRORS = {1: "a bounded wait inside a tensor-core kernel gave up; the step's results are not valid",
+                 2: "a token id outside the vocabulary reached the embedding kernel (non-finite logits upstream?)"}
+
+
+def error_flag(device: torch.device) -> torch.Tensor:
+    """The device's error word (int32 [1]); kernels set bits in it, ``raise_for_error_word`` names and clears them."""
+    device = torch.device(device)
+    if device not in _error_flags:
+        _error_flags[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[device]
+
+
+def raise_for_error_word(word: int, device: torch.device) -> None:
+    """Raise KernelError if ``word`` (a host copy of the device's error word) has a bit set, clearing the word on the device."""
+    if word:
+        error_flag(device).zero_()
+        reasons = [text for bit, text in DEVICE_ERRORS.items() if word & bit] or [f"unknown error bits {word:#x}"]
+        raise KernelError("the device reported: " + "; ".join(reasons))
+
+
+def check_device_errors(device: torch.device) -> None:
+    """Read the device's error word (this synchronises) and raise if a kernel reported a fault."""
+    device = torch.device(device)
+    if device in _error_flags:
+        raise_for_error_word(int(_error_flags[device].item()), device)
+
+
 # --- rows --------------------------------------------------------------------------------
 def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> None:
-    """residual[t] = float(table[ids[t]])."""
+    """residual[t] = float(table[ids[t]]); an id outside the table reads row 0 and sets bit 1 of the device's error word."""
     rows, hidden = residual.shape
-    _check(core().tlie_embedding(_code(table), _ptr(table), _i32(ids, "ids"), _ptr(residual), c_int(rows), c_int(hidden), _stream()), "embedding")
+    if table.shape[1] != hidden:
+        raise KernelError("embedding: the table's width is not the residual's", code="invalid_shape")
+    _check(core().tlie_embedding(_code(table), _ptr(table), _i32(ids, "ids"), _ptr(residual), c_int(rows), c_int(hidden), c_int(table.shape[0]),
+                                 _ptr(error_flag(residual.device)), _stream()), "embedding")
 
 
 def add_rmsnorm(residual, delta, weight, eps: float, out, rows=None) -> None:

@@ -14,7 +14,15 @@ from ..errors import KernelError
 from .build import build_library, load_library
 
 library_gemm_calls = 0  # vendor-library matrix products issued (not this engine's kernels)
-SM_COUNT = 148
+
+
+@functools.lru_cache(maxsize=None)
+def sm_count() -> int:
+    """Streaming multiprocessors of the current CUDA device (148 on a B200, which is also the answer without a device)."""
+    if torch.cuda.is_available():
+        return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    return 148
+
 DEFAULT_HEAD_DIMS = (64, 128)
 _scratch: dict[torch.device, list[torch.Tensor]] = {}
 
@@ -119,7 +127,6 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
 
 
 # --- tensor-core product for many rows (tcgen05, TMA, tensor memory) -------------------------------------
-_tcgen05_error: dict[torch.device, torch.Tensor] = {}
 TCGEN05_MIN_ROWS = 128     # from this many rows on the engine's own tcgen05 kernel runs instead of the library's product
 use_tcgen05 = True
 
@@ -139,7 +146,7 @@ def tcgen05_takes(M: int, N: int, K: int) -> bool:
     saved.)"""
     if M < TCGEN05_MIN_ROWS:
         return False
-    return -(-M // 128) * -(-N // 256) >= SM_COUNT // 2 or K < 4096
+    return -(-M // 128) * -(-N // 256) >= sm_count() // 2 or K < 4096
 
 
 def tcgen05_library():
@@ -147,10 +154,8 @@ def tcgen05_library():
 
 
 def tcgen05_error_flag(device: torch.device) -> torch.Tensor:
-    """A device int the kernel sets to 1 if one of its bounded waits gave up (read it after a synchronize)."""
-    if device not in _tcgen05_error:
-        _tcgen05_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tcgen05_error[device]
+    """The device's error word: the tensor-core kernels set bit 0 of it if one of their bounded waits gave up."""
+    return _ops().error_flag(device)
 
 
 GEMM_TILE_WIDTHS = (256, 192, 160, 128)
@@ -169,7 +174,7 @@ def gemm_tile_width(M: int, N: int, pair: bool = False) -> int:
 
     A tile costs its width plus a fixed part about as large as 300 columns (measured: a 128 x 160 tile takes 0.8 of the time
     of a 128 x 256 one), so the widest tile wins unless a narrower one saves a whole wave; the wider tile on a tie."""
-    workers = SM_COUNT // 2 if pair else SM_COUNT
+    workers = sm_count() // 2 if pair else sm_count()
     row_blocks = -(-M // (256 if pair else 128))
     return min(GEMM_TILE_WIDTHS, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * (width + 300), -width))
 
@@ -275,7 +280,7 @@ def decode_attention_library(head_dim: int, narrow: bool = False):
 
 def decode_splits(requests: int, kv_heads: int, max_context: int) -> int:
     """Parts the key range is cut into: at most one CTA (eight warps) per SM, at least 256 keys per part, at most 32 parts."""
-    by_occupancy = max(1, SM_COUNT // max(1, requests * kv_heads))   # rounded down: one CTA too many is a second wave
+    by_occupancy = max(1, sm_count() // max(1, requests * kv_heads))   # rounded down: one CTA too many is a second wave
     by_length = max(1, -(-max_context // 256))
     return max(1, min(by_occupancy, by_length, 32))
 
@@ -297,7 +302,7 @@ def decode_attention(qkv, pages, positions, block_table, out, q_heads: int, kv_h
     """
     ops = _ops()
     requests = qkv.shape[0]
-    lib = decode_attention_library(head_dim, narrow=requests * kv_heads > SM_COUNT)
+    lib = decode_attention_library(head_dim, narrow=requests * kv_heads > sm_count())
     floats = lib.tlie_decode_attention_scratch_floats(c_int(requests), c_int(q_heads), c_int(splits))
     buffer = scratch(qkv.device, floats)
     ops._check(
@@ -314,7 +319,7 @@ def can_fuse_rope_into_decode(batch, qkv, head_dim: int, q_heads: int, kv_heads:
     """Whether a decode step's rotation and cache write can happen inside the attention kernel."""
     if batch is None or qkv.dtype != torch.bfloat16 or not batch.decode_only or qkv.shape[0] != batch.num_seqs:
         return False
-    if head_dim > 128 or q_heads // kv_heads > 16 or batch.num_seqs * kv_heads > 16384:
+    if head_dim % 16 != 0 or head_dim > 128 or q_heads // kv_heads > 16 or batch.num_seqs * kv_heads > 16384:
         return False
     return inv_freq is None or (rotary_dim == head_dim and head_dim % 32 == 0)
 

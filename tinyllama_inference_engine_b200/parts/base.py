@@ -35,7 +35,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..errors import ConfigError
+from ..errors import BatchError, ConfigError
 from .spec import PartSpec, TensorSpec
 
 
@@ -72,7 +72,10 @@ class LayerCache:
 
 
 class Workspace:
-    """Named activation buffers of fixed address, sized once for the largest step."""
+    """Named activation buffers of fixed address, sized once for the largest step.
+
+    A buffer never moves and never grows: a captured CUDA graph keeps the address it saw, so a step of more rows than
+    ``max_tokens`` is refused instead of being given a new buffer."""
 
     def __init__(self, device: torch.device, max_tokens: int):
         self.device = device
@@ -80,11 +83,12 @@ class Workspace:
         self._buffers: dict[tuple, torch.Tensor] = {}
 
     def get(self, name: str, rows: int, width: int, dtype: torch.dtype) -> torch.Tensor:
+        if rows > self.max_tokens:
+            raise BatchError(f"a step of {rows} rows does not fit the workspace of {self.max_tokens} (max_batch_tokens)")
         key = (name, width, dtype)
-        capacity = max(self.max_tokens, rows)
         buffer = self._buffers.get(key)
-        if buffer is None or buffer.shape[0] < capacity:
-            buffer = torch.empty((capacity, width), dtype=dtype, device=self.device)
+        if buffer is None:
+            buffer = torch.empty((self.max_tokens, width), dtype=dtype, device=self.device)
             self._buffers[key] = buffer
         return buffer[:rows]
 

@@ -37,8 +37,9 @@ class LinearHead(Part):
     """logits = W . normed, 32-bit out, for the wanted rows only (src/model.cpp:217-225).
 
     params: ``vocab_size``, ``hidden_size``, ``name``, ``tied_to`` (name of the
-    embedding table, or None).  With ``tied_to`` and no tensor of its own the head
-    aliases the embedding table; the reference refuses tied checkpoints
+    embedding table, or None).  With ``tied_to`` the head's own tensor is optional:
+    a checkpoint that stores it anyway is read as it is, one that does not makes the
+    head alias the embedding table.  The reference refuses tied checkpoints
     (src/model_config.cpp:72).
     """
 
@@ -46,14 +47,13 @@ class LinearHead(Part):
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
-        if spec.get("tied_to"):
-            return []
-        return [TensorSpec(f"{spec['name']}.weight", (spec["vocab_size"], spec["hidden_size"]))]
+        return [TensorSpec(f"{spec['name']}.weight", (spec["vocab_size"], spec["hidden_size"]), optional=bool(spec.get("tied_to")))]
 
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
-        source = spec.get("tied_to") or spec["name"]
-        self.weight = weights.get(f"{source}.weight", runtime.dtype).contiguous()
+        own = f"{spec['name']}.weight"
+        source = own if not spec.get("tied_to") or weights.has(own) else f"{spec['tied_to']}.weight"
+        self.weight = weights.get(source, runtime.dtype).contiguous()
         self.vocab = int(spec["vocab_size"])
 
     def forward(self, normed_rows):

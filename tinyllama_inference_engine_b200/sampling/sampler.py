@@ -28,4 +28,6 @@ class Sampler:
             seeds = torch.tensor([[p.seed, k] for p, k in zip(params, draw_indices)], dtype=torch.int64)
             host, seeds = host.to(logits.device), seeds.to(logits.device)
             ops.sample(logits, host[:, 0].contiguous(), host[:, 1].contiguous(), seeds[:, 0].contiguous(), seeds[:, 1].contiguous(), out)
-        return out.cpu().tolist()
+        tokens = out.cpu().tolist()                 # the host waits for the step here,
+        ops.check_device_errors(logits.device)      # so this is where a fault a kernel recorded on the device surfaces
+        return tokens

@@ -43,12 +43,16 @@ def random_tensors(expected: Iterable[TensorSpec], seed: int, dtype: torch.dtype
 
 
 def write_random_model(folder: str | Path, config: Any, seed: int, storage_dtype: str | None = None) -> Path:
-    """Write ``config.json`` and ``model.safetensors`` for ``config`` (any registered architecture)."""
+    """Write ``config.json`` and ``model.safetensors`` for ``config`` (any registered architecture).
+
+    ``config`` is a typed configuration or the dictionary of a config.json, which the registry turns into one."""
     from ..config.registry import architecture_for
     from ..models.model import expected_tensors
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
+    if isinstance(config, dict):
+        config = architecture_for(config).config_class.from_dict(config)
     data = config.to_dict()
     architecture = architecture_for(data)
     spec = architecture.build_spec(config)

@@ -3,9 +3,12 @@
 In the manner of the reference's WeightStore::Load / Get / Validate
 (src/weight_store.cpp:118-295): every expected tensor is looked up once, and the
 folder is refused with ONE error that lists every missing tensor, every unexpected
-tensor and every wrong shape.  Storage rule: 16-bit floating tensors are kept in
-bfloat16, a tensor stored in 32-bit stays 32-bit, integer tables become int32.
-Parts ask for the dtype they compute in when they are built.
+tensor and every wrong shape.  Storage rule: a tensor is kept as the file has it
+(bfloat16 stays bfloat16, float16 stays float16, 32-bit stays 32-bit), integer tables
+become int32.  Parts ask for the dtype they compute in when they are built
+(``get(name, dtype)``): the 32-bit engine therefore sees every 16-bit value exactly,
+and only the bfloat16 engine rounds a float16 checkpoint (the reference's GPU
+checkpoints are float16, scripts/convert_model_fp16.py:23-67) to bfloat16.
 """
 from __future__ import annotations
 
@@ -24,7 +27,7 @@ def _storage_dtype(dtype: torch.dtype, integer: bool) -> torch.dtype:
     if dtype in (torch.float32, torch.float64):
         return torch.float32
     if dtype in (torch.bfloat16, torch.float16):
-        return torch.bfloat16
+        return dtype
     if dtype in (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8, torch.bool):
         return torch.int32
     raise EngineError(f"unsupported tensor dtype {dtype}", code="invalid_dtype")
