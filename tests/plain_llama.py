@@ -20,9 +20,9 @@ _NP = {"F32": np.float32, "F16": np.float16, "I32": np.int32, "I64": np.int64}
 
 def read_safetensors(path) -> dict[str, torch.Tensor]:
     """Minimal reader of its own (header length, JSON header, raw payload); values as float32."""
-    raw = Path(path).read_bytes()
-    (n,) = struct.unpack("<Q", raw[:8])
-    header = json.loads(raw[8 : 8 + n])
+    raw = np.memmap(path, dtype=np.uint8, mode="r")
+    (n,) = struct.unpack("<Q", raw[:8].tobytes())
+    header = json.loads(raw[8 : 8 + n].tobytes())
     out = {}
     for name, info in header.items():
         if name == "__metadata__":
@@ -30,11 +30,10 @@ def read_safetensors(path) -> dict[str, torch.Tensor]:
         begin, end = info["data_offsets"]
         blob = raw[8 + n + begin : 8 + n + end]
         if info["dtype"] == "BF16":
-            bits = np.frombuffer(blob, dtype=np.uint16).astype(np.uint32) << 16
-            array = bits.view(np.float32)
+            value = torch.from_numpy(np.array(blob)).view(torch.bfloat16).to(torch.float32)   # exact: bfloat16 is the upper half of a float32
         else:
-            array = np.frombuffer(blob, dtype=_NP[info["dtype"]]).astype(np.float32)
-        out[name] = torch.from_numpy(array.reshape(info["shape"]).copy())
+            value = torch.from_numpy(np.array(blob).view(_NP[info["dtype"]]).astype(np.float32))
+        out[name] = value.reshape(info["shape"])
     return out
 
 
@@ -86,13 +85,16 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = 0
     groups = heads // k.shape[1]
     scale = (1.0 / np.sqrt(np.float32(D))) if scale is None else scale
     out = torch.zeros_like(q)
+    # keys a query may not see get a score of -inf: exp gives exactly 0, so sums and products are those of the visible keys
+    query, key = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    hidden = key > query
+    if window > 0:
+        hidden = hidden | (key < query - window + 1)
     for h in range(heads):
         g = h // groups
         scores = (q[:, h, :] @ k[:, g, :].T) * np.float32(scale)
-        for i in range(S):
-            lo = max(0, i - window + 1) if window > 0 else 0
-            p = softmax_rows(scores[i, lo : i + 1][None, :])[0]
-            out[i, h, :] = p @ v[lo : i + 1, g, :]
+        p = softmax_rows(scores.masked_fill(hidden, float("-inf")))
+        out[:, h, :] = p @ v[:, g, :]
     return out
 
 
@@ -111,8 +113,11 @@ def greedy(logits: torch.Tensor) -> int:
     return int(torch.nonzero(logits == logits.max())[0].item())
 
 
-def forward(config: dict, w: dict[str, torch.Tensor], tokens: list[int], trace: dict | None = None) -> torch.Tensor:
-    """Logits [len(tokens), vocab] of one whole sequence (src/model.cpp:80-234, one position at a time there)."""
+def forward(config: dict, w: dict[str, torch.Tensor], tokens: list[int], trace: dict | None = None, rows: list[int] | None = None) -> torch.Tensor:
+    """Logits [len(tokens), vocab] of one whole sequence (src/model.cpp:80-234, one position at a time there).
+
+    ``rows``: only these positions' logits (a large vocabulary makes the head the most expensive product of all).
+    ``trace``: filled with every layer's output (the reference's ModelTrace, src/model.cpp:98-100, 200-206)."""
     H = config["hidden_size"]
     heads = config["num_attention_heads"]
     kv_heads = config.get("num_key_value_heads") or heads
@@ -135,6 +140,8 @@ def forward(config: dict, w: dict[str, torch.Tensor], tokens: list[int], trace: 
         hidden = hidden + linear(w[p + "mlp.down_proj.weight"], act)      # :196-203
         if trace is not None:
             trace[f"layer{layer}.output"] = hidden.clone()
+    if rows is not None:
+        hidden = hidden[torch.tensor(rows, dtype=torch.long)]
     normed = rms_norm(hidden, w["model.norm.weight"], eps)                # :217
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return linear(head, normed)                                           # :225

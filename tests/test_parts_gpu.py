@@ -158,8 +158,9 @@ def test_embedding_and_head_parts(dtype, fraction):
     residual = embedding.forward(ids.cuda())
     assert residual.dtype == torch.float32 and torch.equal(residual.cpu(), table[ids.long()])
     x = torch.randn(4, HIDDEN).bfloat16().float()
-    for tied, matrix in ((None, own), ("emb", table)):
-        head = build_part("head", PartSpec("linear_head", {"vocab_size": vocab, "hidden_size": HIDDEN, "name": "out", "tied_to": tied}), "", weights, runtime)
+    # untied: its own tensor; tied without a tensor of its own: the embedding table; tied with one stored all the same: that one
+    for tied, stored, matrix in ((None, weights, own), ("emb", _weights({"emb.weight": table}), table), ("emb", weights, own)):
+        head = build_part("head", PartSpec("linear_head", {"vocab_size": vocab, "hidden_size": HIDDEN, "name": "out", "tied_to": tied}), "", stored, runtime)
         logits = head.forward(x.cuda().to(dtype))
         assert logits.dtype == torch.float32
         _close(logits, plain_llama.linear(matrix, x), fraction)

@@ -118,3 +118,79 @@ def test_float32_rows_do_not_depend_on_the_cut(cases, key):
             entries.insert(0, {"id": "o", "tokens": [other[i]], "want": []})
         rows.append(replay_step(b, {"step": i, "entries": entries, "end": []})[0])
     assert torch.equal(torch.stack(rows), whole)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["d", "e"])
+def test_mixed_steps_with_long_portions(cases, key, dtype):
+    """Portions of up to 300 tokens that start anywhere inside a request, beside decoded tokens of up to three other requests:
+    the tensor-core products, their accumulate epilogue and the prompt attention kernels (head size 128 and 64) in steps that also
+    carry single rows, with a pool of exactly the peak so that pages are used again."""
+    folder, requests, full, scale = cases[key]
+    steps, peak = trace_tools.mixed(requests, seed=8, max_portion=300, page_size=64)
+    assert max(len(e["tokens"]) for s in steps for e in s["entries"]) >= 128
+    assert any(len(s["entries"]) > 1 and max(len(e["tokens"]) for e in s["entries"]) >= 128 and min(len(e["tokens"]) for e in s["entries"]) == 1 for s in steps)
+    runner = _runner(folder, dtype, max_tokens=peak, page_size=64)
+    worst = trace_tools.run_and_compare(runner, steps, full, atol=TOLERANCE[dtype] * scale)
+    runner.cache.check()
+    assert not runner.cache.records and runner.cache.stats()["groups"][0]["reuses"] > 0
+    print(f"{key} {dtype} mixed with long portions: worst {worst:.3e} of scale {scale:.3f}")
+
+
+def _crowd(folder, live: int, decoded: int, seed: int):
+    """``live`` requests with prompts of mixed length, and the plain logits of each."""
+    config, weights = plain_llama.load_model(folder)
+    rng = __import__("numpy").random.default_rng(seed)
+    lengths = [int(n) + decoded for n in rng.integers(3, 90, size=live)]
+    requests = trace_tools.make_requests(config["vocab_size"], lengths, seed=seed + 1)
+    full = {rid: plain_llama.forward(config, weights, tokens) for rid, tokens in requests.items()}
+    return requests, full, max(float(v.abs().max()) for v in full.values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key,live", [("e", 24), ("e", 64), ("d", 64), ("b", 33)])
+def test_many_requests_decode_together(model_folders, key, live, dtype):
+    """24, 33 and 64 live requests: prompts in steps of several requests, then all of them decoding in one step, every row's logits
+    compared.  Between 17 and 127 rows the bfloat16 products are not the small-step kernels any more, and with more (request, kv
+    head) pairs than SMs decode attention runs its narrow build; neither is reached by four live requests."""
+    decoded = 6
+    folder = model_folders[key]
+    requests, full, scale = _crowd(folder, live, decoded, seed=31)
+    steps, ids = [], list(requests)
+    for begin in range(0, live, 7):   # prompts, seven requests a step
+        group = ids[begin : begin + 7]
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": requests[rid][:-decoded], "want": [len(requests[rid]) - decoded - 1]} for rid in group], "end": []})
+    for k in range(decoded, 0, -1):   # then everybody decodes together
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": [requests[rid][-k]], "want": [0]} for rid in ids], "end": ids if k == 1 else []})
+    runner = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=16 if key == "b" else 64, max_cache_tokens=live * 128, max_requests=live, max_batch_tokens=1024, poison_freed_pages=True))
+    worst = trace_tools.run_and_compare(runner, steps, full, atol=TOLERANCE[dtype] * scale)
+    runner.cache.check()
+    print(f"{key} {live} live {dtype}: worst {worst:.3e} of scale {scale:.3f}")
+
+
+@pytest.mark.parametrize("key,live", [("e", 64), ("d", 24)])
+def test_decode_session_of_many_requests(model_folders, key, live):
+    """The same crowd through a decode session: steps kernel by kernel, the capture, and replays of the graph, fed with given tokens;
+    the logits of every step against the plain implementation."""
+    from tinyllama_inference_engine_b200.engine.batch import StepEntry
+    from tinyllama_inference_engine_b200.engine.decode_session import DecodeSession
+
+    decoded = 6
+    folder = model_folders[key]
+    requests, full, scale = _crowd(folder, live, decoded, seed=37)
+    ids = list(requests)
+    runner = ModelRunner(folder, EngineConfig(dtype="bfloat16", page_size=64, max_cache_tokens=live * 128, max_requests=live, max_batch_tokens=1024))
+    for rid in ids:
+        runner.step([StepEntry(rid, requests[rid][:-decoded], [])])
+    session = DecodeSession(runner, live)
+    session.load(ids, [requests[rid][-decoded] for rid in ids])
+    for k in range(decoded, 0, -1):
+        if k != decoded:
+            session.set_tokens([requests[rid][-k] for rid in ids])
+        session.step()
+        torch.cuda.synchronize()
+        got = session.logits.float().cpu()
+        want = torch.stack([full[rid][len(requests[rid]) - k] for rid in ids])
+        error = float((got - want).abs().max())
+        assert error <= TOLERANCE["bfloat16"] * scale, (k, error, scale)
+    assert session.graph is not None   # the later steps were replays

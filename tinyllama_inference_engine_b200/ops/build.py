@@ -47,9 +47,8 @@ def build_dir() -> Path:
     for folder in candidates:
         try:
             folder.mkdir(parents=True, exist_ok=True)
-            probe = folder / f".probe_{os.getpid()}"
-            probe.write_text("")
-            probe.unlink()
+            with tempfile.NamedTemporaryFile(prefix=".probe_", dir=folder):   # a name of its own: threads and processes may ask at once
+                pass
             return folder
         except OSError:
             continue
