@@ -391,6 +391,66 @@ def test_gemv_fused(ops, M, N, K):
         assert torch.allclose(via_prepared, via_norm, rtol=1e-5, atol=1e-6 * float(via_norm.abs().max()))
 
 
+@pytest.mark.parametrize("M", [1, 17, 33, 64, 100, 127])
+@pytest.mark.parametrize("N,K", [(130, 80), (2560, 2048), (2048, 5632), (1000, 200), (4096, 14336), (32000, 2048)])
+def test_gemm_skinny(ops, M, N, K):
+    """The weight-streaming tensor-core product of 17 to 127 rows against the 32-bit product: every epilogue, K cut over clusters of
+    every size (the shapes give 1 to 8 parts), widths and depths that are no multiple of the tile, and the prepared-norm hand-over."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    torch.manual_seed(13)
+    x = torch.randn(M, K).bfloat16()
+    w = (torch.randn(N, K) * 0.05).bfloat16()
+    want = x.float() @ w.float().T
+    scale = float(want.abs().max())
+    xc, wc = x.cuda(), w.cuda()
+    for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 1.6e-2)):
+        got = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+        fast.gemm_skinny(xc, wc, got)
+        error = (got.cpu().float() - want).abs()
+        assert float(error.max()) <= tol * scale, (dtype, float(error.max()), scale, divmod(int(error.argmax()), N))
+    residual = torch.randn(M, N)
+    got = residual.clone().cuda()
+    fast.gemm_skinny(xc, wc, got, epilogue="accumulate")
+    assert torch.allclose(got.cpu(), residual + want, atol=1e-4 * scale + 1e-5)
+    again = residual.clone().cuda()
+    fast.gemm_skinny(xc, wc, again, epilogue="accumulate")
+    assert torch.equal(again, got)   # the parts are added in rank order: the same bits every time
+    half = N // 2
+    g, u = want[:, :half].bfloat16().float(), want[:, half:2 * half].bfloat16().float()
+    gated = torch.full((M, half), float("nan"), dtype=torch.bfloat16, device="cuda")
+    fast.gemm_skinny(xc, wc[: 2 * half], gated, epilogue="gated")
+    expect = (g / (1 + torch.exp(-g))) * u
+    assert torch.allclose(gated.cpu().float(), expect, atol=1.6e-2 * float(expect.abs().max()) + 2e-3 * scale)
+    # a product that completes the residual prepares the norm that follows; the next product scales its results by the rows' norms
+    if N <= 4096:
+        torch.manual_seed(14)
+        residual = torch.randn(M, N) * 2
+        next_weight = 1 + 0.1 * torch.randn(N)
+        w2 = (torch.randn(72, N) * 0.05).bfloat16()
+        total = residual.clone().cuda()
+        x_out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        squares = torch.full((M, fast.skinny_square_runs(M, N, K) + 3), float("nan"), dtype=torch.float32, device="cuda")[:, :-3]   # rows may be strided
+        fast.gemm_skinny(xc, wc, total, epilogue="accumulate", prepare=(next_weight.cuda(), x_out, squares))
+        assert torch.allclose(total.cpu(), residual + want, atol=1e-4 * scale + 1e-5)
+        assert torch.equal(x_out.cpu(), (total.cpu() * next_weight).bfloat16())
+        assert torch.allclose(squares.sum(1).cpu(), (total.cpu() ** 2).sum(1), rtol=1e-5)
+        if N % 8 == 0:
+            normed = torch.empty(M, N, dtype=torch.bfloat16)
+            plain_ops.add_rmsnorm(total.cpu().clone(), None, next_weight, 1e-5, normed)
+            want_n = normed.float() @ w2.float().T
+            via_prepared = torch.full((M, 72), float("nan"), dtype=torch.float32, device="cuda")
+            fast.gemm_skinny(x_out, w2.cuda(), via_prepared, prepared=(squares, 1e-5))
+            assert torch.allclose(via_prepared.cpu(), want_n, atol=6e-3 * float(want_n.abs().max())), float((via_prepared.cpu() - want_n).abs().max())
+            gated_n = torch.full((M, 36), float("nan"), dtype=torch.bfloat16, device="cuda")
+            fast.gemm_skinny(x_out, w2.cuda(), gated_n, epilogue="gated", prepared=(squares, 1e-5))
+            gn, un = want_n[:, :36].bfloat16().float(), want_n[:, 36:].bfloat16().float()
+            expect_n = (gn / (1 + torch.exp(-gn))) * un
+            assert torch.allclose(gated_n.cpu().float(), expect_n, atol=2.5e-2 * float(expect_n.abs().max()) + 6e-3 * float(want_n.abs().max()))
+    torch.cuda.synchronize()
+    assert int(fast.tcgen05_error_flag(got.device)) == 0, "a bounded wait inside the kernel gave up"
+
+
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window,rotate", [
     (32, 4, 64, 64, 0, True), (8, 8, 128, 64, 0, True), (6, 2, 32, 32, 0, True), (8, 2, 64, 16, 100, True), (4, 2, 64, 16, 0, False), (12, 3, 96, 16, 0, True),
 ])

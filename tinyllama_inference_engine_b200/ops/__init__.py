@@ -213,11 +213,15 @@ def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
     """out = rmsnorm(residual) * norm_weight . weight^T in one kernel (``gated``: silu(gate) * up of the two halves)."""
     from . import fast
 
+    epilogue = "gated" if gated else "store"
     if fast.gemv_fits(out.shape[0], weight.shape[1], norm=True, gated=gated):
         if x.prepared is not None:
-            fast.gemv_fused(x.prepared[0], weight, out, prepared=(x.prepared[1], x.eps), epilogue="gated" if gated else "store")
+            fast.gemv_fused(x.prepared[0], weight, out, prepared=(x.prepared[1], x.eps), epilogue=epilogue)
         else:
-            fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), epilogue="gated" if gated else "store")
+            fast.gemv_fused(x.residual, weight, out, norm=(x.weight, x.eps, x.rows), epilogue=epilogue)
+    elif fast.use_skinny and x.prepared is not None and fast.skinny_fits(out.shape[0], weight, x.prepared[0]) and out.is_contiguous():
+        # the rows' scale is applied to the product's result: the operand is bfloat16(residual * norm weight) as it was left
+        fast.gemm_skinny(x.prepared[0], weight, out, epilogue=epilogue, prepared=(x.prepared[1], x.eps))
     elif gated:
         linear_gated(x.tensor(), weight, out)
     else:
@@ -232,24 +236,40 @@ def can_accumulate(rows: int, weight) -> bool:
 
 
 def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) -> None:
-    """residual += x . weight^T, the sum in 32-bit, in one kernel (bfloat16 x; up to the fused row limit in the weight-streaming
-    kernel, for prompt portions in the tensor-core product's epilogue).
+    """residual += x . weight^T, the sum in 32-bit, in one kernel (bfloat16 x; up to 16 rows in the register-fed weight-streaming
+    kernel, up to 127 in the tensor-core one, for prompt portions in the tensor-core product's epilogue).
 
     ``prepare``: the lazy norm of this residual (all rows) that the next product will consume; the kernel then leaves that
     norm's input beside the residual (``prepare.prepared``), written by the threads that hold the finished sums."""
     from . import fast
 
-    if fast.gemv_fits(x.shape[0], weight.shape[1], norm=False):
-        if prepare is not None and prepare.rows is None and prepare.residual is residual and use_prepared_norms and residual.shape[0] >= PREPARED_NORM_MIN_ROWS:
+    rows = x.shape[0]
+    preparing = (prepare is not None and prepare.rows is None and prepare.residual is residual and use_prepared_norms
+                 and residual.shape[0] >= PREPARED_NORM_MIN_ROWS)
+    if fast.gemv_fits(rows, weight.shape[1], norm=False):
+        if preparing:
             buffers = fast.prepared_norm_buffers(residual.shape[0], residual.shape[1], residual.device) if prepare.buffers is None else prepare.buffers
             fast.gemv_fused(x, weight, residual, epilogue="accumulate", prepare=(prepare.weight, buffers[0], buffers[1]))
             prepare.prepared = buffers
         else:
             fast.gemv_fused(x, weight, residual, epilogue="accumulate")
-    elif x.dtype == torch.bfloat16 and fast.can_accumulate(x.shape[0], weight) and x.is_contiguous() and residual.is_contiguous():
+    elif fast.use_skinny and fast.skinny_fits(rows, weight, x) and residual.is_contiguous():
+        buffers = None
+        if preparing:
+            buffers = fast.prepared_norm_buffers(residual.shape[0], residual.shape[1], residual.device) if prepare.buffers is None else prepare.buffers
+            runs = fast.skinny_square_runs(rows, weight.shape[0], weight.shape[1])   # this kernel's partial sums per row: one per CTA that finishes a run of columns
+            if runs > buffers[1].shape[1]:
+                buffers = None   # a narrow matrix cut many ways: more partial sums than the buffer has room for
+        if buffers is not None:
+            squares = buffers[1][:, :runs]
+            fast.gemm_skinny(x, weight, residual, epilogue="accumulate", prepare=(prepare.weight, buffers[0], squares))
+            prepare.prepared = (buffers[0], squares)
+        else:
+            fast.gemm_skinny(x, weight, residual, epilogue="accumulate")
+    elif x.dtype == torch.bfloat16 and fast.can_accumulate(rows, weight) and x.is_contiguous() and residual.is_contiguous():
         fast.gemm_tcgen05_accumulate(x, weight, residual)
     else:
-        delta = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        delta = torch.empty((rows, weight.shape[0]), dtype=x.dtype, device=x.device)
         linear(x, weight, delta)
         add_(residual, delta)
 
@@ -262,6 +282,8 @@ def linear_gated(x, weight, out) -> None:
         fast.gemv_fused(x, weight, out, epilogue="gated")
     elif fast.use_tcgen05 and x.shape[0] >= fast.TCGEN05_MIN_ROWS and weight.shape[1] % 8 == 0 and x.is_contiguous():
         fast.gemm_tcgen05_gated(x, weight, out)
+    elif fast.use_skinny and fast.skinny_fits(x.shape[0], weight, x) and out.is_contiguous() and out.dtype == torch.bfloat16:
+        fast.gemm_skinny(x, weight, out, epilogue="gated")
     else:
         gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
         linear(x, weight, gate_up)

@@ -6,6 +6,8 @@ and compiled only for what a model needs.
 from __future__ import annotations
 
 import functools
+import os
+import weakref
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -32,6 +34,7 @@ def build_all() -> list:
     built.append(build_library("tlie_attn_decode_d64_w4", ["attention_decode.cu"], {"HEAD_DIM": 64, "DECODE_WARPS": 4, "DECODE_STAGES": 3}))
     built += [build_library(f"tlie_attn_prefill_d{d}", ["attention_prefill.cu"], {"HEAD_DIM": d}) for d in DEFAULT_HEAD_DIMS]
     built.append(build_library("tlie_gemv_fused", ["gemv_fused.cu"]))
+    built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
     built.append(build_library("tlie_gemm_tcgen05", TCGEN05_SOURCES))
     built.append(build_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"]))
     return built
@@ -58,7 +61,7 @@ def gemv_library():
 
 def gemv_fits(rows: int, K: int, norm: bool, gated: bool = False) -> bool:
     """Whether the fused kernel's shared memory (x as bfloat16 and the warps' partial tiles) fits."""
-    if rows > FUSED_MAX_ROWS or K % 8 != 0:
+    if rows > GEMV_KERNEL_MAX_ROWS or K % 8 != 0:
         return False
     padded_rows = 8 if rows <= 8 else 16
     stride = K + ((32 - K % 64) + 64) % 64
@@ -124,6 +127,111 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
         emit = (ops._ptr(norm_weight), ops._ptr(x_out), ops._ptr(squares_out))
     ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), *consume, *emit, ops._stream()),
                "gemv_fused")
+
+
+# --- tensor-core product for 17 to 127 rows (tcgen05 with the operands swapped, K cut over a cluster) -----------------
+SKINNY_MAX_ROWS = 127      # steps of more rows than the register-fed kernels take and fewer than a 128-row tile
+# Off unless asked for (``enable_skinny`` or TLIE_SKINNY=1).  Measured on the 1.1B shapes, a decode step of 24 / 32 / 64 requests:
+# 1.28 / 1.28 / 1.64 ms with this kernel and its fusions against 1.14 / 1.15 / 1.29 ms on the library's products with separate
+# norm and activation kernels.  Its tiles are few (10 for 2,560 weight rows), so K is cut over a cluster, and what the CTAs then
+# exchange (64 rows x 256 columns of 32-bit partial sums each) is half as many bytes as the weights they read.
+use_skinny = False
+
+
+def enable_skinny(on: bool = True) -> None:
+    """Route products of 17 to 127 rows (and what surrounds them: norm in front, gate or residual add behind) to ``gemm_skinny``."""
+    global use_skinny, FUSED_MAX_ROWS
+    use_skinny = bool(on)
+    FUSED_MAX_ROWS = SKINNY_MAX_ROWS if on else GEMV_KERNEL_MAX_ROWS
+
+
+_SKINNY_EPILOGUES = {"store": None, "gated": 2, "accumulate": 3}
+
+
+def skinny_library():
+    return load_library("tlie_gemm_skinny", ["gemm_skinny.cu"])
+
+
+def skinny_fits(rows: int, weight, x=None) -> bool:
+    """Whether ``gemm_skinny`` takes a product of this many rows with this weight (and this x, if given)."""
+    if not 1 <= rows <= SKINNY_MAX_ROWS or weight.dtype != torch.bfloat16 or weight.shape[1] % 8 != 0 or not weight.is_contiguous():
+        return False
+    return x is None or (x.dtype == torch.bfloat16 and x.is_contiguous() and x.data_ptr() % 16 == 0)
+
+
+_skinny_packed: dict[tuple, tuple] = {}
+
+
+def skinny_packed(weight: torch.Tensor, gated: bool = False) -> torch.Tensor:
+    """The copy of ``weight`` that ``gemm_skinny`` streams: its 128 x 64 operand tiles, each as the contiguous 16 KB image the tensor
+    cores read from shared memory (``gated``: a group is 64 gate rows and the 64 up rows of the same outputs).  Made on first use and
+    kept for as long as the weight tensor lives: weights do not change, and a captured graph keeps pointing at the copy.  The entry
+    is tied to the tensor object itself (an address alone could be handed to another tensor once this one is freed)."""
+    key = (weight.data_ptr(), tuple(weight.shape), bool(gated), weight.device)
+    found = _skinny_packed.get(key)
+    if found is not None and found[0]() is weight:
+        return found[1]
+    ops = _ops()
+    N, K = weight.shape
+    library = skinny_library()
+    if not getattr(library, "_tlie_typed", False):
+        library.tlie_gemm_skinny_packed_elements.restype = c_longlong
+        library._tlie_typed = True
+    elements = library.tlie_gemm_skinny_packed_elements(c_int(N), c_int(K), c_int(1 if gated else 0))
+    packed = torch.empty(elements, dtype=torch.bfloat16, device=weight.device)
+    ops._check(library.tlie_gemm_skinny_pack(ops._ptr(weight), ops._ptr(packed), c_int(N), c_int(K), c_int(1 if gated else 0), ops._stream()), "gemm_skinny_pack")
+    _skinny_packed[key] = (weakref.ref(weight, lambda _, key=key: _skinny_packed.pop(key, None)), packed)
+    return packed
+
+
+def skinny_square_runs(rows: int, N: int, K: int) -> int:
+    """Partial sums of squares per row that ``gemm_skinny(..., prepare=)`` leaves for a [N, K] weight and this many rows."""
+    return int(skinny_library().tlie_gemm_skinny_square_runs(c_int(rows), c_int(N), c_int(K)))
+
+
+def gemm_skinny(x, weight, out, *, epilogue: str = "store", prepared=None, prepare=None) -> None:
+    """out (+)= x . weight^T for up to 128 rows on the tensor cores, the weights streamed once; one kernel.
+
+    x         bfloat16 [M, K], contiguous.
+    prepared  (squares, eps): x is bfloat16(residual * norm weight) and ``squares`` [M, runs] (rows may be strided) partial sums of
+              squares of the residual's rows; every result is scaled by its row's 1 / sqrt(mean + eps) (not with "accumulate").
+    epilogue  "store": out [M, N] bfloat16 or 32-bit; "gated": weight is [gate rows | up rows], out [M, N / 2] = silu(gate) * up;
+              "accumulate": out is the 32-bit residual [M, N], out += result.
+    prepare   ("accumulate" only) (norm_weight [N], x_out bfloat16 [M, N], squares_out [M, skinny_square_runs(M, N, K)], rows may be
+              strided): also leave the next norm's input, for a later call with ``prepared``.
+    """
+    ops = _ops()
+    N, K = weight.shape
+    M = x.shape[0]
+    if not skinny_fits(M, weight, x) or x.shape[1] != K:
+        raise KernelError(f"gemm_skinny takes contiguous bfloat16 operands with K % 8 == 0 and at most {SKINNY_MAX_ROWS + 1} rows", code="invalid_shape")
+    code = _SKINNY_EPILOGUES[epilogue]
+    if epilogue == "store":
+        if out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError("gemm_skinny stores bfloat16 or 32-bit", code="invalid_dtype")
+        code = 1 if out.dtype == torch.float32 else 0
+    elif epilogue == "accumulate" and out.dtype != torch.float32:
+        raise KernelError("gemm_skinny accumulates into the 32-bit residual only", code="invalid_dtype")
+    elif epilogue == "gated" and (out.dtype != torch.bfloat16 or N % 2):
+        raise KernelError("gemm_skinny: a gated product stores bfloat16 and its weight has an even number of rows", code="invalid_shape")
+    if out.shape != (M, N // 2 if epilogue == "gated" else N) or not out.is_contiguous():
+        raise KernelError("gemm_skinny: the output's shape does not fit the weight", code="invalid_shape")
+    consume = (c_void_p(0), c_int(0), c_int(0), c_float(0.0))
+    if prepared is not None:
+        squares, eps = prepared
+        if epilogue == "accumulate" or squares.dtype != torch.float32 or squares.dim() != 2 or squares.shape[0] != M or squares.stride(1) != 1 or not squares.is_cuda:
+            raise KernelError("gemm_skinny: a prepared norm brings 32-bit sums of squares [M, runs], and not with accumulate", code="invalid_shape")
+        consume = (c_void_p(squares.data_ptr()), c_int(squares.shape[1]), c_int(squares.stride(0)), c_float(eps))
+    emit = (c_void_p(0), c_void_p(0), c_void_p(0), c_int(0))
+    if prepare is not None:
+        norm_weight, x_out, squares_out = prepare
+        if (epilogue != "accumulate" or norm_weight.dtype != torch.float32 or norm_weight.numel() != N or x_out.dtype != torch.bfloat16 or x_out.shape != (M, N)
+                or squares_out.dtype != torch.float32 or squares_out.dim() != 2 or squares_out.shape != (M, skinny_square_runs(M, N, K)) or squares_out.stride(1) != 1
+                or not x_out.is_contiguous() or not squares_out.is_cuda):
+            raise KernelError("gemm_skinny: prepare takes a 32-bit norm weight [N], bfloat16 [M, N] and 32-bit [M, skinny_square_runs(M, N, K)], with accumulate", code="invalid_shape")
+        emit = (ops._ptr(norm_weight), ops._ptr(x_out), c_void_p(squares_out.data_ptr()), c_int(squares_out.stride(0)))
+    ops._check(skinny_library().tlie_gemm_skinny(ops._ptr(x), ops._ptr(skinny_packed(weight, epilogue == "gated")), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code),
+                                                 *consume, *emit, ops._ptr(tcgen05_error_flag(x.device)), ops._stream()), "gemm_skinny")
 
 
 # --- tensor-core product for many rows (tcgen05, TMA, tensor memory) -------------------------------------
@@ -253,6 +361,9 @@ def linear_bf16(x, weight, out) -> None:
     if use_tcgen05 and tcgen05_takes(x.shape[0], weight.shape[0], weight.shape[1]) and weight.shape[1] % 8 == 0 and x.is_contiguous():
         gemm_tcgen05(x, weight, out)
         return
+    if use_skinny and skinny_fits(x.shape[0], weight, x) and out.is_contiguous():
+        gemm_skinny(x, weight, out)
+        return
     library_gemm_calls += 1
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
@@ -378,3 +489,7 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
                           head_dim, page_size, window, scale)
         return True
     return False
+
+
+if os.environ.get("TLIE_SKINNY", "0") == "1":
+    enable_skinny(True)
