@@ -111,6 +111,19 @@ def test_command_line_generates_on_the_gpu(model_folders, capsys):
     assert main(["benchmark", str(model_folders["a"]), "20", "6", "1", "2", "--batch", "2"]) == 0
     report = json.loads(capsys.readouterr().out)
     assert report["deterministic"] and report["median_decode_tokens_per_second"] > 0
+    # the prompt as seeded random ids, the cache given in pages of 16, timings split as the reference splits them
+    import numpy as np
+
+    seeded = [int(t) for t in np.random.default_rng(5).integers(0, config["vocab_size"], size=9)]
+    assert main(["generate", str(model_folders["a"]), "4", "--prompt-len", "9", "--prompt-seed", "5", "--page-size", "16", "--num-pages", "3", "--dtype", "float32"]) == 0
+    result = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert result["generated_tokens"] == plain_llama.generate_greedy(config, weights, seeded, 4) and result["prompt_tokens"] == 9
+    assert result["prefill_compute_ms"] > 0 and result["decode_compute_ms"] > 0 and result["decode_steps"] == 3
+    assert result["prefill_transfer_ms"] >= 0 and result["decode_transfer_ms"] >= 0
+    assert main(["generate", str(model_folders["a"]), "60", "--prompt-len", "9", "--page-size", "16", "--num-pages", "3"]) == 1   # 69 tokens do not fit three pages
+    assert "error" in json.loads(capsys.readouterr().err.strip().splitlines()[-1])
+    assert main(["generate", str(model_folders["a"]), text, "2", "--device", "cpu"]) == 1                                       # no CPU path, said loudly
+    assert json.loads(capsys.readouterr().err.strip().splitlines()[-1])["error"]["code"] == "cuda"
     assert main(["kernel-bench", str(model_folders["b"]), "4", "100", "3"]) == 0
     kernels = json.loads(capsys.readouterr().out)["kernels"]
     assert {"add_rmsnorm", "rope_store", "linear_qkv", "attention_decode_split_kv", "argmax"} <= set(kernels)
@@ -205,3 +218,29 @@ def test_a_fault_recorded_on_the_device_fails_the_step(model_folders):
     with pytest.raises(KernelError, match="outside the vocabulary"):
         replay_step(runner, {"step": 0, "entries": [{"id": "x", "tokens": [1, 2], "want": [1]}], "end": ["x"]})
     assert replay_step(runner, {"step": 1, "entries": [{"id": "y", "tokens": [1, 2], "want": [1]}], "end": ["y"]}) is not None
+
+
+def test_step_timings_and_layer_trace(model_folders):
+    """A step that is asked says what it cost (device time of the forward pass and of the copies, host wall time), and can hand
+    out the hidden state after every layer, which the plain implementation's trace locates a wrong layer with."""
+    from tinyllama_inference_engine_b200.engine.batch import StepEntry
+    from tinyllama_inference_engine_b200.engine.timing import StepTimings
+
+    folder = model_folders["b"]
+    config, weights = plain_llama.load_model(folder)
+    tokens = _prompts(config["vocab_size"], [41], seed=4)[0]
+    plain_trace: dict = {}
+    plain = plain_llama.forward(config, weights, tokens, trace=plain_trace)
+    for dtype, fraction in (("float32", 2e-5), ("bfloat16", 2.5e-2)):
+        runner = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=64, max_requests=2, max_batch_tokens=64))
+        timings, trace = StepTimings(), {}
+        first = runner.step([StepEntry("r", tokens[:30], [29])], timings, trace)
+        second_trace: dict = {}
+        second = runner.step([StepEntry("r", tokens[30:], [10])], timings, second_trace)
+        assert timings.steps == 2 and timings.compute_ms > 0 and timings.wall_ms >= timings.compute_ms * 0.5 and timings.transfer_ms >= 0
+        assert float((first[0].cpu() - plain[29]).abs().max()) <= fraction * float(plain.abs().max())
+        assert float((second[0].cpu() - plain[40]).abs().max()) <= fraction * float(plain.abs().max())
+        assert set(trace) == {f"layer{i}.output" for i in range(config["num_hidden_layers"])}
+        for name, want in plain_trace.items():
+            got = torch.cat([trace[name], second_trace[name]]).cpu()
+            assert got.shape == want.shape and float((got - want).abs().max()) <= fraction * float(want.abs().max()), name

@@ -309,7 +309,7 @@ def test_prefill_attention_flash(ops, q_heads, kv_heads, head_dim, page_size, wi
     plain_ops.paged_attention(qkv, pages, positions, token_seq, table, want, q_heads, kv_heads, head_dim, page_size, window)
     starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     firsts = np.array([s - q for s, q in zip(seq_lens, q_lens)], dtype=np.int32)
-    from tinyllama_inference_engine_b200.engine.batch import ATTENTION_TILE_ROWS
+    from tinyllama_inference_engine_b200.ops.fast import ATTENTION_TILE_ROWS
     tiles = [[i, int(starts[i]) + off] for i, q in enumerate(q_lens) for off in range(0, q, ATTENTION_TILE_ROWS)]
     pages_gpu = pages.cuda()
     held = set(int(p) for p in table.flatten() if p >= 0)
@@ -547,7 +547,7 @@ def test_gemm_tcgen05_gated(ops, M, inter, K, pair):
 @pytest.mark.parametrize("q_heads,kv_heads,page_size,window", [(32, 4, 64, 0), (8, 2, 64, 100), (4, 4, 128, 0), (16, 1, 64, 37), (3, 3, 64, 0)])
 def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, window):
     """The tcgen05 prompt kernel (head size 64) against the plain function: portions that start anywhere, page edges, single rows."""
-    from tinyllama_inference_engine_b200.engine.batch import paired_attention_tiles
+    from tinyllama_inference_engine_b200.ops.fast import paired_attention_tiles
     from tinyllama_inference_engine_b200.ops import fast
 
     head_dim = 64

@@ -4,6 +4,7 @@ from __future__ import annotations
 import random
 
 import pytest
+import torch
 
 from tinyllama_inference_engine_b200.cache import CacheManager, PagePool
 from tinyllama_inference_engine_b200.engine.request import FINISHED, Request, SamplingParams
@@ -54,6 +55,30 @@ def test_groups_have_pools_of_their_own_and_windows_give_pages_back():
     cache.release("a")
     assert cache.free_pages() == [12, 12]
     cache.check()
+
+
+def test_a_page_may_hold_other_planes_than_keys_and_values():
+    """What a page holds is the mixer's to say: one latent vector per token, or keys and values of different widths, are cache
+    needs like any other; the manager gives them pools, tables and device memory without knowing what they mean."""
+    latent = CacheNeed("pages", planes=((1, 24),))
+    uneven = CacheNeed("pages", planes=((2, 16), (2, 48)), window=32)
+    assert FULL.page_planes() == ((FULL.kv_heads, FULL.head_dim),) * 2 and FULL.uniform_planes()
+    assert latent.uniform_planes() and not uneven.uniform_planes()
+    cache = CacheManager({0: FULL, 1: latent, 2: uneven, 3: latent}, page_size=16, num_pages=6, max_requests=2, max_positions=96, device="cpu", poison_freed_pages=True)
+    assert [g.streams for g in cache.page_groups] == [[0], [1, 3], [2]]
+    assert tuple(cache.page_groups[1].tensor.shape) == (2, 6, 1, 1, 16, 24)
+    assert [tuple(t.shape) for t in cache.page_groups[2].plane_tensors] == [(1, 6, 2, 16, 16), (1, 6, 2, 16, 48)]
+    cache.admit("a")
+    cache.reserve("a", 40)
+    tables = torch.tensor(cache.block_table_rows(cache.page_groups[0], ["a"]), dtype=torch.int32)
+    caches = cache.layer_caches([tables] * 3)
+    assert tuple(caches[1].pages.shape) == (6, 1, 1, 16, 24) and caches[1].plane_pages == ()
+    assert caches[2].pages is None and [tuple(t.shape) for t in caches[2].plane_pages] == [(6, 2, 16, 16), (6, 2, 16, 48)]
+    expected = sum(t.numel() * 4 for g in cache.page_groups for t in g.tensors())
+    assert cache.cache_bytes() == expected
+    cache.release("a")
+    cache.check()
+    assert all(bool(torch.isnan(t).all()) for g in cache.page_groups for t in g.tensors())   # poisoned when given back
 
 
 def test_reserve_is_all_or_nothing_across_groups():

@@ -63,3 +63,21 @@ def test_trace_run_reports_errors_as_json_and_fails(model_folders, tmp_path):
                            capture_output=True, text=True, timeout=300)
     assert child.returncode != 0
     assert "error" in (child.stdout + child.stderr).lower()
+
+
+def test_trace_run_dumps_layers(model_folders, tmp_path):
+    """--dump-layers: the hidden state after every layer, for every row of the step, beside the logits."""
+    folder = model_folders["a"]
+    config, weights = plain_llama.load_model(folder)
+    tokens = trace_tools.make_requests(config["vocab_size"], [13], seed=2)["r0"]
+    plain_trace: dict = {}
+    plain_llama.forward(config, weights, tokens, trace=plain_trace)
+    out = tmp_path / "o"
+    step = {"step": 0, "entries": [{"id": "x", "tokens": tokens, "want": [12]}], "end": ["x"]}
+    child = subprocess.run([sys.executable, str(PROGRAM), "--model", str(folder), "--dtype", "float32", "--out", str(out), "--max-tokens", "64", "--dump-layers"],
+                           input=json.dumps(step) + "\n", capture_output=True, text=True, timeout=300)
+    assert child.returncode == 0 and "done 0" in child.stdout
+    layers = np.fromfile(out / "0.layers.f32", dtype="<f4").reshape(config["num_hidden_layers"], 13, config["hidden_size"])
+    for index in range(config["num_hidden_layers"]):
+        want = plain_trace[f"layer{index}.output"].numpy()
+        assert float(np.abs(layers[index] - want).max()) <= 2e-5 * float(np.abs(want).max())

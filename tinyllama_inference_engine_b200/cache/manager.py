@@ -5,9 +5,10 @@ cache stream of the model's order list.  Streams with the same need form a *grou
 
 * a **page group** (all keys, or a window of them) owns a page pool and, per request,
   a block table from logical page (position // page_size) to physical page.  One page
-  id covers every stream of the group: the device tensor is
-  ``[stream, page, 2 (k, v), kv_head, slot, head_dim]``.  Groups with different needs
-  have pools of their own.  Pages go back to the pool when the request ends, and, in a
+  id covers every stream of the group and every *plane* of a page (``CacheNeed.page_planes``:
+  keys and values are two equal planes).  Equal planes share one device tensor
+  ``[stream, page, plane, head, slot, width]``; unequal ones get a tensor each,
+  ``[stream, page, head, slot, width]``.  Groups with different needs have pools of their own.  Pages go back to the pool when the request ends, and, in a
   window group, as soon as every later query is past them; they are handed out again
   without being cleared (positions beyond a request's length are never read).
 * a **state group** holds one tensor of fixed size per request *slot* and stream,
@@ -45,7 +46,11 @@ class PageGroup:
         self.streams = streams
         self.page_size = page_size
         self.pool = PagePool(num_pages)
-        self.tensor: torch.Tensor | None = None
+        self.tensor: torch.Tensor | None = None          # equal planes
+        self.plane_tensors: list[torch.Tensor] = []       # unequal planes
+
+    def tensors(self) -> list:
+        return [self.tensor] if self.tensor is not None else list(self.plane_tensors)
 
     def pages_for(self, record: RequestRecord, new_total: int) -> int:
         """How many new pages positions < new_total need beyond the request's table."""
@@ -109,17 +114,25 @@ class CacheManager:
     # --- device memory ------------------------------------------------------------------
     def _allocate_tensors(self) -> None:
         for group in self.page_groups:
-            shape = (len(group.streams), group.pool.num_pages, 2, group.need.kv_heads, self.page_size, group.need.head_dim)
-            group.tensor = torch.zeros(shape, dtype=self.dtype, device=self.device)
+            planes = group.need.page_planes()
+            streams, pages = len(group.streams), group.pool.num_pages
+            if group.need.uniform_planes():
+                heads, width = planes[0]
+                group.tensor = torch.zeros((streams, pages, len(planes), heads, self.page_size, width), dtype=self.dtype, device=self.device)
+            else:
+                group.plane_tensors = [torch.zeros((streams, pages, heads, self.page_size, width), dtype=self.dtype, device=self.device) for heads, width in planes]
             if self.poison:
-                group.tensor.fill_(float("nan"))
+                for tensor in group.tensors():
+                    tensor.fill_(float("nan"))
         for group in self.state_groups:
             shape = (len(group.streams), self.max_requests, *group.need.state_shape)
             group.tensor = torch.zeros(shape, dtype=torch.float32, device=self.device)
 
     def cache_bytes(self) -> int:
         total = 0
-        for group in self.page_groups + self.state_groups:
+        for group in self.page_groups:
+            total += sum(tensor.numel() * tensor.element_size() for tensor in group.tensors())
+        for group in self.state_groups:
             if group.tensor is not None:
                 total += group.tensor.numel() * group.tensor.element_size()
         return total
@@ -205,8 +218,9 @@ class CacheManager:
         if not pages:
             return
         group.pool.free(pages, owner)
-        if self.poison and group.tensor is not None:
-            group.tensor[:, torch.tensor(pages, device=group.tensor.device)] = float("nan")
+        if self.poison:
+            for tensor in group.tensors():
+                tensor[:, torch.tensor(pages, device=tensor.device)] = float("nan")
 
     # --- what a step needs ----------------------------------------------------------------
     def block_table_rows(self, group: PageGroup, request_ids: list[object]) -> list[list[int]]:
@@ -225,7 +239,8 @@ class CacheManager:
             need = self.needs[stream]
             if kind == "pages":
                 group = self.page_groups[group_index]
-                caches[stream] = LayerCache(need, True, group.tensor[position], block_tables[group_index], self.page_size, None)
+                caches[stream] = LayerCache(need, True, None if group.tensor is None else group.tensor[position], block_tables[group_index], self.page_size, None,
+                                            tuple(tensor[position] for tensor in group.plane_tensors))
             elif kind == "state":
                 group = self.state_groups[group_index]
                 caches[stream] = LayerCache(need, True, None, None, 0, group.tensor[position])

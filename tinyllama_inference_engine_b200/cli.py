@@ -13,9 +13,12 @@ with the same positional arguments and JSON on standard output; ``reference`` pr
 Errors are one JSON object ``{"error": {"code", "message"}}`` on standard error and
 exit status 1 (app/reference_cli.cpp:20-25).  PROMPT is text when MODEL_DIR holds a
 ``tokenizer.model`` (SentencePiece, BOS prepended as src/tokenizer.cpp:103-105 does),
-otherwise a list of token ids separated by commas or spaces.  Options, before or
-after the positionals: ``--dtype bfloat16|float32``, ``--temperature``, ``--top-p``,
-``--seed``, ``--batch``.  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
+otherwise a list of token ids separated by commas or spaces; with ``--prompt-len N``
+(and ``--prompt-seed S``) the PROMPT argument is left out and N seeded random token ids
+stand in for it.  Options, before or after the positionals: ``--dtype bfloat16|float32``,
+``--temperature``, ``--top-p``, ``--seed``, ``--batch``, ``--max-batch-tokens``,
+``--page-size``, ``--num-pages`` (cache pages; by default what the request needs),
+``--device`` (a CUDA device; there is no CPU path and ``cpu`` is refused with an error).  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
 (median and 95th percentile), like the reference's benchmarks/kernel_benchmarks.cu:127-325.
 """
 from __future__ import annotations
@@ -78,9 +81,20 @@ def _engine(args, max_cache_tokens: int, max_requests: int = 1):
     from . import EngineConfig
     from .engine.api import Engine
 
-    config = EngineConfig(dtype=args.dtype, max_cache_tokens=max(64, -(-max_cache_tokens // 64) * 64), max_requests=max(1, max_requests),
-                          max_batch_tokens=args.max_batch_tokens)
+    page = args.page_size
+    cache_tokens = args.num_pages * page if args.num_pages else max(page, -(-max_cache_tokens // page) * page)
+    config = EngineConfig(dtype=args.dtype, page_size=page, max_cache_tokens=cache_tokens, max_requests=max(1, max_requests),
+                          max_batch_tokens=args.max_batch_tokens, device=args.device)
     return Engine(args.model_dir, config)
+
+
+def _prompt(args, tokens: "_Tokens", vocab: int) -> list[int]:
+    """The PROMPT argument, or --prompt-len seeded random token ids."""
+    if args.prompt_len:
+        import numpy as np
+
+        return [int(t) for t in np.random.default_rng(args.prompt_seed).integers(0, vocab, size=args.prompt_len)]
+    return tokens.encode(args.rest[0])
 
 
 def _generate(args) -> int:
@@ -90,14 +104,18 @@ def _generate(args) -> int:
     max_tokens = _positive(args.rest[1], "MAX_TOKENS")
     _, model_config = load_model_config(args.model_dir)
     tokens = _Tokens(Path(args.model_dir), getattr(model_config, "bos_token_id", None))
-    prompt = tokens.encode(args.rest[0])
+    prompt = _prompt(args, tokens, model_config.vocab_size)
     engine = _engine(args, len(prompt) + max_tokens)
+    from .engine.timing import StepTimings
+
+    prefill, decode = StepTimings(), StepTimings()   # device time of compute and of copies, as the reference reports them (app/cuda_reference.cu:149-226)
     started = time.perf_counter()
     request_id = engine.add_request(prompt, SamplingParams(max_tokens=max_tokens, temperature=args.temperature, top_p=args.top_p, seed=args.seed))
-    engine.step()
+    while not engine.requests[request_id].generated and engine.has_unfinished():
+        engine.step(prefill)
     prefill_ms = (time.perf_counter() - started) * 1e3
     while engine.has_unfinished():
-        engine.step()
+        engine.step(decode)
     total_ms = (time.perf_counter() - started) * 1e3
     generated = engine.requests[request_id].generated
     if args.command == "reference":
@@ -108,7 +126,9 @@ def _generate(args) -> int:
         print("text: " + tokens.decode(generated))
         return 0
     result = {"prompt_tokens": len(prompt), "generated_tokens": generated, "text": tokens.decode(generated),
-              "prefill_ms": prefill_ms, "decode_ms": total_ms - prefill_ms, "dtype": args.dtype}
+              "prefill_ms": prefill_ms, "decode_ms": total_ms - prefill_ms, "dtype": args.dtype,
+              "prefill_compute_ms": prefill.compute_ms, "prefill_transfer_ms": prefill.transfer_ms,
+              "decode_compute_ms": decode.compute_ms, "decode_transfer_ms": decode.transfer_ms, "decode_steps": decode.steps}
     if len(args.rest) > 2:
         golden = json.loads(Path(args.rest[2]).read_text())
         expected = golden.get("generated_tokens", golden.get("greedy_token_ids"))
@@ -125,7 +145,7 @@ def _logits(args) -> int:
     from .engine.batch import StepEntry
 
     _, model_config = load_model_config(args.model_dir)
-    prompt = _Tokens(Path(args.model_dir), getattr(model_config, "bos_token_id", None)).encode(args.rest[0])
+    prompt = _prompt(args, _Tokens(Path(args.model_dir), getattr(model_config, "bos_token_id", None)), model_config.vocab_size)
     engine = _engine(args, len(prompt))
     logits = engine.runner.step([StepEntry("logits", prompt, [len(prompt) - 1])])
     print(json.dumps({"prompt_tokens": len(prompt), "logits": logits[0].cpu().tolist()}))
@@ -270,11 +290,18 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--max-batch-tokens", type=int, default=2048)
+    parser.add_argument("--page-size", type=int, default=64, help="tokens per cache page (a multiple of 16)")
+    parser.add_argument("--num-pages", type=int, default=0, help="cache pages (default: what the request needs)")
+    parser.add_argument("--prompt-len", type=int, default=0, help="use this many seeded random token ids as the prompt; the PROMPT argument is then left out")
+    parser.add_argument("--prompt-seed", type=int, default=0)
+    parser.add_argument("--device", default="cuda:0", help="the CUDA device to run on (there is no CPU path)")
     try:
         args = parser.parse_intermixed_args(argv)
     except SystemExit as exc:
         return int(exc.code or 0) and 1
     handler, (low, high) = _COMMANDS[args.command]
+    if args.prompt_len and args.command in ("generate", "reference", "logits"):
+        args.rest.insert(0, "")   # the place of the PROMPT that --prompt-len stands in for
     try:
         if not low <= len(args.rest) <= high:
             raise EngineError("invalid tinyllama_b200 command or arguments\n" + USAGE, code="invalid_argument")

@@ -6,36 +6,30 @@ from dataclasses import dataclass, field
 import torch
 
 
-ATTENTION_TILE_ROWS = 64   # rows of one work item of the prompt-attention kernel (csrc/attention_prefill.cu: PREFILL_ROWS)
-ATTENTION_TC_TILE_ROWS = 128   # rows of one work item of the tensor-memory kernel (csrc/attention_prefill_tc.cu)
+# --- per-step work lists -----------------------------------------------------------------------
+# A kernel may want, beside the step's description, a list of work items that depends on how the step is cut (which runs of
+# rows form a tile, in which order they are best run).  Whoever owns the kernel registers a function for it here; the packer
+# calls every registered function once per step and ships the lists in the same buffer and the same copy as everything
+# else.  The packer itself knows no kernel and no tile size.
+@dataclass(frozen=True)
+class StepPlan:
+    name: str
+    columns: int                                   # the list is int32 [n, columns]
+    build: "callable"                              # (q_lens, first_positions, seq_starts) -> flat list of ints
+    wanted: "callable" = lambda q_lens: True       # (q_lens) -> whether this step needs the list at all
 
 
-def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int]) -> list[int]:
-    """Work items of the tensor-memory attention kernel: (entry, first row, entry or -1, first row) per item.
+_STEP_PLANS: dict[str, StepPlan] = {}
 
-    A run of ATTENTION_TC_TILE_ROWS rows late in a long request sees many keys, an early one few.  Pairing the heaviest
-    tile with the lightest, the second heaviest with the second lightest, and so on, gives every CTA about the same
-    number of key tiles, so the grid finishes together instead of waiting for the last heavy tiles.
-    """
-    singles = []
-    for index, count in enumerate(q_lens):
-        for offset in range(0, count, ATTENTION_TC_TILE_ROWS):
-            rows = min(ATTENTION_TC_TILE_ROWS, count - offset)
-            work = -(-(first_positions[index] + offset + rows) // 64)
-            singles.append((work, index, seq_starts[index] + offset))
-    singles.sort(key=lambda item: -item[0])
-    flat: list[int] = []
-    low, high = 0, len(singles) - 1
-    while low <= high:
-        _, index, row = singles[low]
-        if low < high:
-            _, index2, row2 = singles[high]
-            flat += [index, row, index2, row2]
-        else:
-            flat += [index, row, -1, 0]
-        low += 1
-        high -= 1
-    return flat
+
+def register_step_plan(plan: StepPlan, *, replace: bool = False) -> None:
+    if plan.name in _STEP_PLANS and not replace:
+        raise ValueError(f"step plan {plan.name!r} is already registered")
+    _STEP_PLANS[plan.name] = plan
+
+
+def unregister_step_plan(name: str) -> None:
+    _STEP_PLANS.pop(name, None)
 
 
 @dataclass
@@ -60,8 +54,7 @@ class StepContext:
       state_slots[B]              the request's slot in per-request state tensors
       want_rows[W]                rows whose logits are returned, in entry and want order
       block_tables[g][B, width]   page ids of every entry in page group g (-1: none)
-      attn_tiles[N, 2]            (entry, first row) of every run of up to ATTENTION_TILE_ROWS consecutive rows of one entry:
-                                  the work list of the prompt-attention kernel
+      plans[name][N, columns]     work lists registered with ``register_step_plan`` (see ``plan``)
     """
 
     num_tokens: int
@@ -82,13 +75,16 @@ class StepContext:
     host_state_slots: list[int]
     max_q_len: int
     max_seq_len: int
-    attn_tiles: torch.Tensor | None = None
     wants_every_row_in_order: bool = False      # want_rows is 0, 1, ..., num_tokens - 1
-    attn_tiles_tc: torch.Tensor | None = None   # work items of the tensor-memory kernel: pairs of 128-row runs (int32 [n, 4])
+    plans: dict = field(default_factory=dict)   # name -> int32 [n, columns] work list of a registered step plan
 
     @property
     def decode_only(self) -> bool:
         return self.max_q_len == 1
+
+    def plan(self, name: str):
+        """The work list ``name`` of this step, or None if nobody registered it or this step has no use for it."""
+        return self.plans.get(name)
 
 
 def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[int], table_rows: list[list[list[int]]],
@@ -109,12 +105,9 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         want_rows += [start + w for w in entry.want]
         seq_starts.append(start + len(entry.tokens))
     seq_lens = [f + n for f, n in zip(first_positions, q_lens)]
-    tiles: list[int] = []
-    for index, count in enumerate(q_lens):
-        for offset in range(0, count, ATTENTION_TILE_ROWS):
-            tiles += [index, seq_starts[index] + offset]
-    tiles_tc = paired_attention_tiles(q_lens, first_positions, seq_starts)
-    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows, tiles, tiles_tc]
+    plans = [plan for plan in _STEP_PLANS.values() if plan.wanted(q_lens)]
+    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows]
+    sections += [plan.build(q_lens, first_positions, seq_starts) for plan in plans]
     flat: list[int] = []
     offsets = []
     for section in sections:
@@ -138,6 +131,31 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         first_positions=views[5], state_slots=views[6], want_rows=views[7] if want_rows else None,
         block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=q_lens,
         host_first_positions=list(first_positions), host_state_slots=list(slots),
-        max_q_len=max(q_lens), max_seq_len=max(seq_lens), attn_tiles=views[8].view(-1, 2),
-        attn_tiles_tc=views[9].view(-1, 4), wants_every_row_in_order=want_rows == list(range(num_tokens)),
+        max_q_len=max(q_lens), max_seq_len=max(seq_lens), wants_every_row_in_order=want_rows == list(range(num_tokens)),
+        plans={plan.name: views[8 + i].view(-1, plan.columns) for i, plan in enumerate(plans)},
     )
+
+
+def decode_context(buffer: torch.Tensor, count: int, table_width: int, groups: int, max_positions: int, request_ids: list) -> tuple["StepContext", list]:
+    """The context of a step of ``count`` single decoded tokens over a device buffer of fixed address (a decode session's), laid
+    out as ``pack_step`` lays a step out: [tokens | positions | token_seq | seq_starts | seq_lens | first_positions | slots | want |
+    tables...].  Returns the context and the section offsets.  ``max_seq_len`` is the longest context a request can reach, so
+    that launch shapes chosen from it hold for every later step of the session."""
+    sizes = decode_layout(count, table_width, groups)
+    offsets = [0]
+    for size in sizes:
+        offsets.append(offsets[-1] + size)
+    view = [buffer[offsets[i] : offsets[i + 1]] for i in range(len(sizes))]
+    tables = [view[8 + g].view(count, table_width) for g in range(groups)]
+    ctx = StepContext(
+        num_tokens=count, num_seqs=count, token_ids=view[0], positions=view[1], token_seq=view[2], seq_starts=view[3], seq_lens=view[4],
+        first_positions=view[5], state_slots=view[6], want_rows=view[7], block_tables=tables, request_ids=request_ids,
+        host_q_lens=[1] * count, host_first_positions=[0] * count, host_state_slots=[0] * count, max_q_len=1,
+        max_seq_len=max_positions, wants_every_row_in_order=True,
+    )
+    return ctx, offsets
+
+
+def decode_layout(count: int, table_width: int, groups: int) -> list[int]:
+    """Section sizes (int32 words) of a decode step's buffer."""
+    return [count, count, count, count + 1, count, count, count, count] + [count * table_width] * groups

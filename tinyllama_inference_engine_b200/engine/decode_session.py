@@ -15,7 +15,7 @@ import torch
 
 from .. import ops
 from ..errors import BatchError
-from .batch import StepContext
+from .batch import decode_context, decode_layout
 
 # A session runs its first steps kernel by kernel and is captured as a graph only when it is still in use after them:
 # a batch that changes with every step (requests finishing one after another) would otherwise pay a capture, which costs
@@ -32,13 +32,11 @@ class DecodeSession:
         device = runner.device
         width = self.cache.table_width
         groups = len(self.cache.page_groups)
-        # one int32 buffer: [tokens | positions | token_seq | seq_starts | seq_lens | first_positions | slots | want | tables...]
-        sizes = [count, count, count, count + 1, count, count, count, count] + [count * width] * groups
+        # one int32 buffer laid out as the packer lays a step out (engine.batch.decode_layout): host copy and device copy
+        sizes = decode_layout(count, width, groups)
         self._host = torch.zeros(sum(sizes), dtype=torch.int32).pin_memory()
         self._device = torch.zeros(sum(sizes), dtype=torch.int32, device=device)
-        offsets = [0]
-        for size in sizes:
-            offsets.append(offsets[-1] + size)
+        self.ctx, offsets = decode_context(self._device, count, width, groups, runner.spec.max_positions, self.request_ids)
         self._offsets = offsets
         view = lambda buffer, i: buffer[offsets[i] : offsets[i + 1]]  # noqa: E731
         self.h_tokens, self.h_positions = view(self._host, 0), view(self._host, 1)
@@ -51,19 +49,12 @@ class DecodeSession:
         view(self._host, 2).copy_(torch.arange(count))
         view(self._host, 3).copy_(torch.arange(count + 1))
         view(self._host, 7).copy_(torch.arange(count))
-        d = [view(self._device, i) for i in range(8)]
-        self.d_tables = [view(self._device, 8 + g).view(count, width) for g in range(groups)]
+        self.d_tables = self.ctx.block_tables
         self.sampled = torch.zeros(count, dtype=torch.int32, device=device)
         self.temperature = torch.zeros(count, dtype=torch.float32, device=device)
         self.top_p = torch.ones(count, dtype=torch.float32, device=device)
         self.seeds = torch.zeros(count, dtype=torch.int64, device=device)
         self.counters = torch.zeros(count, dtype=torch.int64, device=device)
-        self.ctx = StepContext(
-            num_tokens=count, num_seqs=count, token_ids=d[0], positions=d[1], token_seq=d[2], seq_starts=d[3], seq_lens=d[4],
-            first_positions=d[5], state_slots=d[6], want_rows=d[7], block_tables=self.d_tables, request_ids=self.request_ids,
-            host_q_lens=[1] * count, host_first_positions=[0] * count, host_state_slots=[0] * count, max_q_len=1,
-            max_seq_len=runner.spec.max_positions, wants_every_row_in_order=True,
-        )
         self.positions = [0] * count      # host mirror: position of the token each request runs next
         self.use_graph = use_graph
         self._fresh = True

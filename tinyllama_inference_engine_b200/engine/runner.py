@@ -19,6 +19,7 @@ from ..models import DecoderModel, expected_tensors
 from ..parts.base import Runtime, Workspace
 from ..weights import WeightStore
 from .batch import StepContext, StepEntry, pack_step
+from .timing import StepClock, StepTimings
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -80,8 +81,13 @@ class ModelRunner:
             raise BatchError(f"more than {self.cache.max_requests} live requests")
         return firsts
 
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
-        """Run the entries as one batch; returns 32-bit logits [wanted, vocab] (None if nothing is wanted)."""
+    def step(self, entries: list[StepEntry], timings: StepTimings | None = None, trace: dict | None = None) -> torch.Tensor | None:
+        """Run the entries as one batch; returns 32-bit logits [wanted, vocab] (None if nothing is wanted).
+
+        ``timings``: filled with what the step cost (the call then waits for the device).  ``trace``: filled with the hidden
+        state after every run of a layer, ``trace["layer<i>.output"]`` [rows, hidden] in 32-bit, as the reference's traced
+        forward keeps them (src/model.cpp:98-100, 200-206), so that a wrong logit can be followed back to its layer."""
+        clock = StepClock(self.device, timings is not None)
         firsts = self.validate(entries)
         wanted = [(e.request_id if self.cache.has(e.request_id) else None, f + len(e.tokens)) for e, f in zip(entries, firsts)]
         if not self.cache.can_reserve(wanted):
@@ -97,16 +103,19 @@ class ModelRunner:
         ids = [e.request_id for e in entries]
         table_rows = [self.cache.block_table_rows(group, ids) for group in self.cache.page_groups]
         ctx = pack_step(entries, firsts, slots, table_rows, self.device)
-        logits = self.run(ctx)
+        clock.mark()
+        logits = self.run(ctx, trace)
+        clock.mark()
         for entry, first in zip(entries, firsts):
             self.cache.advance(entry.request_id, first + len(entry.tokens))
         self.steps += 1
         self.tokens_run += ctx.num_tokens
+        clock.finish(timings, ("transfer", "compute"))
         return logits
 
-    def run(self, ctx: StepContext) -> torch.Tensor | None:
+    def run(self, ctx: StepContext, trace: dict | None = None) -> torch.Tensor | None:
         caches = self.cache.layer_caches(ctx.block_tables)
-        return self.model.forward(ctx, caches)
+        return self.model.forward(ctx, caches, trace)
 
     def finish(self, request_id: object) -> None:
         """The request has ended; what it holds is given back."""

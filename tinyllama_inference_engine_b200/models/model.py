@@ -38,15 +38,17 @@ class DecoderModel:
         self.head = build_part("head", spec.head, "", weights, runtime)
         self.cache_needs = cache_needs(spec)
 
-    def forward(self, ctx, caches: dict[int, LayerCache]):
-        """Logits (32-bit, [len(want_rows), vocab]) of the rows ``ctx.want_rows``."""
-        hidden, pending = self._run_blocks(ctx, caches)
+    def forward(self, ctx, caches: dict[int, LayerCache], trace: dict | None = None):
+        """Logits (32-bit, [len(want_rows), vocab]) of the rows ``ctx.want_rows``.
+
+        ``trace``: a dictionary that receives the hidden state of all rows after every run of a layer (32-bit copies)."""
+        hidden, pending = self._run_blocks(ctx, caches, trace)
         return self.logits(hidden, ctx.want_rows, pending if ctx.wants_every_row_in_order else None)
 
     def forward_hidden(self, ctx, caches: dict[int, LayerCache]):
         return self._run_blocks(ctx, caches)[0]
 
-    def _run_blocks(self, ctx, caches: dict[int, LayerCache]):
+    def _run_blocks(self, ctx, caches: dict[int, LayerCache], trace: dict | None = None):
         """The complete residual stream of the step's rows, and a lazy final norm of it if the last block left one prepared."""
         from .. import ops
 
@@ -56,7 +58,7 @@ class DecoderModel:
         for index, entry in enumerate(order):
             cache = caches[entry.cache]
             if cache.writes != entry.writes_cache:
-                cache = LayerCache(cache.need, entry.writes_cache, cache.pages, cache.block_table, cache.page_size, cache.state)
+                cache = LayerCache(cache.need, entry.writes_cache, cache.pages, cache.block_table, cache.page_size, cache.state, cache.plane_pages)
             block = self.blocks[entry.layer]
             if block.accepts_next_norm:
                 # the norm that reads this block's result: the next block's first one (if it names one), or the final norm
@@ -66,6 +68,10 @@ class DecoderModel:
                 if isinstance(pending, ops.LazyNorm):
                     pending = None   # the residual is complete; this block does not know prepared norms
                 residual, pending = block.forward(residual, pending, ctx, cache)
+            if trace is not None:
+                # the layer's output is the residual with what is still pending on it (a prepared norm means nothing is)
+                complete = residual if pending is None or isinstance(pending, ops.LazyNorm) else residual + pending.float()
+                trace[f"layer{index}.output"] = complete.float().clone()
         if isinstance(pending, ops.LazyNorm):
             return residual, pending
         if pending is not None:

@@ -436,6 +436,59 @@ def can_fuse_rope_into_decode(batch, qkv, head_dim: int, q_heads: int, kv_heads:
 
 
 # --- prompt (and mixed) attention -----------------------------------------------------------------
+ATTENTION_TILE_ROWS = 64       # rows of one work item of the mma.sync prompt kernel (csrc/attention_prefill.cu: PREFILL_ROWS)
+ATTENTION_TC_TILE_ROWS = 128   # rows of one work item of the tensor-memory kernel (csrc/attention_prefill_tc.cu)
+
+
+def attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int]) -> list[int]:
+    """Work items of the mma.sync prompt kernel: (entry, first row) of every run of up to ATTENTION_TILE_ROWS rows of one entry."""
+    tiles: list[int] = []
+    for index, count in enumerate(q_lens):
+        for offset in range(0, count, ATTENTION_TILE_ROWS):
+            tiles += [index, seq_starts[index] + offset]
+    return tiles
+
+
+def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int]) -> list[int]:
+    """Work items of the tensor-memory attention kernel: (entry, first row, entry or -1, first row) per item.
+
+    A run of ATTENTION_TC_TILE_ROWS rows late in a long request sees many keys, an early one few.  Pairing the heaviest
+    tile with the lightest, the second heaviest with the second lightest, and so on, gives every CTA about the same
+    number of key tiles, so the grid finishes together instead of waiting for the last heavy tiles.
+    """
+    singles = []
+    for index, count in enumerate(q_lens):
+        for offset in range(0, count, ATTENTION_TC_TILE_ROWS):
+            rows = min(ATTENTION_TC_TILE_ROWS, count - offset)
+            work = -(-(first_positions[index] + offset + rows) // 64)
+            singles.append((work, index, seq_starts[index] + offset))
+    singles.sort(key=lambda item: -item[0])
+    flat: list[int] = []
+    low, high = 0, len(singles) - 1
+    while low <= high:
+        _, index, row = singles[low]
+        if low < high:
+            _, index2, row2 = singles[high]
+            flat += [index, row, index2, row2]
+        else:
+            flat += [index, row, -1, 0]
+        low += 1
+        high -= 1
+    return flat
+
+
+def _register_step_plans() -> None:
+    """The prompt-attention kernels' work lists travel with every step that is not pure decoding (engine.batch.register_step_plan)."""
+    from ..engine.batch import StepPlan, register_step_plan
+
+    not_decode = lambda q_lens: max(q_lens) > 1  # noqa: E731
+    register_step_plan(StepPlan("attention_tiles", 2, attention_tiles, not_decode), replace=True)
+    register_step_plan(StepPlan("attention_tiles_tc", 4, paired_attention_tiles, not_decode), replace=True)
+
+
+_register_step_plans()
+
+
 def prefill_attention(qkv, pages, tiles, seq_starts, first_positions, block_table, out, q_heads: int, kv_heads: int, head_dim: int,
                       page_size: int, window: int, scale: float) -> None:
     """Flash attention of every tile in ``tiles`` (int32 [n, 2]: request, first row; up to 128 rows each) over the paged cache; bfloat16."""
@@ -479,13 +532,14 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
         splits = decode_splits(batch.num_seqs, kv_heads, batch.max_seq_len)
         decode_attention(qkv, pages, positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, splits)
         return True
-    tc_tiles = getattr(batch, "attn_tiles_tc", None)
+    tc_tiles = batch.plan("attention_tiles_tc")
     if (use_tc_attention and tc_tiles is not None and head_dim == 64 and page_size % 64 == 0 and pages.is_contiguous()
             and batch.num_tokens >= TC_ATTENTION_MIN_ROWS_PER_TILE * 2 * tc_tiles.shape[0]):
         prefill_attention_tc(qkv, pages, tc_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads, page_size, window, scale)
         return True
-    if batch.attn_tiles is not None and head_dim <= 128:
-        prefill_attention(qkv, pages, batch.attn_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads,
+    tiles = batch.plan("attention_tiles")
+    if tiles is not None and head_dim <= 128:
+        prefill_attention(qkv, pages, tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads,
                           head_dim, page_size, window, scale)
         return True
     return False

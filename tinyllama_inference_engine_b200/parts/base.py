@@ -43,8 +43,10 @@ from .spec import PartSpec, TensorSpec
 class CacheNeed:
     """What a mixer keeps per request between steps.
 
-    kind "pages": keys and values of ``kv_heads`` heads of ``head_dim`` for every
-    cached token, or only the last ``window`` tokens if window > 0.
+    kind "pages": for every cached token (or only the last ``window`` tokens if window > 0) a number of *planes*, each
+    ``heads`` vectors of ``width`` elements: ``planes = ((heads, width), ...)``.  Keys and values of ``kv_heads`` heads of
+    ``head_dim`` are two equal planes, which is what ``kv_heads`` / ``head_dim`` alone mean; one latent vector per token
+    would be a single plane, keys and values of different widths two unequal ones.
     kind "state": one tensor of ``state_shape`` per request (always 32-bit).
     kind "none": nothing.
     """
@@ -54,9 +56,20 @@ class CacheNeed:
     head_dim: int = 0
     window: int = 0
     state_shape: tuple[int, ...] = ()
+    planes: tuple[tuple[int, int], ...] = ()
+
+    def page_planes(self) -> tuple[tuple[int, int], ...]:
+        """The planes of a page: as given, or keys and values of ``kv_heads`` x ``head_dim``."""
+        if self.planes:
+            return tuple((int(h), int(w)) for h, w in self.planes)
+        return ((self.kv_heads, self.head_dim), (self.kv_heads, self.head_dim)) if self.kind == "pages" else ()
+
+    def uniform_planes(self) -> bool:
+        planes = self.page_planes()
+        return all(plane == planes[0] for plane in planes)
 
     def group_key(self) -> tuple:
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape)
+        return (self.kind, self.page_planes(), self.window, self.state_shape)
 
 
 @dataclass
@@ -65,10 +78,11 @@ class LayerCache:
 
     need: CacheNeed
     writes: bool = True
-    pages: torch.Tensor | None = None        # [num_pages, 2, kv_heads, page_size, head_dim]
+    pages: torch.Tensor | None = None        # equal planes: [num_pages, planes, heads, page_size, width] (keys and values: planes = 2)
     block_table: torch.Tensor | None = None  # int32 [requests in step, width], -1 where no page
     page_size: int = 0
     state: torch.Tensor | None = None        # [slots, *state_shape] float32
+    plane_pages: tuple = ()                  # unequal planes: one [num_pages, heads, page_size, width] tensor per plane
 
 
 class Workspace:
