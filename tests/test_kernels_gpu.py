@@ -544,13 +544,13 @@ def test_gemm_tcgen05_gated(ops, M, inter, K, pair):
     assert float((got.cpu().float() - want).abs().max()) <= 1.6e-2 * float(want.abs().max()) + 2e-3 * float(both.abs().max())
 
 
+@pytest.mark.parametrize("head_dim", [64, 128])
 @pytest.mark.parametrize("q_heads,kv_heads,page_size,window", [(32, 4, 64, 0), (8, 2, 64, 100), (4, 4, 128, 0), (16, 1, 64, 37), (3, 3, 64, 0)])
-def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, window):
-    """The tcgen05 prompt kernel (head size 64) against the plain function: portions that start anywhere, page edges, single rows."""
+def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, window, head_dim):
+    """The tcgen05 prompt kernel (head size 64 and 128) against the plain function: portions that start anywhere, page edges, single rows."""
     from tinyllama_inference_engine_b200.ops.fast import paired_attention_tiles
     from tinyllama_inference_engine_b200.ops import fast
 
-    head_dim = 64
     rng = np.random.default_rng(15)
     torch.manual_seed(15)
     seq_lens = [300, 64, 65, 1, 127, 131, 700, 2, 129, 1000]
@@ -585,7 +585,7 @@ def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, wind
             pages_gpu[int(table[i, n // page_size]), :, :, n % page_size :] = float("nan")
     got = torch.full((tokens, q_heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
     fast.prefill_attention_tc(qkv.cuda(), pages_gpu, torch.tensor(tiles, dtype=torch.int32).view(-1, 4).cuda(), torch.from_numpy(starts).cuda(), torch.from_numpy(firsts).cuda(),
-                              table.cuda(), got, q_heads, kv_heads, page_size, window, head_dim ** -0.5)
+                              table.cuda(), got, q_heads, kv_heads, head_dim, page_size, window, head_dim ** -0.5)
     torch.cuda.synchronize()
     assert int(fast.tcgen05_error_flag(got.device)) == 0, "a bounded wait inside the kernel gave up"
     error = (got.cpu().float() - want.float()).abs().max(1).values

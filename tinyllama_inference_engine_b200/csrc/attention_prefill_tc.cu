@@ -1,12 +1,13 @@
-// Paged grouped-query flash attention for prompt portions on the 5th-generation tensor cores (head size 64, bfloat16).
+// Paged grouped-query flash attention for prompt portions on the 5th-generation tensor cores (head size 64 or 128, bfloat16).
 //
 // Same mathematics as attention_prefill.cu (src/operators.cpp:102-146 per row, 32-bit softmax, causal by position,
 // optional window), built the way this GPU wants it:
 //   * a CTA owns 128 consecutive query rows of one request and one query head; thread i of the four softmax warps
 //     owns row i, which is lane i of tensor memory, so row maxima and sums need no shuffles at all;
-//   * Q (from the step's [q | k | v] rows) and each page of K and V (64 keys x 64 dims = one 8 KB box, exactly one
-//     page of the cache) arrive by TMA with the 128-byte swizzle; the block table gives the page of every tile;
-//   * S = Q . K^T is one tcgen05.mma group (128 x 64 x 64) into tensor memory, double-buffered so that the scores of
+//   * Q (from the step's [q | k | v] rows) and each page of K and V (64 keys x 64 dims = one 8 KB box; a head of 128 is two
+//     such boxes side by side, the two halves of a row 128 bytes each) arrive by TMA with the 128-byte swizzle; the block
+//     table gives the page of every tile;
+//   * S = Q . K^T is one tcgen05.mma group (128 x 64 x head size) into tensor memory, double-buffered so that the scores of
 //     the next tile are computed while the softmax of this one runs;
 //   * the softmax warps read S with tcgen05.ld, mask, exponentiate (scale folded into the exponent), write P as
 //     bfloat16 into shared memory in the swizzled K-major layout, and a second tcgen05.mma group computes P . V with
@@ -20,14 +21,18 @@
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and tensor-memory owner, warps 2..5 softmax (128 threads).
 // Every mbarrier wait is bounded; on a timeout the CTA raises `error_flag`, stops, lets copies land, frees its tensor
 // memory and returns.  Needs page_size % 64 == 0; other shapes use the mma.sync kernel.
+// Two CTAs share an SM, so that one's products run under the other's softmax.  Head size 64: three K / V stages, two P buffers,
+// 97 KB of shared memory and 256 columns of tensor memory (two score buffers, one running output per row tile).  Head size 128
+// is made to fit the same way: two stages, ONE P buffer (a tile's softmax writes it when the product of the tile before has
+// read it) and ONE running output of 128 columns that the second row tile takes over when the first has been read out:
+// 112 KB and 256 columns.  (One CTA per SM with everything doubled ran the 8,192-token prefill of the 8B shapes at 1.41 ms a layer.)
 #include "tcgen05_utils.cuh"
 
 namespace tlie {
 
-constexpr int kD = 64;            // head size
 constexpr int kRowsTC = 128;      // query rows per CTA
 constexpr int kKeysTC = 64;       // keys per tile (one box)
-constexpr int kKvStages = 3;
+constexpr int kBoxDims = 64;      // dims of one box: 128 bytes, the swizzle span
 constexpr int kThreadsTC = 192;
 constexpr float kLog2eTC = 1.4426950408889634f;
 // The running output stays in tensor memory and is rescaled only when a row's maximum has grown by more than this many
@@ -70,25 +75,33 @@ __device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[64]) 
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
+// A tile of D dims is D / 64 sub-tiles of 64 dims side by side in memory, each [rows][64] in the 128-byte swizzle.
+template <int D>
 struct SmemTC {
+  static constexpr int kStages = D <= 64 ? 3 : 2;
+  static constexpr int kPBuffers = D <= 64 ? 2 : 1;
   // all tiles are 1024-byte aligned (the struct is placed on a 1024-byte boundary)
-  __nv_bfloat16 q[kRowsTC * kD];                     // 16 KB
-  __nv_bfloat16 k[kKvStages][kKeysTC * kD];          // 8 KB each
-  __nv_bfloat16 v[kKvStages][kKeysTC * kD];          // 8 KB each
-  __nv_bfloat16 p[2][kRowsTC * kKeysTC];             // 16 KB each
-  uint64_t q_full, q_empty, kv_full[kKvStages], kv_empty[kKvStages], s_full[2], s_empty[2], p_full[2], pv_full, o_full[2];
+  __nv_bfloat16 q[kRowsTC * D];                      // 16 KB per 64 dims
+  __nv_bfloat16 k[kStages][kKeysTC * D];             // 8 KB per 64 dims each
+  __nv_bfloat16 v[kStages][kKeysTC * D];
+  __nv_bfloat16 p[kPBuffers][kRowsTC * kKeysTC];     // 16 KB each
+  uint64_t q_full, q_empty, kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_full, o_full[2], o_read;
   uint32_t tmem_base;
   int abort_flag;
 };
 
 // tiles: [n_items][4] = (request, first row, request, first row): one or two 128-row tiles per CTA (second request -1: none)
+template <int kD>
 __global__ void __launch_bounds__(kThreadsTC)
     prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                 const int* __restrict__ tiles, const int* __restrict__ seq_starts, const int* __restrict__ first_positions,
                                 const int* __restrict__ block_table, int table_stride, __nv_bfloat16* __restrict__ out, int q_heads,
                                 int kv_heads, int page_size, int window, float scale, int* __restrict__ error_flag) {
   extern __shared__ uint8_t smem_raw[];
-  SmemTC& sm = *reinterpret_cast<SmemTC*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  using Smem = SmemTC<kD>;
+  constexpr int kKvStages = Smem::kStages;
+  constexpr int kSubTiles = kD / kBoxDims;
+  Smem& sm = *reinterpret_cast<Smem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   volatile int* abort_flag = &sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -97,7 +110,16 @@ __global__ void __launch_bounds__(kThreadsTC)
   const int* item = tiles + (size_t)blockIdx.x * 4;
   const int head = blockIdx.y;
   const int kvh = head / (q_heads / kv_heads);
-  constexpr int kTmemCols = 256;   // S0 [0,64), S1 [64,128), O of the first row tile [128,192), of the second [192,256)
+  // S0 [0,64), S1 [64,128), O of the first row tile [128, 128 + D), of the second [128 + D, 128 + 2 D)
+  // (head size 128: both row tiles use [128, 256), one after the other)
+  constexpr int kTmemCols = 256;
+  constexpr int kOutCol0 = 2 * kKeysTC;
+  constexpr bool kCompact = kD > 64;
+  constexpr int kOutStride = kCompact ? 0 : kD;
+  if (kCompact && (smem_u32(smem_raw) & 1023u) != 0) {   // no room was asked for to align by hand: the tiles must lie on 1 KB boundaries as they are
+    if (threadIdx.x == 0) atomicOr(error_flag, 1);
+    return;
+  }
 
   struct RowTile {
     int row0, rows_here, pos0, n_keys, first_kt, num_kt;
@@ -138,6 +160,7 @@ __global__ void __launch_bounds__(kThreadsTC)
     mbar_init(&sm.pv_full, 1);
     mbar_init(&sm.o_full[0], 1);   // used once each: all products of a row tile are done
     mbar_init(&sm.o_full[1], 1);
+    mbar_init(&sm.o_read, 4);      // the first row tile's output has been read out of tensor memory (one arrival per softmax warp)
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -167,19 +190,23 @@ __global__ void __launch_bounds__(kThreadsTC)
         if (u > 0) ok = mbar_wait(&sm.q_empty, 0, abort_flag);   // the first row tile's score products have read Q
         if (!ok) break;
         mbar_expect_tx(&sm.q_full, kRowsTC * kD * 2);
-        tma_load_2d(sm.q, &map_q, head * kD, t.row0, &sm.q_full);
+#pragma unroll
+        for (int c = 0; c < kSubTiles; ++c) tma_load_2d(sm.q + c * kRowsTC * kBoxDims, &map_q, head * kD + c * kBoxDims, t.row0, &sm.q_full);
         for (int j = 0; j < t.num_kt; ++j, ring.advance()) {
           ok = mbar_wait(empty_addr + 8 * ring.stage, ring.phase ^ 1, abort_flag);
           if (!ok) break;
           const int key0 = (t.first_kt + j) * kKeysTC;
           const int page = t.table[key0 / page_size];
           const int in_page = key0 % page_size;
-          const int k_row = ((page * 2 + 0) * kv_heads + kvh) * page_size + in_page;   // row of the [rows, 64] view of the pool
+          const int k_row = ((page * 2 + 0) * kv_heads + kvh) * page_size + in_page;   // row of the [rows, head size] view of the pool
           const int v_row = ((page * 2 + 1) * kv_heads + kvh) * page_size + in_page;
           const uint32_t bar = full_addr + 8 * ring.stage;
           mbar_expect_tx(bar, 2 * kKeysTC * kD * 2);
-          tma_load_2d(k_addr + ring.stage * (kKeysTC * kD * 2), &map_kv, 0, k_row, bar);
-          tma_load_2d(v_addr + ring.stage * (kKeysTC * kD * 2), &map_kv, 0, v_row, bar);
+#pragma unroll
+          for (int c = 0; c < kSubTiles; ++c) {
+            tma_load_2d(k_addr + ring.stage * (kKeysTC * kD * 2) + c * (kKeysTC * kBoxDims * 2), &map_kv, c * kBoxDims, k_row, bar);
+            tma_load_2d(v_addr + ring.stage * (kKeysTC * kD * 2) + c * (kKeysTC * kBoxDims * 2), &map_kv, c * kBoxDims, v_row, bar);
+          }
         }
       }
     }
@@ -188,7 +215,11 @@ __global__ void __launch_bounds__(kThreadsTC)
       constexpr uint32_t idesc_s = umma_instr_desc(kRowsTC, kKeysTC);      // S = Q . K^T   (B = K tile, K-major)
       constexpr uint32_t idesc_pv = instr_desc_b_mn(kRowsTC, kD);          // O += P . V    (B = V tile, MN-major)
       constexpr uint32_t kTileLow = (kKeysTC * kD * 2) >> 4;               // one K or V tile further, in descriptor units
-      const uint32_t q_low = umma_desc_low(smem_u32(sm.q)), k_low = umma_desc_low(smem_u32(sm.k)), v_low = umma_desc_low(smem_u32(sm.v));
+      // V is the MN-major operand: its dims run along N.  Beyond 64 dims the next sub-tile of 64 lies kKeysTC * 128 bytes on,
+      // which the descriptor's leading-dimension offset says (bits 16-29, in 16-byte units); one sub-tile needs none.
+      constexpr uint32_t kVLeading = kSubTiles > 1 ? ((uint32_t)(kKeysTC * kBoxDims * 2) >> 4) : 1u;
+      const uint32_t q_low = umma_desc_low(smem_u32(sm.q)), k_low = umma_desc_low(smem_u32(sm.k));
+      const uint32_t v_low = ((smem_u32(sm.v) >> 4) & 0x3FFF) | (kVLeading << 16);
       const uint32_t p_low = umma_desc_low(smem_u32(sm.p));
       const uint32_t kv_full = smem_u32(sm.kv_full), kv_empty = smem_u32(sm.kv_empty), s_full = smem_u32(sm.s_full), s_empty = smem_u32(sm.s_empty);
       const uint32_t p_full = smem_u32(sm.p_full), pv_full = smem_u32(&sm.pv_full);
@@ -200,7 +231,10 @@ __global__ void __launch_bounds__(kThreadsTC)
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t k_tile = k_low + s_ring.stage * kTileLow;
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) umma_bf16(tmem + b * kKeysTC, q_low + kk * 2, k_tile + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < kD / 16; ++kk) {   // 16 dims further: 32 bytes inside a sub-tile's rows, then the next sub-tile
+          constexpr uint32_t kQSub = (kRowsTC * kBoxDims * 2) >> 4, kKSub = (kKeysTC * kBoxDims * 2) >> 4;
+          umma_bf16(tmem + b * kKeysTC, q_low + (kk >> 2) * kQSub + (kk & 3) * 2, k_tile + (kk >> 2) * kKSub + (kk & 3) * 2, idesc_s, kk > 0 ? 1u : 0u);
+        }
         umma_commit(s_full + 8 * b);
         s_ring.advance();
         return true;
@@ -213,7 +247,8 @@ __global__ void __launch_bounds__(kThreadsTC)
         ok = mbar_wait(&sm.q_full, q_phase, abort_flag);
         q_phase ^= 1;
         if (ok) ok = issue_s(g);
-        const uint32_t tmem_o = tmem + (2 + u) * kKeysTC;   // this row tile's running output
+        const uint32_t tmem_o = tmem + kOutCol0 + u * kOutStride;   // this row tile's running output
+        bool output_free = !(kCompact && u > 0);   // the one output buffer: the softmax warps must have read the first row tile's result out of it
         for (int j = 0; j < t.num_kt && ok; ++j, ++g, pv_ring.advance()) {
           if (j + 1 < t.num_kt) {
             ok = issue_s(g + 1);   // the next tile's scores run under this tile's softmax
@@ -223,12 +258,16 @@ __global__ void __launch_bounds__(kThreadsTC)
           if (!ok) break;
           const uint32_t b = g & 1;
           ok = mbar_wait(p_full + 8 * b, (g >> 1) & 1, abort_flag);   // P is written (and O rescaled, if it had to be)
+          if (ok && !output_free) {
+            ok = mbar_wait(&sm.o_read, 0, abort_flag);
+            output_free = true;
+          }
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint32_t p_tile = p_low + b * ((kRowsTC * kKeysTC * 2) >> 4), v_tile = v_low + pv_ring.stage * kTileLow;
+          const uint32_t p_tile = p_low + (kCompact ? 0u : b) * ((kRowsTC * kKeysTC * 2) >> 4), v_tile = v_low + pv_ring.stage * kTileLow;
 #pragma unroll
-          for (int kk = 0; kk < kKeysTC / 16; ++kk)   // 16 keys further: 32 bytes inside P's rows, 16 rows (2048 bytes) down in V
-            umma_bf16(tmem_o, p_tile + kk * 2, v_tile + kk * ((16 * kD * 2) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kKeysTC / 16; ++kk)   // 16 keys further: 32 bytes inside P's rows, 16 rows (2048 bytes) down in a V sub-tile
+            umma_bf16(tmem_o, p_tile + kk * 2, v_tile + kk * ((16 * kBoxDims * 2) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
           umma_commit(pv_full);
           umma_commit(kv_empty + 8 * pv_ring.stage);   // both products of this stage are done when this fires
         }
@@ -247,7 +286,7 @@ __global__ void __launch_bounds__(kThreadsTC)
       if (t.num_kt == 0) continue;
       const int my_pos = t.pos0 + min(row, t.rows_here - 1);   // rows past the end behave like the last row; never stored
       const int my_lo = (window > 0 && my_pos - window + 1 > 0) ? my_pos - window + 1 : 0;
-      const uint32_t tmem_o = tmem + lane_base + (2 + u) * kKeysTC;
+      const uint32_t tmem_o = tmem + lane_base + kOutCol0 + u * kOutStride;
       // The row's reference maximum (times scale * log2 e) that the exponents are taken against, and the sum against it.
       float reference = -INFINITY, row_sum = 0.0f;
       for (int j = 0; j < t.num_kt && ok; ++j, ++g) {
@@ -296,11 +335,14 @@ __global__ void __launch_bounds__(kThreadsTC)
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float alpha = grown ? exp2f(reference - scaled_max) : 1.0f;
-            float o[kD];
-            tmem_ld64(tmem_o, o);
 #pragma unroll
-            for (int i = 0; i < kD; ++i) o[i] *= alpha;
-            tmem_st64(tmem_o, o);
+            for (int c = 0; c < kSubTiles; ++c) {   // 64 columns of the output at a time
+              float o[64];
+              tmem_ld64(tmem_o + c * 64, o);
+#pragma unroll
+              for (int i = 0; i < 64; ++i) o[i] *= alpha;
+              tmem_st64(tmem_o + c * 64, o);
+            }
             row_sum *= alpha;
             if (grown) reference = scaled_max;
           }
@@ -319,7 +361,13 @@ __global__ void __launch_bounds__(kThreadsTC)
         }
         row_sum += sum;
         // P as bfloat16 into the swizzled K-major tile: row r at (r / 8) * 1024 + (r % 8) * 128, 16-byte chunk c at c ^ (r % 8)
-        uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p[b]) + (row >> 3) * 1024 + (row & 7) * 128;
+        if (kCompact && g > 0) {
+          // one P buffer: the product of the tile before must have read it.  The parity is enough: this warp waited for the product
+          // two tiles back before it wrote P of the tile before, so the barrier cannot be further behind than that phase.
+          ok = mbar_wait(&sm.pv_full, (g - 1) & 1, abort_flag);
+          if (!ok) break;
+        }
+        uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p[kCompact ? 0 : b]) + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
         for (int c = 0; c < kKeysTC / 8; ++c)
           *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
@@ -329,7 +377,9 @@ __global__ void __launch_bounds__(kThreadsTC)
           const int first_bad = t.n_keys - key0;
           uint8_t* v_tile = reinterpret_cast<uint8_t*>(sm.v[g % kKvStages]);
           for (int r = first_bad + (row >> 3); r < kKeysTC; r += kRowsTC / 8)
-            *reinterpret_cast<uint4*>(v_tile + (r >> 3) * 1024 + (r & 7) * 128 + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int c = 0; c < kSubTiles; ++c)
+              *reinterpret_cast<uint4*>(v_tile + c * (kKeysTC * kBoxDims * 2) + (r >> 3) * 1024 + (r & 7) * 128 + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");   // and a rescaled O before the product that adds to it
@@ -342,15 +392,23 @@ __global__ void __launch_bounds__(kThreadsTC)
       if (ok) ok = mbar_wait(&sm.o_full[u], 0, abort_flag);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        float o[kD];
-        tmem_ld64(tmem_o, o);
-        if (row < t.rows_here) {
-          const float inv = 1.0f / row_sum;
-          __nv_bfloat16* dst = out + ((size_t)(t.row0 + row) * q_heads + head) * kD;
+        const float inv = 1.0f / row_sum;
 #pragma unroll
-          for (int c = 0; c < kD / 8; ++c)
-            *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv), pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
-                                                               pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+        for (int half = 0; half < kSubTiles; ++half) {   // 64 columns of the output at a time (the load is warp-wide: every row takes part)
+          float o[64];
+          tmem_ld64(tmem_o + half * 64, o);
+          if (row < t.rows_here) {
+            __nv_bfloat16* dst = out + ((size_t)(t.row0 + row) * q_heads + head) * kD + half * 64;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv), pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                                                 pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+          }
+        }
+        if (kCompact && u == 0) {   // the output buffer may be written again
+          asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.o_read);
         }
       }
     }
@@ -384,27 +442,40 @@ using namespace tlie;
 
 TLIE_EXPORT int tlie_prefill_attention_tc_tile_rows() { return kRowsTC; }
 
-// q: the step's rows [tokens, q_row_stride] starting with the rotated q heads (head size 64); pages: one layer's pool
-// [num_pages, 2, kv_heads, page_size, 64]; tiles: int32 [n_tiles, 4] work items of one or two 128-row tiles (request, first
-// row, request or -1, first row); error_flag: device int, zero.
-TLIE_EXPORT int tlie_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* pages, int num_pages, const int* tiles,
-                                          int n_tiles, const int* seq_starts, const int* first_positions, const int* block_table,
-                                          int table_stride, void* out, int q_heads, int kv_heads, int page_size, int window, float scale,
-                                          int* error_flag, cudaStream_t stream) {
-  if (n_tiles <= 0) return 0;
-  if (kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads > 65535 || page_size % kKeysTC != 0 || q_row_stride % 8 != 0 || error_flag == nullptr)
-    return (int)cudaErrorInvalidValue;
+template <int kD>
+static int launch_attention_tc(const void* q, int q_row_stride, int tokens, const void* pages, int num_pages, const int* tiles, int n_tiles,
+                               const int* seq_starts, const int* first_positions, const int* block_table, int table_stride, void* out, int q_heads,
+                               int kv_heads, int page_size, int window, float scale, int* error_flag, cudaStream_t stream) {
   CUtensorMap map_q, map_kv;
   if (!make_map_2d(&map_q, q, tokens, (long long)q_heads * kD, q_row_stride, kRowsTC)) return (int)cudaErrorInvalidValue;
   if (!make_map_2d(&map_kv, pages, (long long)num_pages * 2 * kv_heads * page_size, kD, kD, kKeysTC)) return (int)cudaErrorInvalidValue;
-  const int smem = (int)sizeof(SmemTC) + 1024;
+  // head size 128: exactly the structure, no room to align it by hand (the kernel checks that it need not): 1 KB more and two CTAs no longer share an SM
+  const int smem = (int)sizeof(SmemTC<kD>) + (kD <= 64 ? 1024 : 0);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<kD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(n_tiles, q_heads);
-  return (int)launch_pdl(prefill_attention_tc_kernel, grid, dim3(kThreadsTC), (size_t)smem, stream, map_q, map_kv, tiles, seq_starts, first_positions,
+  return (int)launch_pdl(prefill_attention_tc_kernel<kD>, grid, dim3(kThreadsTC), (size_t)smem, stream, map_q, map_kv, tiles, seq_starts, first_positions,
                          block_table, table_stride, (__nv_bfloat16*)out, q_heads, kv_heads, page_size, window, scale, error_flag);
+}
+
+// q: the step's rows [tokens, q_row_stride] starting with the rotated q heads (head size 64 or 128); pages: one layer's pool
+// [num_pages, 2, kv_heads, page_size, head size]; tiles: int32 [n_tiles, 4] work items of one or two 128-row tiles (request, first
+// row, request or -1, first row); error_flag: device int, zero.
+TLIE_EXPORT int tlie_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* pages, int num_pages, const int* tiles,
+                                          int n_tiles, const int* seq_starts, const int* first_positions, const int* block_table,
+                                          int table_stride, void* out, int q_heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                                          int* error_flag, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads > 65535 || page_size % kKeysTC != 0 || q_row_stride % 8 != 0 || error_flag == nullptr ||
+      (head_dim != 64 && head_dim != 128))
+    return (int)cudaErrorInvalidValue;
+  if (head_dim == 64)
+    return launch_attention_tc<64>(q, q_row_stride, tokens, pages, num_pages, tiles, n_tiles, seq_starts, first_positions, block_table, table_stride, out,
+                                   q_heads, kv_heads, page_size, window, scale, error_flag, stream);
+  return launch_attention_tc<128>(q, q_row_stride, tokens, pages, num_pages, tiles, n_tiles, seq_starts, first_positions, block_table, table_stride, out,
+                                  q_heads, kv_heads, page_size, window, scale, error_flag, stream);
 }

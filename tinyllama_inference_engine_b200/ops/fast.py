@@ -504,20 +504,23 @@ def prefill_attention(qkv, pages, tiles, seq_starts, first_positions, block_tabl
     )
 
 
-use_tc_attention = True    # the tcgen05 / tensor-memory prompt attention (head size 64, pages of a multiple of 64 keys)
+use_tc_attention = True    # the tcgen05 / tensor-memory prompt attention (head size 64 or 128, pages of a multiple of 64 keys)
+TC_ATTENTION_HEAD_DIMS = (64, 128)
 TC_ATTENTION_MIN_ROWS_PER_TILE = 32
 
 
-def prefill_attention_tc(qkv, pages, tiles, seq_starts, first_positions, block_table, out, q_heads: int, kv_heads: int, page_size: int,
+def prefill_attention_tc(qkv, pages, tiles, seq_starts, first_positions, block_table, out, q_heads: int, kv_heads: int, head_dim: int, page_size: int,
                          window: int, scale: float) -> None:
-    """Flash attention of the work items in ``tiles`` (int32 [n, 4], see ``paired_attention_tiles``) on the 5th-generation tensor cores; head size 64, bfloat16."""
+    """Flash attention of the work items in ``tiles`` (int32 [n, 4], see ``paired_attention_tiles``) on the 5th-generation tensor cores; head size 64 or 128, bfloat16."""
     ops = _ops()
+    if head_dim not in TC_ATTENTION_HEAD_DIMS or page_size % 64 != 0:
+        raise KernelError("the tensor-memory attention takes head sizes 64 and 128 and pages of a multiple of 64 keys", code="invalid_shape")
     lib = load_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"])
     ops._check(
         lib.tlie_prefill_attention_tc(
             ops._ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), ops._ptr(pages), c_int(pages.shape[0]), ops._i32(tiles, "tiles"), c_int(tiles.shape[0]),
             ops._i32(seq_starts, "seq_starts"), ops._i32(first_positions, "first_positions"), ops._i32(block_table, "block_table"),
-            c_int(block_table.shape[1]), ops._ptr(out), c_int(q_heads), c_int(kv_heads), c_int(page_size), c_int(window), c_float(scale),
+            c_int(block_table.shape[1]), ops._ptr(out), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(page_size), c_int(window), c_float(scale),
             ops._ptr(tcgen05_error_flag(qkv.device)), ops._stream(),
         ),
         "prefill_attention_tc",
@@ -533,9 +536,9 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
         decode_attention(qkv, pages, positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, splits)
         return True
     tc_tiles = batch.plan("attention_tiles_tc")
-    if (use_tc_attention and tc_tiles is not None and head_dim == 64 and page_size % 64 == 0 and pages.is_contiguous()
+    if (use_tc_attention and tc_tiles is not None and head_dim in TC_ATTENTION_HEAD_DIMS and page_size % 64 == 0 and pages.is_contiguous()
             and batch.num_tokens >= TC_ATTENTION_MIN_ROWS_PER_TILE * 2 * tc_tiles.shape[0]):
-        prefill_attention_tc(qkv, pages, tc_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads, page_size, window, scale)
+        prefill_attention_tc(qkv, pages, tc_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale)
         return True
     tiles = batch.plan("attention_tiles")
     if tiles is not None and head_dim <= 128:
