@@ -244,3 +244,30 @@ def test_step_timings_and_layer_trace(model_folders):
         for name, want in plain_trace.items():
             got = torch.cat([trace[name], second_trace[name]]).cpu()
             assert got.shape == want.shape and float((got - want).abs().max()) <= fraction * float(want.abs().max()), name
+
+
+@pytest.mark.parametrize("dtype,fraction", [("float32", 2e-5), ("bfloat16", 2.5e-2)])
+def test_step_shapes_that_repeat_are_replayed_as_graphs(model_folders, dtype, fraction):
+    """A step shape that comes up again is captured as a CUDA graph and replayed: other tokens, other positions, other pages
+    and other wanted places each time, the same logits as the plain implementation every time."""
+    from tinyllama_inference_engine_b200.engine.batch import StepEntry
+
+    folder = model_folders["e"]
+    config, weights = plain_llama.load_model(folder)
+    runner = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=64, max_cache_tokens=2048, max_requests=4, max_batch_tokens=512, use_cuda_graphs=True))
+    prompts = _prompts(config["vocab_size"], [330, 330, 330, 330, 330], seed=31)
+    worst = 0.0
+    for index, tokens in enumerate(prompts):
+        full = plain_llama.forward(config, weights, tokens)
+        scale = float(full.abs().max())
+        # the same three shapes for every request of 330 tokens: (150 tokens, 1 wanted), (150, 2), (30, 30); the pool hands out other pages
+        cuts = [(0, 150, [149 - index]), (150, 300, [index, 149]), (300, len(tokens), list(range(len(tokens) - 300)))]
+        for begin, end, want in cuts:
+            got = runner.step([StepEntry(f"r{index}", tokens[begin:end], want)])
+            expect = torch.stack([full[begin + w] for w in want])
+            worst = max(worst, float((got.cpu() - expect).abs().max()) / scale)
+        if index % 2:
+            runner.finish(f"r{index}")   # some requests stay, so that later ones get other pages
+    assert worst <= fraction, worst
+    graphs = [slot for slot in runner._step_graphs.values() if slot.graph is not None]
+    assert len(graphs) == 3 and all(slot.uses >= 4 for slot in graphs)

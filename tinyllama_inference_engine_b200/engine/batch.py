@@ -87,9 +87,8 @@ class StepContext:
         return self.plans.get(name)
 
 
-def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[int], table_rows: list[list[list[int]]],
-              device: torch.device) -> StepContext:
-    """Flatten the entries into one int32 buffer, copy it once, and slice the views."""
+def lay_out_step(entries: list[StepEntry], first_positions: list[int], slots: list[int], table_rows: list[list[list[int]]]) -> dict:
+    """The step as one flat list of int32 words and where its sections lie (host work only)."""
     q_lens = [len(e.tokens) for e in entries]
     num_tokens, num_seqs = sum(q_lens), len(entries)
     token_ids: list[int] = []
@@ -119,21 +118,46 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         table_offsets.append((len(flat), num_seqs, width))
         for row in rows:
             flat += row
-    host = torch.tensor(flat, dtype=torch.int32)
-    if device.type == "cuda":
-        host = host.pin_memory()
-    buffer = host.to(device, non_blocking=True)
+    return {"flat": flat, "offsets": offsets, "table_offsets": table_offsets, "plans": plans, "q_lens": q_lens, "seq_lens": seq_lens,
+            "num_tokens": num_tokens, "num_seqs": num_seqs, "want_rows": want_rows}
+
+
+def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[int], table_rows: list[list[list[int]]],
+              device: torch.device, into: tuple | None = None) -> StepContext:
+    """Flatten the entries into one int32 buffer, copy it once, and slice the views.
+
+    ``into``: (pinned host tensor, device tensor) of fixed address to write and copy into, for a step whose kernels were captured
+    in a CUDA graph and read their description from there; they must be at least as long as the step's layout."""
+    layout = lay_out_step(entries, first_positions, slots, table_rows)
+    flat, offsets, table_offsets, plans = layout["flat"], layout["offsets"], layout["table_offsets"], layout["plans"]
+    if into is None:
+        host = torch.tensor(flat, dtype=torch.int32)
+        if device.type == "cuda":
+            host = host.pin_memory()
+        buffer = host.to(device, non_blocking=True)
+    else:
+        host, buffer = into
+        host.numpy()[: len(flat)] = flat
+        buffer[: len(flat)].copy_(host[: len(flat)], non_blocking=True)
     views = [buffer[o : o + n] for o, n in offsets]
     tables = [buffer[o : o + b * w].view(b, w) for o, b, w in table_offsets]
+    want_rows, num_tokens = layout["want_rows"], layout["num_tokens"]
     return StepContext(
-        num_tokens=num_tokens, num_seqs=num_seqs,
+        num_tokens=num_tokens, num_seqs=layout["num_seqs"],
         token_ids=views[0], positions=views[1], token_seq=views[2], seq_starts=views[3], seq_lens=views[4],
         first_positions=views[5], state_slots=views[6], want_rows=views[7] if want_rows else None,
-        block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=q_lens,
+        block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=layout["q_lens"],
         host_first_positions=list(first_positions), host_state_slots=list(slots),
-        max_q_len=max(q_lens), max_seq_len=max(seq_lens), wants_every_row_in_order=want_rows == list(range(num_tokens)),
+        max_q_len=max(layout["q_lens"]), max_seq_len=max(layout["seq_lens"]), wants_every_row_in_order=want_rows == list(range(num_tokens)),
         plans={plan.name: views[8 + i].view(-1, plan.columns) for i, plan in enumerate(plans)},
     )
+
+
+def step_shape(entries: list[StepEntry]) -> tuple:
+    """What of a step decides its kernels' launch shapes and its buffer's layout: every entry's number of tokens and of wanted
+    places (and whether all rows are wanted in order).  Everything else about it is data the kernels read on the device."""
+    in_order = all(entry.want == list(range(len(entry.tokens))) for entry in entries)
+    return tuple((len(entry.tokens), len(entry.want)) for entry in entries) + (in_order,)
 
 
 def decode_context(buffer: torch.Tensor, count: int, table_width: int, groups: int, max_positions: int, request_ids: list) -> tuple["StepContext", list]:

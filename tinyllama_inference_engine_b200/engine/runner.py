@@ -18,10 +18,50 @@ from ..errors import BatchError, KernelError
 from ..models import DecoderModel, expected_tensors
 from ..parts.base import Runtime, Workspace
 from ..weights import WeightStore
-from .batch import StepContext, StepEntry, pack_step
+from .batch import StepContext, StepEntry, lay_out_step, pack_step, step_shape
 from .timing import StepClock, StepTimings
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+STEP_GRAPH_AFTER_USES = 2    # a step shape is captured when it comes up the second time
+MAX_STEP_GRAPHS = 32         # captured shapes kept (least recently used goes first)
+
+
+class GraphedStep:
+    """One step shape: its description's buffer of fixed address and, from its second use on, the CUDA graph of its kernels."""
+
+    def __init__(self):
+        self.uses = 0
+        self.host: torch.Tensor | None = None
+        self.device: torch.Tensor | None = None
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+
+    def run(self, runner: "ModelRunner", entries, firsts, slots, table_rows) -> torch.Tensor | None:
+        if self.host is None:
+            words = len(lay_out_step(entries, firsts, slots, table_rows)["flat"])
+            self.host = torch.zeros(words, dtype=torch.int32).pin_memory()
+            self.device = torch.zeros(words, dtype=torch.int32, device=runner.device)
+        ctx = pack_step(entries, firsts, slots, table_rows, runner.device, into=(self.host, self.device))
+        # launch shapes chosen from the context length must hold for every later step of this shape
+        ctx.max_seq_len = runner.spec.max_positions
+        if self.graph is not None:
+            self.graph.replay()
+            return None if self.logits is None else self.logits.clone()   # the graph's own memory is written again by the next replay
+        # This use runs kernel by kernel (with the settings the capture will have, so that every library and buffer it needs
+        # exists), then the same launches are recorded for the uses to come.
+        logits = runner.run(ctx)
+        graph = torch.cuda.CUDAGraph()
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            graph.capture_begin()
+            try:
+                self.logits = runner.run(ctx)
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream().wait_stream(stream)
+        self.graph = graph
+        return logits
 
 
 class ModelRunner:
@@ -45,6 +85,7 @@ class ModelRunner:
         )
         self.steps = 0
         self.tokens_run = 0
+        self._step_graphs: dict[tuple, GraphedStep] = {}
 
     # --- the step --------------------------------------------------------------------------
     def validate(self, entries: list[StepEntry]) -> list[int]:
@@ -102,16 +143,40 @@ class ModelRunner:
             slots.append(self.cache.records[entry.request_id].slot)
         ids = [e.request_id for e in entries]
         table_rows = [self.cache.block_table_rows(group, ids) for group in self.cache.page_groups]
-        ctx = pack_step(entries, firsts, slots, table_rows, self.device)
-        clock.mark()
-        logits = self.run(ctx, trace)
-        clock.mark()
+        graphed = self._graphed_step(entries) if timings is None and trace is None else None
+        if graphed is not None:
+            logits = graphed.run(self, entries, firsts, slots, table_rows)
+        else:
+            ctx = pack_step(entries, firsts, slots, table_rows, self.device)
+            clock.mark()
+            logits = self.run(ctx, trace)
+            clock.mark()
         for entry, first in zip(entries, firsts):
             self.cache.advance(entry.request_id, first + len(entry.tokens))
         self.steps += 1
-        self.tokens_run += ctx.num_tokens
+        self.tokens_run += sum(len(entry.tokens) for entry in entries)
         clock.finish(timings, ("transfer", "compute"))
         return logits
+
+    def _graphed_step(self, entries: list[StepEntry]):
+        """The captured form of steps of this shape, once the shape has come up often enough to be worth capturing (else None).
+
+        A prompt portion of a few hundred tokens is some 160 kernels of a few microseconds each: launched one by one the host
+        needs 2.8 ms for them whatever the GPU takes (0.6 to 2 ms).  A shape that repeats is captured the second time it runs
+        and replayed from then on; the step's description (tokens, positions, block tables, work lists) lives in a buffer of
+        fixed address that every replay refreshes with one copy."""
+        if not (self.engine_config.use_cuda_graphs and self.device.type == "cuda") or self.cache.state_groups:
+            return None   # parts that keep state of their own may read the step's host lists: not capturable
+        shape = step_shape(entries)
+        slot = self._step_graphs.get(shape)
+        if slot is None:
+            if len(self._step_graphs) >= MAX_STEP_GRAPHS:
+                self._step_graphs.pop(next(iter(self._step_graphs)))   # the shape seen longest ago
+            slot = self._step_graphs[shape] = GraphedStep()
+        else:
+            self._step_graphs[shape] = self._step_graphs.pop(shape)   # most recently used last
+        slot.uses += 1
+        return slot if slot.uses >= STEP_GRAPH_AFTER_USES else None
 
     def run(self, ctx: StepContext, trace: dict | None = None) -> torch.Tensor | None:
         caches = self.cache.layer_caches(ctx.block_tables)

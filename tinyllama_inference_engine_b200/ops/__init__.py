@@ -34,8 +34,6 @@ def core():
 
 def build_all() -> list:
     """Compile every kernel set (used by the build check); returns the library paths."""
-    from . import fast
-
     return [build_library("tlie_core", CORE_SOURCES)] + fast.build_all()
 
 
@@ -169,8 +167,6 @@ def linear(x, weight, out) -> None:
             raise KernelError("linear: the 32-bit path takes 32-bit weights and outputs", code="invalid_dtype")
         _check(core().tlie_gemm_nt_f32(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), _stream()), "gemm_nt_f32")
         return
-    from . import fast
-
     fast.linear_bf16(x, weight, out)
 
 
@@ -178,8 +174,6 @@ def fused_rows_limit(dtype: torch.dtype, device: torch.device) -> int:
     """Up to how many rows a step may use the fused decode kernels (0: never, as in the 32-bit path)."""
     if dtype != torch.bfloat16 or device.type != "cuda":
         return 0
-    from . import fast
-
     return fast.FUSED_MAX_ROWS
 
 
@@ -211,8 +205,6 @@ class LazyNorm:
 
 def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
     """out = rmsnorm(residual) * norm_weight . weight^T in one kernel (``gated``: silu(gate) * up of the two halves)."""
-    from . import fast
-
     epilogue = "gated" if gated else "store"
     if fast.gemv_fits(out.shape[0], weight.shape[1], norm=True, gated=gated):
         if x.prepared is not None:
@@ -230,8 +222,6 @@ def norm_linear(x: "LazyNorm", weight, out, gated: bool = False) -> None:
 
 def can_accumulate(rows: int, weight) -> bool:
     """Whether ``linear_accumulate`` is one kernel for a step of this many rows beyond the fused row limit."""
-    from . import fast
-
     return fast.can_accumulate(rows, weight)
 
 
@@ -241,8 +231,6 @@ def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) ->
 
     ``prepare``: the lazy norm of this residual (all rows) that the next product will consume; the kernel then leaves that
     norm's input beside the residual (``prepare.prepared``), written by the threads that hold the finished sums."""
-    from . import fast
-
     rows = x.shape[0]
     preparing = (prepare is not None and prepare.rows is None and prepare.residual is residual and use_prepared_norms
                  and residual.shape[0] >= PREPARED_NORM_MIN_ROWS)
@@ -276,8 +264,6 @@ def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) ->
 
 def linear_gated(x, weight, out) -> None:
     """out = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel."""
-    from . import fast
-
     if fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True):
         fast.gemv_fused(x, weight, out, epilogue="gated")
     elif fast.use_tcgen05 and x.shape[0] >= fast.TCGEN05_MIN_ROWS and weight.shape[1] % 8 == 0 and x.is_contiguous():
@@ -325,8 +311,6 @@ def paged_attention(qkv, pages, positions, token_seq, block_table, out, q_heads:
     if scale is None:
         scale = head_dim ** -0.5
     if qkv.dtype == torch.bfloat16:
-        from . import fast
-
         if fast.paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, batch):
             return
     _check(
@@ -343,8 +327,6 @@ def attention_step(qkv, positions, token_seq, block_table, inv_freq, rotary_dim:
                    head_dim: int, page_size: int, window: int = 0, scale: float | None = None, write_cache: bool = True, batch=None) -> None:
     """Rotate q and k, store k and v in the pages, and attend: ``rope_store`` then ``paged_attention``, in one kernel where one exists."""
     if qkv.dtype == torch.bfloat16:
-        from . import fast
-
         if fast.can_fuse_rope_into_decode(batch, qkv, head_dim, q_heads, kv_heads, inv_freq, rotary_dim):
             splits = fast.decode_splits(batch.num_seqs, kv_heads, batch.max_seq_len)
             fast.decode_attention(qkv, pages, positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window,
@@ -391,3 +373,6 @@ def uniform_from(seed: int, counter: int) -> float:
     z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
     z = z ^ (z >> 31)
     return (z >> 40) / 16777216.0
+
+
+from . import fast  # noqa: E402  (the bfloat16 kernels; at the end because it refers back to this module)

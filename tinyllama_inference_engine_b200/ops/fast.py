@@ -40,10 +40,16 @@ def build_all() -> list:
     return built
 
 
-def _ops():
-    from .. import ops
+_ops_module = None
 
-    return ops
+
+def _ops():
+    global _ops_module
+    if _ops_module is None:
+        from .. import ops
+
+        _ops_module = ops
+    return _ops_module
 
 
 GEMV_KERNEL_MAX_ROWS = 16   # what gemv_fused.cu can take
