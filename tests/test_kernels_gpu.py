@@ -76,6 +76,26 @@ def test_add_rmsnorm(ops, dtype, hidden, eps):
         assert torch.allclose(got.cpu().float(), want.float(), atol=_tol(dtype, 8), rtol=_tol(dtype))
 
 
+@pytest.mark.parametrize("hidden", [2048, 1000, 4096, 5120])
+def test_add_rmsnorm_of_many_rows(ops, hidden):
+    """Steps of hundreds of rows normalise with a warp per row (bfloat16 out; widths up to 4096, wider ones on the other kernel)."""
+    torch.manual_seed(2)
+    rows_total, eps = 300, 1e-5
+    residual = torch.randn(rows_total, hidden) * 3
+    delta = torch.randn(rows_total, hidden).bfloat16()
+    weight = 1 + 0.1 * torch.randn(hidden)
+    picked = torch.randperm(rows_total)[:260].to(torch.int32)
+    for use_delta, rows in ((True, None), (False, None), (False, picked)):
+        r_plain, r_gpu = residual.clone(), residual.clone().cuda()
+        n = rows_total if rows is None else rows.shape[0]
+        want = torch.empty(n, hidden, dtype=torch.bfloat16)
+        plain_ops.add_rmsnorm(r_plain, delta if use_delta else None, weight, eps, want, rows)
+        got = torch.full((n, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.add_rmsnorm(r_gpu, delta.cuda() if use_delta else None, weight.cuda(), eps, got, None if rows is None else rows.cuda())
+        assert torch.allclose(r_gpu.cpu(), r_plain, atol=1e-6)
+        assert torch.allclose(got.cpu().float(), want.float(), atol=_tol(torch.bfloat16, 8), rtol=_tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul_and_add(ops, dtype):
     torch.manual_seed(2)
