@@ -182,3 +182,59 @@ def test_toy_mixer_with_state_steps_on_cpu(toy_folder, monkeypatch):
 @pytest.mark.parametrize("dtype,fraction", [("float32", 2e-5), ("bfloat16", 2.5e-2)])
 def test_toy_mixer_with_state_steps_on_gpu(toy_folder, dtype, fraction):
     _check_toy(toy_folder, "cuda:0", dtype, fraction)
+
+
+class DeviceDecayMixer(DecayMixer):
+    """The same recurrence from the step's device tensors alone: every row's state is a decayed sum over the earlier rows of
+    its own entry plus the decayed state its request carried in, so nothing of the step is read on the host and a step
+    through it may be captured and replayed with other tokens, positions and slots."""
+
+    capturable = True
+
+    def forward(self, x, ctx, cache):
+        drive = x.float() @ self.w_in.T
+        entry = ctx.token_seq.long()
+        position = ctx.positions.float()
+        gap = position[:, None] - position[None, :]
+        weight = torch.where((entry[:, None] == entry[None, :]) & (gap >= 0), self.decay ** gap.clamp(min=0), torch.zeros_like(gap))
+        slots = ctx.state_slots.long()
+        carried = cache.state[slots[entry]] * (self.decay ** (position - ctx.first_positions.float()[entry] + 1))[:, None]
+        states = weight @ drive + carried
+        cache.state[slots] = states[ctx.seq_starts[1:].long() - 1]          # each entry's last row is what its request keeps
+        return (states @ self.w_out.T).to(x.dtype)
+
+
+@pytest.mark.gpu
+def test_a_part_with_state_that_vouches_for_itself_runs_in_the_graphs(toy_folder):
+    """Whether steps are captured is each part's own word (``capturable``), not a property of having state: the toy model with
+    the host-loop mixer runs kernel by kernel, with the device-only mixer its decode steps and repeated prompt shapes are
+    captured, and both generate what the uncaptured engine generates."""
+    from tinyllama_inference_engine_b200 import Engine, SamplingParams
+
+    rng = np.random.default_rng(5)
+    prompts = [[int(t) for t in rng.integers(0, 97, size=n)] for n in (33, 33, 33, 20)]
+
+    class DeviceRouted(RoutedFeedForward):      # the other two toys read nothing on the host as they are: they only have to say so
+        capturable = True
+
+    class DeviceWave(WavePosition):
+        capturable = True
+
+    def run(mixer, graphs):
+        register_part("mixer", "toy_decay", mixer, replace=True)
+        register_part("feed_forward", "toy_routed", DeviceRouted, replace=True)
+        register_part("position", "toy_wave", DeviceWave, replace=True)
+        engine = Engine(toy_folder, EngineConfig(dtype="float32", page_size=16, max_cache_tokens=640, max_requests=4, max_batch_tokens=40, use_cuda_graphs=graphs))
+        out = []
+        for wave in range(3):                      # the same step shapes come up again: prompt steps are captured the second time
+            out.append([r.generated_tokens for r in engine.generate(prompts, SamplingParams(max_tokens=12))])
+        captured = sum(1 for s in engine._sessions.values() if s.graph is not None), sum(1 for g in engine.runner._step_graphs.values() if g.graph is not None)
+        return out, engine.runner.model.capturable, captured
+
+    plain, vouched, captured = run(DecayMixer, True)
+    assert not vouched and captured == (0, 0)
+    eager, vouched, captured = run(DeviceDecayMixer, False)
+    assert vouched and captured == (0, 0) and eager == plain
+    graphed, vouched, captured = run(DeviceDecayMixer, True)
+    assert vouched and captured[0] >= 1 and captured[1] >= 1
+    assert graphed == plain

@@ -165,8 +165,8 @@ class ModelRunner:
         needs 2.8 ms for them whatever the GPU takes (0.6 to 2 ms).  A shape that repeats is captured the second time it runs
         and replayed from then on; the step's description (tokens, positions, block tables, work lists) lives in a buffer of
         fixed address that every replay refreshes with one copy."""
-        if not (self.engine_config.use_cuda_graphs and self.device.type == "cuda") or self.cache.state_groups:
-            return None   # parts that keep state of their own may read the step's host lists: not capturable
+        if not (self.engine_config.use_cuda_graphs and self.device.type == "cuda" and self.model.capturable):
+            return None   # some part reads the step on the host: kernel by kernel
         shape = step_shape(entries)
         slot = self._step_graphs.get(shape)
         if slot is None:

@@ -1,7 +1,7 @@
 """A decoder assembled from a ModelSpec: embedding, the ordered runs of blocks, norm, head."""
 from __future__ import annotations
 
-from ..parts.base import CacheNeed, LayerCache, Runtime, build_part, part_class
+from ..parts.base import CacheNeed, LayerCache, Runtime, build_part, capturable, part_class
 from ..parts.spec import ModelSpec, TensorSpec
 
 
@@ -37,6 +37,8 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm["name"], weights, runtime)
         self.head = build_part("head", spec.head, "", weights, runtime)
         self.cache_needs = cache_needs(spec)
+        # whether a step through this model may be captured as a CUDA graph: every part has to vouch for itself
+        self.capturable = all(capturable(part) for part in [self.embedding, *self.blocks, self.final_norm, self.head])
 
     def forward(self, ctx, caches: dict[int, LayerCache], trace: dict | None = None):
         """Logits (32-bit, [len(want_rows), vocab]) of the rows ``ctx.want_rows``.

@@ -22,6 +22,7 @@ class Attention(Mixer):
     weights are stacked once at load time and one product yields ``[q | k | v]``.
     """
 
+    capturable = True
     accepts_lazy_norm = True
     fuses_residual_add = True
     prepares_next_norm = True

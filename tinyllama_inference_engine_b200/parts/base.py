@@ -119,6 +119,10 @@ class Runtime:
 
 class Part:
     category = ""
+    # True: forward launches kernels only and reads nothing of the step on the host (no ``ctx.host_*`` list, no ``.item()``),
+    # so a step through it can be captured as a CUDA graph and replayed with other tokens.  A model is captured only if every
+    # part of it says so; a part that says nothing runs kernel by kernel.
+    capturable = False
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
@@ -128,6 +132,13 @@ class Part:
         self.spec = spec
         self.prefix = prefix
         self.runtime = runtime
+
+
+def capturable(part) -> bool:
+    """Whether the part and every part it holds can be captured (see ``Part.capturable``)."""
+    if not part.capturable:
+        return False
+    return all(capturable(value) for value in vars(part).values() if isinstance(value, Part))
 
 
 class Norm(Part):

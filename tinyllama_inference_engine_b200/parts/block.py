@@ -18,6 +18,7 @@ class PreNormResidualBlock(Block):
 
     _SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"))
 
+    capturable = True
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
         specs: list[TensorSpec] = []

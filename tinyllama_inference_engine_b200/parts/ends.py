@@ -16,6 +16,7 @@ class TokenEmbedding(Part):
     with a device memcpy, src/cuda/model.cu:572-576).
     """
 
+    capturable = True
     category = "embedding"
 
     @classmethod
@@ -43,6 +44,7 @@ class LinearHead(Part):
     (src/model_config.cpp:72).
     """
 
+    capturable = True
     category = "head"
 
     @classmethod

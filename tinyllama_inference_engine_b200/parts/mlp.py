@@ -19,6 +19,7 @@ class GatedMLP(FeedForward):
     ``up`` are computed in 32-bit.
     """
 
+    capturable = True
     accepts_lazy_norm = True
     fuses_residual_add = True
     prepares_next_norm = True

@@ -16,6 +16,7 @@ class RMSNorm(Norm):
     the weight is held in 32-bit (exact for a bfloat16 checkpoint).
     """
 
+    capturable = True
     supports_lazy = True
 
     @classmethod

@@ -18,6 +18,8 @@ class RotaryEmbedding(PositionEncoding):
     depends on this part.
     """
 
+    capturable = True
+
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
         self.rotary_dim = int(spec["rotary_dim"])
@@ -33,6 +35,8 @@ class RotaryEmbedding(PositionEncoding):
 
 class NoPositionEncoding(PositionEncoding):
     """Leaves q and k as they are (a mixer that needs no positions)."""
+
+    capturable = True
 
     def rotary_table(self):
         return None
