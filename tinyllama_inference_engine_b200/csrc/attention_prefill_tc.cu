@@ -118,6 +118,34 @@ __device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_
       : "memory");
 }
 
+// A softmax thread's time is its instruction count (a warp issues an instruction every two to three cycles at best), so the loop
+// over a row's scores uses what this GPU has for it: the maximum of three numbers in one instruction, and multiply-add and add
+// on two floats at once (the same roundings as one at a time).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+struct Float2Bits {
+  unsigned long long bits;
+};
+__device__ __forceinline__ Float2Bits pair_of(float lo, float hi) {
+  Float2Bits r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r.bits) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpair(Float2Bits v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v.bits)); }
+__device__ __forceinline__ Float2Bits fma2(Float2Bits a, Float2Bits b, Float2Bits c) {
+  Float2Bits r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits), "l"(c.bits));
+  return r;
+}
+__device__ __forceinline__ Float2Bits add2(Float2Bits a, Float2Bits b) {
+  Float2Bits r;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
+  return r;
+}
+
 // Where a CTA's time goes, when compiled with TLIE_ATTN_TIMELINE: one thread of each role of CTA (0, 0) reports the cycles of its
 // whole loop (slot 6 of its group: softmax 0-7, issuer 8-15, producer 16-23), its tiles (slot 7) and, with TLIE_ATTN_TIMELINE_SLOT = k,
 // the cycles spent between stamp k - 1 and stamp k (slot k).  One slot per build: more would cost registers the kernel does not have.
@@ -414,13 +442,13 @@ __global__ void __launch_bounds__(kThreadsTC, 2)
             tile_max = fmaxf(tile_max, sc[i]);
           }
         } else {
-          float m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;   // four chains instead of one of 64 dependent maxima
+          float m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;   // four chains of eight three-way maxima instead of one of 64 dependent ones
 #pragma unroll
-          for (int i = 0; i < kKeysTC; i += 4) {
-            tile_max = fmaxf(tile_max, sc[i]);
-            m1 = fmaxf(m1, sc[i + 1]);
-            m2 = fmaxf(m2, sc[i + 2]);
-            m3 = fmaxf(m3, sc[i + 3]);
+          for (int i = 0; i < kKeysTC; i += 8) {
+            tile_max = max3(tile_max, sc[i], sc[i + 1]);
+            m1 = max3(m1, sc[i + 2], sc[i + 3]);
+            m2 = max3(m2, sc[i + 4], sc[i + 5]);
+            m3 = max3(m3, sc[i + 6], sc[i + 7]);
           }
           tile_max = fmaxf(fmaxf(tile_max, m1), fmaxf(m2, m3));
         }
@@ -452,17 +480,20 @@ __global__ void __launch_bounds__(kThreadsTC, 2)
         const float base = (reference == -INFINITY) ? 0.0f : reference;   // a row that has seen no key yet: every p is 0
         TL(3)
         uint32_t packed[kKeysTC / 2];
-        float sum0 = 0.0f, sum1 = 0.0f;
+        const Float2Bits scale2 = pair_of(sl2, sl2), minus_base2 = pair_of(-base, -base);
+        Float2Bits sums = pair_of(0.0f, 0.0f);   // the even keys' sum and the odd keys'
         // (Taking a share of the exponentials on the FMA pipe, by a polynomial, was measured: a quarter of them gains 2 %, half
         // of them loses 17 %.)
 #pragma unroll
         for (int i = 0; i < kKeysTC / 2; ++i) {
-          const float p0 = exp2_approx(fmaf(sc[2 * i], sl2, -base));
-          const float p1 = exp2_approx(fmaf(sc[2 * i + 1], sl2, -base));
-          sum0 += p0;
-          sum1 += p1;
+          float x0, x1;
+          unpair(fma2(pair_of(sc[2 * i], sc[2 * i + 1]), scale2, minus_base2), x0, x1);
+          const float p0 = exp2_approx(x0), p1 = exp2_approx(x1);
+          sums = add2(sums, pair_of(p0, p1));
           packed[i] = pack_bf16(p0, p1);
         }
+        float sum0, sum1;
+        unpair(sums, sum0, sum1);
         row_sum += sum0 + sum1;
         TL(4)
         // P over the first 32 columns of this tile's scores: key 2 i in the lower half of column i, key 2 i + 1 in the upper.  The
