@@ -117,52 +117,59 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return v;
 }
 
+// A block takes kRopeTokens tokens: their cosines and sines are computed by that many times rotary_dim / 2 threads at once (one
+// token per block left all but 32 threads of a block of head size 64 idle while those walked through cosf and sinf, and a
+// 2,048-token step took 12 us where its bytes need 4), and every thread then has a few 16-byte pairs of its own in flight.
+constexpr int kRopeTokens = 4;
+
 __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ token_seq,
                                       const int* __restrict__ block_table, int table_stride, const float* __restrict__ inv_freq, int rotary_dim,
-                                      __nv_bfloat16* __restrict__ pages, int q_heads, int kv_heads, int head_dim, int page_size, int write_cache) {
-  __shared__ float cos_s[kMaxRotaryHalf], sin_s[kMaxRotaryHalf];
+                                      __nv_bfloat16* __restrict__ pages, int tokens, int q_heads, int kv_heads, int head_dim, int page_size, int write_cache) {
+  __shared__ float cos_s[kRopeTokens][kMaxRotaryHalf], sin_s[kRopeTokens][kMaxRotaryHalf];
+  __shared__ long long k_offset[kRopeTokens];   // where a token's k head 0 goes in the pool, in elements
   grid_launch_dependents();   // launched as a programmatic dependent: the kernel before it has completed when the wait returns
   grid_dependency_wait();
-  const int t = blockIdx.x;
+  const int t0 = blockIdx.x * kRopeTokens;
+  const int here = min(kRopeTokens, tokens - t0);
   const int row_width = (q_heads + 2 * kv_heads) * head_dim;
-  __nv_bfloat16* row = qkv + (size_t)t * row_width;
   const int half = rotary_dim / 2;
   // pairs of 8 + 8 elements of the rotated part of the q heads and (when the cache is written) the k heads
   const int pieces = half / 8;
   const int items = (q_heads + (write_cache ? kv_heads : 0)) * pieces;
+  const int all_items = here * items;
   // A thread's first pair is fetched before anything that waits for the position (the angles, the page of the cache): the
-  // row does not depend on it, and a CTA lives for one memory round trip instead of two in a row.
+  // row does not depend on it, and a block lives for one memory round trip instead of two in a row.
   uint4 first_lo = make_uint4(0, 0, 0, 0), first_hi = first_lo;
-  if ((int)threadIdx.x < items) {
-    const int head = threadIdx.x / pieces, d = (threadIdx.x - head * pieces) * 8;
-    first_lo = *reinterpret_cast<const uint4*>(row + (size_t)head * head_dim + d);
-    first_hi = *reinterpret_cast<const uint4*>(row + (size_t)head * head_dim + d + half);
+  if ((int)threadIdx.x < all_items) {
+    const int token = threadIdx.x / items, item = threadIdx.x - token * items;
+    const int head = item / pieces, d = (item - head * pieces) * 8;
+    const __nv_bfloat16* x = qkv + (size_t)(t0 + token) * row_width + (size_t)head * head_dim + d;
+    first_lo = *reinterpret_cast<const uint4*>(x);
+    first_hi = *reinterpret_cast<const uint4*>(x + half);
   }
-  const int pos = positions[t];
   if (inv_freq != nullptr) {
-    for (int d = threadIdx.x; d < half; d += blockDim.x) {
-      const float angle = (float)pos * inv_freq[d];
-      cos_s[d] = cosf(angle);
-      sin_s[d] = sinf(angle);
+    for (int index = threadIdx.x; index < here * half; index += blockDim.x) {
+      const int token = index / half, d = index - token * half;
+      const float angle = (float)positions[t0 + token] * inv_freq[d];
+      cos_s[token][d] = cosf(angle);
+      sin_s[token][d] = sinf(angle);
     }
   }
-  __nv_bfloat16* k_dst = nullptr;
-  __nv_bfloat16* v_dst = nullptr;
   const size_t head_stride_in_page = (size_t)page_size * head_dim;
-  if (write_cache) {
-    const int seq = token_seq[t];
-    const int page = block_table[(size_t)seq * table_stride + pos / page_size];
-    const size_t plane = (size_t)kv_heads * page_size * head_dim;
-    k_dst = pages + (size_t)page * 2 * plane + (size_t)(pos % page_size) * head_dim;
-    v_dst = k_dst + plane;
+  const size_t plane = (size_t)kv_heads * page_size * head_dim;
+  if (write_cache && (int)threadIdx.x < here) {
+    const int t = t0 + threadIdx.x, pos = positions[t];
+    const int page = block_table[(size_t)token_seq[t] * table_stride + pos / page_size];
+    k_offset[threadIdx.x] = (long long)((size_t)page * 2 * plane + (size_t)(pos % page_size) * head_dim);
   }
   __syncthreads();
-  for (int item = threadIdx.x; item < items; item += blockDim.x) {
+  for (int index = threadIdx.x; index < all_items; index += blockDim.x) {
+    const int token = index / items, item = index - token * items;
     const int head = item / pieces, d = (item - head * pieces) * 8;
-    const __nv_bfloat16* x = row + (size_t)head * head_dim;
-    __nv_bfloat16* dst = head >= q_heads ? k_dst + (size_t)(head - q_heads) * head_stride_in_page : row + (size_t)head * head_dim;
+    __nv_bfloat16* x = qkv + (size_t)(t0 + token) * row_width + (size_t)head * head_dim;
+    __nv_bfloat16* dst = head >= q_heads ? pages + k_offset[token] + (size_t)(head - q_heads) * head_stride_in_page : x;
     uint4 lo = first_lo, hi = first_hi;
-    if (item != (int)threadIdx.x) {
+    if (index != (int)threadIdx.x) {
       lo = *reinterpret_cast<const uint4*>(x + d);
       hi = *reinterpret_cast<const uint4*>(x + d + half);
     }
@@ -172,7 +179,7 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int
       unpack8(hi, b);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float c = cos_s[d + i], sn = sin_s[d + i];
+        const float c = cos_s[token][d + i], sn = sin_s[token][d + i];
         ra[i] = a[i] * c - b[i] * sn;
         rb[i] = b[i] * c + a[i] * sn;
       }
@@ -187,14 +194,17 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int
   if (!write_cache) return;
   // what lies past the rotated part of the k heads, and the v heads, go to the cache as they are
   const int tail = (head_dim - rotary_dim) / 8, whole = head_dim / 8;
-  for (int item = threadIdx.x; item < kv_heads * tail; item += blockDim.x) {
+  for (int index = threadIdx.x; index < here * kv_heads * tail; index += blockDim.x) {
+    const int token = index / (kv_heads * tail), item = index - token * (kv_heads * tail);
     const int head = item / tail, d = rotary_dim + (item - head * tail) * 8;
-    *reinterpret_cast<uint4*>(k_dst + (size_t)head * head_stride_in_page + d) = *reinterpret_cast<const uint4*>(row + (size_t)(q_heads + head) * head_dim + d);
+    *reinterpret_cast<uint4*>(pages + k_offset[token] + (size_t)head * head_stride_in_page + d) =
+        *reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + token) * row_width + (size_t)(q_heads + head) * head_dim + d);
   }
-  for (int item = threadIdx.x; item < kv_heads * whole; item += blockDim.x) {
+  for (int index = threadIdx.x; index < here * kv_heads * whole; index += blockDim.x) {
+    const int token = index / (kv_heads * whole), item = index - token * (kv_heads * whole);
     const int head = item / whole, d = (item - head * whole) * 8;
-    *reinterpret_cast<uint4*>(v_dst + (size_t)head * head_stride_in_page + d) =
-        *reinterpret_cast<const uint4*>(row + (size_t)(q_heads + kv_heads + head) * head_dim + d);
+    *reinterpret_cast<uint4*>(pages + k_offset[token] + plane + (size_t)head * head_stride_in_page + d) =
+        *reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + token) * row_width + (size_t)(q_heads + kv_heads + head) * head_dim + d);
   }
 }
 
@@ -211,8 +221,8 @@ TLIE_EXPORT int tlie_rope_store(int dtype, void* qkv, const int* positions, cons
   const int block = 256;
   const int half = rotary_dim / 2;
   if (dtype != TLIE_F32 && half % 8 == 0 && head_dim % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)pages & 15) == 0) {
-    return (int)launch_pdl(rope_store_vec_kernel, dim3(tokens), dim3(block), 0, stream, (__nv_bfloat16*)qkv, positions, token_seq, block_table, table_stride,
-                           inv_freq, rotary_dim, (__nv_bfloat16*)pages, q_heads, kv_heads, head_dim, page_size, write_cache);
+    return (int)launch_pdl(rope_store_vec_kernel, dim3((tokens + kRopeTokens - 1) / kRopeTokens), dim3(block), 0, stream, (__nv_bfloat16*)qkv, positions, token_seq,
+                           block_table, table_stride, inv_freq, rotary_dim, (__nv_bfloat16*)pages, tokens, q_heads, kv_heads, head_dim, page_size, write_cache);
   }
   if (dtype == TLIE_F32)
     rope_store_kernel<float><<<tokens, block, 0, stream>>>((float*)qkv, positions, token_seq, block_table,
