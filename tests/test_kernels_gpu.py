@@ -610,3 +610,19 @@ def test_prefill_attention_tensor_memory(ops, q_heads, kv_heads, page_size, wind
     assert int(fast.tcgen05_error_flag(got.device)) == 0, "a bounded wait inside the kernel gave up"
     error = (got.cpu().float() - want.float()).abs().max(1).values
     assert float(error.max()) <= 1.6e-2 * 2, (int(error.argmax()), float(error.max()))
+
+
+def test_hardware_probes_report_what_the_designs_rest_on():
+    """The loops of csrc/probes.cu run to the end (every wait in them is bounded) and say what the kernels assume: a tensor-core
+    product of 256 columns takes about twice one of 128, narrower ones cost no less than a floor, and a completed barrier is cheap."""
+    from tinyllama_inference_engine_b200.ops.probes import hardware_probes
+
+    report = hardware_probes("cuda:0")
+    mma = report["mma_cycles"]
+    wide, half, narrow = (mma[f"128 x {n} x 16, straight-line issue, one CTA per SM"] for n in (256, 128, 64))
+    assert 100 < wide < 200 and 1.6 < wide / half < 2.4 and narrow <= half + 8
+    assert mma["128 x 64 x 16, straight-line issue, two CTAs per SM"] > 1.5 * narrow       # two CTAs share one tensor core
+    assert 0 < report["handoff_cycles"]["wait on a completed barrier"] < 400
+    alone = report["arithmetic_cycles_per_64_values"]["64 exp2, one warp per scheduler"]
+    shared = report["arithmetic_cycles_per_64_values"]["64 exp2, two warps per scheduler"]
+    assert 400 < alone < 1200 and shared > 1.4 * alone                                       # the exponential unit is what two warps wait for

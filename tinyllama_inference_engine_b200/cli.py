@@ -19,7 +19,9 @@ stand in for it.  Options, before or after the positionals: ``--dtype bfloat16|f
 ``--temperature``, ``--top-p``, ``--seed``, ``--batch``, ``--max-batch-tokens``,
 ``--page-size``, ``--num-pages`` (cache pages; by default what the request needs),
 ``--device`` (a CUDA device; there is no CPU path and ``cpu`` is refused with an error).  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
-(median and 95th percentile), like the reference's benchmarks/kernel_benchmarks.cu:127-325.
+(median and 95th percentile), like the reference's benchmarks/kernel_benchmarks.cu:127-325; with ``--probes`` it also measures what the
+kernels' designs rest on (tensor-core time per MMA shape, the cost of a barrier hand-off, a warp's arithmetic rate), with
+``--attention-phases TOKENS`` where a key tile's cycles go in the tensor-memory prompt attention.
 """
 from __future__ import annotations
 
@@ -260,7 +262,16 @@ def _kernel_bench(args) -> int:
             times.append(start.elapsed_time(end) * 1e3)
         times.sort()
         report[name] = {"median_us": times[len(times) // 2], "p95_us": times[min(len(times) - 1, int(len(times) * 0.95))]}
-    print(json.dumps({"rows": rows, "context": context, "samples": samples, "dtype": args.dtype, "device": torch.cuda.get_device_name(0), "kernels": report}))
+    record = {"rows": rows, "context": context, "samples": samples, "dtype": args.dtype, "device": torch.cuda.get_device_name(0), "kernels": report}
+    if args.probes:
+        from .ops.probes import hardware_probes
+
+        record["probes"] = hardware_probes(dev)
+    if args.attention_phases:
+        from .ops.probes import attention_phase_cycles
+
+        record["attention_phases"] = attention_phase_cycles(args.attention_phases, QH, KVH, D, dev)
+    print(json.dumps(record))
     return 0
 
 
@@ -295,6 +306,9 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--prompt-len", type=int, default=0, help="use this many seeded random token ids as the prompt; the PROMPT argument is then left out")
     parser.add_argument("--prompt-seed", type=int, default=0)
     parser.add_argument("--device", default="cuda:0", help="the CUDA device to run on (there is no CPU path)")
+    parser.add_argument("--probes", action="store_true", help="kernel-bench: also what an MMA of each shape, a barrier hand-off and a warp's arithmetic cost on this GPU")
+    parser.add_argument("--attention-phases", type=int, default=0, metavar="TOKENS",
+                        help="kernel-bench: also where a key tile's cycles go in the tensor-memory prompt attention, for one request of TOKENS tokens (seven builds of the kernel)")
     try:
         args = parser.parse_intermixed_args(argv)
     except SystemExit as exc:

@@ -6,8 +6,9 @@
 // weight stream:
 //   * the step's rows (padded by the hardware to the 128 rows of a tcgen05.mma) are the A operand and BN = 256 (128 for more
 //     than 64 rows) rows of w the B operand; the accumulator is 128 lanes x BN columns of tensor memory.  (With the
-//     operands swapped, 128 weight rows as A and the rows as a narrow B, an MMA took the same 128 cycles for a quarter of
-//     the weight bytes, and the tensor pipe, not HBM, set the pace: measured 0.3 us per 16 KB.)
+//     operands swapped, 128 weight rows as A and the rows as a narrow B, four times the MMAs are issued for the same weight
+//     bytes; each cost the issuing thread's k loop about as long as a wide one, and that thread, not HBM, set the pace:
+//     measured 0.3 us per 16 KB.)
 //   * the weights are read from a packed copy made once per matrix (tlie_gemm_skinny_pack): block (128-row group, k block)
 //     is the 16 KB image of a 128 x 64 operand tile exactly as tcgen05.mma wants it in shared memory (K-major, 128-byte
 //     swizzle), so a stage is one or two contiguous bulk copies;

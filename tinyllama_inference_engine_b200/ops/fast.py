@@ -37,6 +37,7 @@ def build_all() -> list:
     built.append(build_library("tlie_gemm_skinny", ["gemm_skinny.cu"]))
     built.append(build_library("tlie_gemm_tcgen05", TCGEN05_SOURCES))
     built.append(build_library("tlie_attn_prefill_tc", ["attention_prefill_tc.cu"]))
+    built.append(build_library("tlie_probes", ["probes.cu"]))
     return built
 
 
