@@ -187,3 +187,35 @@ def test_malformed_files_are_refused(tmp_path):
     path.write_bytes(struct.pack("<Q", len(header)) + header + b"\0" * 4)
     with pytest.raises(EngineError, match="unsupported dtype"):
         SafetensorsFile(path)
+
+
+def test_weights_can_be_pinned_by_their_sha256(tmp_path):
+    """The reference refuses a checkpoint whose digest differs from the pinned one with checksum_mismatch (src/weight_store.cpp:150-190)."""
+    import hashlib
+
+    from tinyllama_inference_engine_b200.weights import verify_weights, weights_sha256
+
+    folder = write_random_model(tmp_path / "m", TINY_A, seed=0)
+    digest = hashlib.sha256((folder / "model.safetensors").read_bytes()).hexdigest()
+    assert weights_sha256(folder) == digest and verify_weights(folder, digest.upper()) == digest
+    with pytest.raises(EngineError, match="expected") as caught:
+        verify_weights(folder, "0" * 64)
+    assert caught.value.code == "checksum_mismatch"
+    with pytest.raises(EngineError, match="64 hexadecimal"):
+        verify_weights(folder, "abc")
+    with pytest.raises(EngineError, match="no model.safetensors"):
+        weights_sha256(tmp_path)
+    # a sharded folder: the digest of the shards' digests, in the order of their names
+    file = SafetensorsFile(folder / "model.safetensors")
+    tensors = {name: file.tensor(name).clone() for name in file.names()}
+    file.close()
+    names = sorted(tensors)
+    shards = {"model-00001-of-00002.safetensors": names[: len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2 :]}
+    sharded = tmp_path / "sharded"
+    sharded.mkdir()
+    (sharded / "config.json").write_text((folder / "config.json").read_text())
+    for shard, members in shards.items():
+        write_safetensors(sharded / shard, {name: tensors[name] for name in members})
+    (sharded / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {name: shard for shard, members in shards.items() for name in members}}))
+    combined = hashlib.sha256(b"".join(hashlib.sha256((sharded / shard).read_bytes()).digest() for shard in sorted(shards))).hexdigest()
+    assert weights_sha256(sharded) == combined

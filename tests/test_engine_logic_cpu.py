@@ -163,3 +163,16 @@ def test_block_lets_a_part_add_to_the_residual_in_steps_of_many_rows(monkeypatch
     calls.clear()
     assert PreNormResidualBlock._run(Norm(), Part(True), many, "pending", False, None) is None
     assert calls == [("norm", True, False), ("part", "normed", True)]
+
+
+def test_the_engine_refuses_weights_with_another_digest(model_folders):
+    """EngineConfig.weights_sha256 pins the model folder's weights (the reference: src/weight_store.cpp:150-190)."""
+    from tinyllama_inference_engine_b200.errors import EngineError
+    from tinyllama_inference_engine_b200.weights import weights_sha256
+
+    folder = model_folders["a"]
+    good = weights_sha256(folder)
+    ModelRunner(folder, EngineConfig(dtype="float32", page_size=16, max_cache_tokens=64, device="cpu", weights_sha256=good))
+    with pytest.raises(EngineError) as caught:
+        ModelRunner(folder, EngineConfig(dtype="float32", page_size=16, max_cache_tokens=64, device="cpu", weights_sha256="f" * 64))
+    assert caught.value.code == "checksum_mismatch"

@@ -18,7 +18,8 @@ otherwise a list of token ids separated by commas or spaces; with ``--prompt-len
 stand in for it.  Options, before or after the positionals: ``--dtype bfloat16|float32``,
 ``--temperature``, ``--top-p``, ``--seed``, ``--batch``, ``--max-batch-tokens``,
 ``--page-size``, ``--num-pages`` (cache pages; by default what the request needs),
-``--device`` (a CUDA device; there is no CPU path and ``cpu`` is refused with an error).  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
+``--device`` (a CUDA device; there is no CPU path and ``cpu`` is refused with an error), ``--weights-sha256`` (the digest the
+folder's weights must have, as the reference pins its checkpoints: src/weight_store.cpp:150-190).  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
 (median and 95th percentile), like the reference's benchmarks/kernel_benchmarks.cu:127-325; with ``--probes`` it also measures what the
 kernels' designs rest on (tensor-core time per MMA shape, the cost of a barrier hand-off, a warp's arithmetic rate), with
 ``--attention-phases TOKENS`` where a key tile's cycles go in the tensor-memory prompt attention.
@@ -86,7 +87,7 @@ def _engine(args, max_cache_tokens: int, max_requests: int = 1):
     page = args.page_size
     cache_tokens = args.num_pages * page if args.num_pages else max(page, -(-max_cache_tokens // page) * page)
     config = EngineConfig(dtype=args.dtype, page_size=page, max_cache_tokens=cache_tokens, max_requests=max(1, max_requests),
-                          max_batch_tokens=args.max_batch_tokens, device=args.device)
+                          max_batch_tokens=args.max_batch_tokens, device=args.device, weights_sha256=args.weights_sha256 or None)
     return Engine(args.model_dir, config)
 
 
@@ -306,6 +307,7 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--prompt-len", type=int, default=0, help="use this many seeded random token ids as the prompt; the PROMPT argument is then left out")
     parser.add_argument("--prompt-seed", type=int, default=0)
     parser.add_argument("--device", default="cuda:0", help="the CUDA device to run on (there is no CPU path)")
+    parser.add_argument("--weights-sha256", default="", help="the SHA-256 the model folder's weights must have; another digest is refused with checksum_mismatch")
     parser.add_argument("--probes", action="store_true", help="kernel-bench: also what an MMA of each shape, a barrier hand-off and a warp's arithmetic cost on this GPU")
     parser.add_argument("--attention-phases", type=int, default=0, metavar="TOKENS",
                         help="kernel-bench: also where a key tile's cycles go in the tensor-memory prompt attention, for one request of TOKENS tokens (seven builds of the kernel)")

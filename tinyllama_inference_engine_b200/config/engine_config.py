@@ -19,6 +19,8 @@ class EngineConfig:
     max_cache_tokens  capacity of every cache group's page pool, in tokens.
     max_requests      live requests (state slots and block-table rows).
     max_batch_tokens  token budget of one step (the scheduler cuts prompts to it).
+    weights_sha256    if given, the SHA-256 the model folder's weights must have (weights/integrity.py); loading a folder
+                      with another digest fails with ``checksum_mismatch``.
     """
 
     dtype: str = "bfloat16"
@@ -29,6 +31,7 @@ class EngineConfig:
     device: str = "cuda:0"
     use_cuda_graphs: bool = True
     poison_freed_pages: bool = False
+    weights_sha256: str | None = None
 
     def __post_init__(self) -> None:
         if self.dtype in ("bf16", "fp32"):

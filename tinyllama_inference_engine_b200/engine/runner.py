@@ -73,6 +73,10 @@ class ModelRunner:
         self.architecture, self.model_config = load_model_config(model_dir)
         self.spec = self.architecture.build_spec(self.model_config)
         self.dtype = _TORCH_DTYPES[self.engine_config.dtype]
+        if self.engine_config.weights_sha256:
+            from ..weights.integrity import verify_weights
+
+            verify_weights(model_dir, self.engine_config.weights_sha256)
         weights = WeightStore.load(model_dir, expected_tensors(self.spec), self.device)
         workspace = Workspace(self.device, self.engine_config.max_batch_tokens)
         self.runtime = Runtime(self.dtype, self.device, workspace, {"engine": self.engine_config})
