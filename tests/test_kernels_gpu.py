@@ -626,3 +626,27 @@ def test_hardware_probes_report_what_the_designs_rest_on():
     alone = report["arithmetic_cycles_per_64_values"]["64 exp2, one warp per scheduler"]
     shared = report["arithmetic_cycles_per_64_values"]["64 exp2, two warps per scheduler"]
     assert 400 < alone < 1200 and shared > 1.4 * alone                                       # the exponential unit is what two warps wait for
+
+
+@pytest.mark.parametrize("M", [1, 8, 16])
+def test_products_of_very_long_rows_stay_in_the_fused_kernel(ops, M):
+    """K = 14,336 (the down projection of the 8B shapes): eight staged rows of x would not fit the kernel's shared memory, but with no
+    more tiles than CTA slots nothing is staged at all, so the product and its residual add stay one kernel of this engine."""
+    from tinyllama_inference_engine_b200.ops import fast
+
+    torch.manual_seed(13)
+    N, K = 4096, 14336
+    x = torch.randn(M, K).bfloat16()
+    w = (torch.randn(N, K) * 0.02).bfloat16()
+    want = x.float() @ w.float().T
+    scale = float(want.abs().max())
+    residual = torch.randn(M, N)
+    assert fast.gemv_fits(M, K, norm=False, N=N) and not fast.gemv_fits(M, K, norm=False)
+    before = fast.library_gemm_calls
+    got = residual.clone().cuda()
+    ops.linear_accumulate(x.cuda(), w.cuda(), got)
+    assert torch.allclose(got.cpu(), residual + want, atol=1e-4 * scale + 1e-5)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.linear(x.cuda(), w.cuda(), out)
+    assert torch.allclose(out.cpu().float(), want, atol=1.6e-2 * scale, rtol=0)
+    assert fast.library_gemm_calls == before

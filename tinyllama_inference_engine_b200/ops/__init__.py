@@ -234,7 +234,7 @@ def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) ->
     rows = x.shape[0]
     preparing = (prepare is not None and prepare.rows is None and prepare.residual is residual and use_prepared_norms
                  and residual.shape[0] >= PREPARED_NORM_MIN_ROWS)
-    if fast.gemv_fits(rows, weight.shape[1], norm=False):
+    if fast.gemv_fits(rows, weight.shape[1], norm=False, N=weight.shape[0]):
         if preparing:
             buffers = fast.prepared_norm_buffers(residual.shape[0], residual.shape[1], residual.device) if prepare.buffers is None else prepare.buffers
             fast.gemv_fused(x, weight, residual, epilogue="accumulate", prepare=(prepare.weight, buffers[0], buffers[1]))

@@ -66,10 +66,16 @@ def gemv_library():
     return load_library("tlie_gemv_fused", ["gemv_fused.cu"])
 
 
-def gemv_fits(rows: int, K: int, norm: bool, gated: bool = False) -> bool:
-    """Whether the fused kernel's shared memory (x as bfloat16 and the warps' partial tiles) fits."""
+def gemv_fits(rows: int, K: int, norm: bool, gated: bool = False, N: int | None = None) -> bool:
+    """Whether the fused kernel's shared memory (x as bfloat16 and the warps' partial tiles) fits.
+
+    ``N`` (plain bfloat16 x only): with no more 16-row tiles than the kernel has CTA slots, every CTA computes one tile, uses each
+    element of x once and reads it straight from global memory: nothing of x is staged, and any K fits (the down projection of
+    wide models: K = 14,336 would need 229 KB for eight staged rows)."""
     if rows > GEMV_KERNEL_MAX_ROWS or K % 8 != 0:
         return False
+    if not norm and not gated and N is not None and -(-N // 16) <= 2 * sm_count():
+        return True
     padded_rows = 8 if rows <= 8 else 16
     stride = K + ((32 - K % 64) + 64) % 64
     stride += 64 if stride == K else 0
@@ -362,7 +368,7 @@ def linear_bf16(x, weight, out) -> None:
     global library_gemm_calls
     if weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("linear: the bfloat16 path takes bfloat16 weights", code="invalid_dtype")
-    if x.stride(0) % 8 == 0 and gemv_fits(x.shape[0], weight.shape[1], norm=False):
+    if x.stride(0) % 8 == 0 and gemv_fits(x.shape[0], weight.shape[1], norm=False, N=weight.shape[0]):
         gemv_fused(x, weight, out)
         return
     if use_tcgen05 and tcgen05_takes(x.shape[0], weight.shape[0], weight.shape[1]) and weight.shape[1] % 8 == 0 and x.is_contiguous():
