@@ -226,8 +226,15 @@ def run_engine(args) -> dict:
 
     sections = set(args.sections.split(","))
     largest = max(64 if "points" in sections else 1, args.batch)
-    config = EngineConfig(dtype="bfloat16", page_size=64, max_cache_tokens=largest * (prompt_tokens + 64 * (-(-generated // 64)) + 64),
-                          max_requests=largest, max_batch_tokens=max(prefill_tokens, prompt_tokens))
+    cache_tokens = largest * (prompt_tokens + 64 * (-(-generated // 64)) + 64)
+    # Requests of mixed length for the scheduler (SURVEY's 7B workload: prompts uniform between 64 tokens and the context, cut into
+    # portions under the token budget and interleaved with the other requests' decode steps); all of them fit the cache at once.
+    mixed_count, mixed_out = 32, 64
+    mixed_lengths = [int(n) for n in rng.integers(64, min(4096, shapes["max_position_embeddings"] - mixed_out - 1) + 1, size=mixed_count)]
+    if "mixed" in sections:
+        largest = max(largest, mixed_count)
+        cache_tokens = max(cache_tokens, sum(64 * (-(-(n + mixed_out) // 64)) + 64 for n in mixed_lengths))
+    config = EngineConfig(dtype="bfloat16", page_size=64, max_cache_tokens=cache_tokens, max_requests=largest, max_batch_tokens=max(prefill_tokens, prompt_tokens))
     engine = Engine(folder, config)
     runner = engine.runner
 
@@ -300,6 +307,24 @@ def run_engine(args) -> dict:
                 points[f"decode_b{batch}_hbm_frac"] = decode_bytes(shapes, layers, batch, mean_context) / (ms / 1e3) / 1e9 / peak["hbm_gbs"]
             points[f"decode_b{batch}_library_gemms_per_step"] = library_per_step.get(batch, 0)
 
+    if "mixed" in sections:
+        count, out_tokens, lengths = mixed_count, mixed_out, mixed_lengths
+        requests = [[int(t) for t in rng.integers(0, vocab, size=n)] for n in lengths]
+        for run in range(4):   # the first runs build kernels and meet every step shape and batch size (graphs are captured on the third use)
+            steps_before = runner.steps
+            torch.cuda.synchronize()
+            started = time.perf_counter()
+            results = engine.generate(requests, SamplingParams(max_tokens=out_tokens))
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - started
+        points["mixed_requests"] = count
+        points["mixed_prompt_tokens"] = sum(lengths)
+        points["mixed_generated_tokens"] = sum(len(r.generated_tokens) for r in results)
+        points["mixed_steps"] = runner.steps - steps_before
+        points["mixed_preemptions"] = sum(r.preemptions for r in results)
+        points["mixed_tokens_per_s"] = (sum(lengths) + points["mixed_generated_tokens"]) / seconds
+        points["mixed_generated_per_s"] = points["mixed_generated_tokens"] / seconds
+
     return {
         "metric": metric_name(args, chosen),
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_per_step,
@@ -368,7 +393,7 @@ def main() -> int:
     parser.add_argument("--prefill-samples", type=int, default=5)
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
     parser.add_argument("--reference-points", action="store_true", help="with --impl reference: also time batch 1 and 64 (minutes)")
-    parser.add_argument("--sections", default="decode,e2e,prefill,points", help="which measurements to take (all by default; fewer for profiling runs)")
+    parser.add_argument("--sections", default="decode,e2e,prefill,points", help="which measurements to take (fewer for profiling runs; `mixed` adds requests of mixed length through the scheduler)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine is single-GPU by design (asked for {args.gpus})")

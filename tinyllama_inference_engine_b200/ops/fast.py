@@ -453,16 +453,27 @@ ATTENTION_TILE_ROWS = 64       # rows of one work item of the mma.sync prompt ke
 ATTENTION_TC_TILE_ROWS = 128   # rows of one work item of the tensor-memory kernel (csrc/attention_prefill_tc.cu)
 
 
-def attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int]) -> list[int]:
+def leading_single_rows(q_lens: list[int]) -> int:
+    """How many entries at the head of a step bring one token each (the scheduler puts the decoding requests first).  In a step
+    that also carries prompt portions these rows go to the decode kernel (split keys, a CTA per part) and the work lists of the
+    prompt kernels leave them out: as 1-row tiles of a prompt kernel each of them cost a whole tile's pass over its keys, and
+    enough of them took the step off the tensor-memory kernel altogether."""
+    lead = 0
+    while lead < len(q_lens) and q_lens[lead] == 1:
+        lead += 1
+    return lead if lead < len(q_lens) else 0
+
+
+def attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int], first_entry: int = 0, end_entry: int | None = None) -> list[int]:
     """Work items of the mma.sync prompt kernel: (entry, first row) of every run of up to ATTENTION_TILE_ROWS rows of one entry."""
     tiles: list[int] = []
-    for index, count in enumerate(q_lens):
-        for offset in range(0, count, ATTENTION_TILE_ROWS):
+    for index in range(first_entry, len(q_lens) if end_entry is None else end_entry):
+        for offset in range(0, q_lens[index], ATTENTION_TILE_ROWS):
             tiles += [index, seq_starts[index] + offset]
     return tiles
 
 
-def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int]) -> list[int]:
+def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int], first_entry: int = 0) -> list[int]:
     """Work items of the tensor-memory attention kernel: (entry, first row, entry or -1, first row) per item.
 
     A run of ATTENTION_TC_TILE_ROWS rows late in a long request sees many keys, an early one few.  Pairing the heaviest
@@ -470,7 +481,8 @@ def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_st
     number of key tiles, so the grid finishes together instead of waiting for the last heavy tiles.
     """
     singles = []
-    for index, count in enumerate(q_lens):
+    for index in range(first_entry, len(q_lens)):
+        count = q_lens[index]
         for offset in range(0, count, ATTENTION_TC_TILE_ROWS):
             rows = min(ATTENTION_TC_TILE_ROWS, count - offset)
             work = -(-(first_positions[index] + offset + rows) // 64)
@@ -491,12 +503,17 @@ def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_st
 
 
 def _register_step_plans() -> None:
-    """The prompt-attention kernels' work lists travel with every step that is not pure decoding (engine.batch.register_step_plan)."""
+    """The prompt-attention kernels' work lists travel with every step that is not pure decoding (engine.batch.register_step_plan).
+
+    They leave out the decoding requests at the head of the step (``leading_single_rows``); ``attention_tiles_lead`` holds those as
+    1-row tiles, for shapes the decode kernel does not take."""
     from ..engine.batch import StepPlan, register_step_plan
 
     not_decode = lambda q_lens: max(q_lens) > 1  # noqa: E731
-    register_step_plan(StepPlan("attention_tiles", 2, attention_tiles, not_decode), replace=True)
-    register_step_plan(StepPlan("attention_tiles_tc", 4, paired_attention_tiles, not_decode), replace=True)
+    register_step_plan(StepPlan("attention_tiles", 2, lambda q, f, s: attention_tiles(q, f, s, leading_single_rows(q)), not_decode), replace=True)
+    register_step_plan(StepPlan("attention_tiles_tc", 4, lambda q, f, s: paired_attention_tiles(q, f, s, leading_single_rows(q)), not_decode), replace=True)
+    register_step_plan(StepPlan("attention_tiles_lead", 2, lambda q, f, s: attention_tiles(q, f, s, 0, leading_single_rows(q)),
+                                lambda q_lens: max(q_lens) > 1 and leading_single_rows(q_lens) > 0), replace=True)
 
 
 _register_step_plans()
@@ -548,13 +565,23 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
         splits = decode_splits(batch.num_seqs, kv_heads, batch.max_seq_len)
         decode_attention(qkv, pages, positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale, splits)
         return True
+    if head_dim > 128:
+        return False
+    lead = leading_single_rows(batch.host_q_lens)
+    if lead:   # decoding requests at the head of a step that also carries prompt portions: rows 0 .. lead - 1, one per entry
+        if q_heads // kv_heads <= 16:
+            decode_attention(qkv[:lead], pages, positions[:lead], block_table[:lead], out[:lead], q_heads, kv_heads, head_dim, page_size, window, scale,
+                             decode_splits(lead, kv_heads, batch.max_seq_len))
+        else:
+            prefill_attention(qkv, pages, batch.plan("attention_tiles_lead"), batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads,
+                              head_dim, page_size, window, scale)
     tc_tiles = batch.plan("attention_tiles_tc")
     if (use_tc_attention and tc_tiles is not None and head_dim in TC_ATTENTION_HEAD_DIMS and page_size % 64 == 0 and pages.is_contiguous()
-            and batch.num_tokens >= TC_ATTENTION_MIN_ROWS_PER_TILE * 2 * tc_tiles.shape[0]):
+            and batch.num_tokens - lead >= TC_ATTENTION_MIN_ROWS_PER_TILE * 2 * tc_tiles.shape[0]):
         prefill_attention_tc(qkv, pages, tc_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale)
         return True
     tiles = batch.plan("attention_tiles")
-    if tiles is not None and head_dim <= 128:
+    if tiles is not None:
         prefill_attention(qkv, pages, tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads,
                           head_dim, page_size, window, scale)
         return True
