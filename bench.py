@@ -393,7 +393,7 @@ def main() -> int:
     parser.add_argument("--prefill-samples", type=int, default=5)
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
     parser.add_argument("--reference-points", action="store_true", help="with --impl reference: also time batch 1 and 64 (minutes)")
-    parser.add_argument("--sections", default="decode,e2e,prefill,points", help="which measurements to take (fewer for profiling runs; `mixed` adds requests of mixed length through the scheduler)")
+    parser.add_argument("--sections", default="decode,e2e,prefill,points,mixed", help="which measurements to take (fewer for profiling runs; `mixed` adds requests of mixed length through the scheduler)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine is single-GPU by design (asked for {args.gpus})")
