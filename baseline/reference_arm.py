@@ -46,7 +46,7 @@ def ensure_sources() -> None:
     """``baseline/_ref`` holds the reference's tree; fill it from a checkout if it is empty and one is at hand."""
     if all((REF / s).exists() for s in SOURCES):
         return
-    origin = Path(os.environ.get("TLIE_REFERENCE_SOURCE", "/root/reference"))
+    origin = Path(os.environ.get("TLIE_REFERENCE_SOURCE", str(HERE.parent.parent / "reference")))   # a checkout beside this repository
     if not (origin / "src" / "cuda" / "model.cu").exists():
         raise Unavailable(f"no copy of the reference's sources under {REF} and none at {origin}")
     REF.mkdir(parents=True, exist_ok=True)

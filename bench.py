@@ -227,7 +227,7 @@ def run_engine(args) -> dict:
     sections = set(args.sections.split(","))
     largest = max(64 if "points" in sections else 1, args.batch)
     cache_tokens = largest * (prompt_tokens + 64 * (-(-generated // 64)) + 64)
-    # Requests of mixed length for the scheduler (SURVEY's 7B workload: prompts uniform between 64 tokens and the context, cut into
+    # Requests of mixed length for the scheduler (prompts uniform between 64 tokens and the context, cut into
     # portions under the token budget and interleaved with the other requests' decode steps); all of them fit the cache at once.
     mixed_count, mixed_out = 32, 64
     mixed_lengths = [int(n) for n in rng.integers(64, min(4096, shapes["max_position_embeddings"] - mixed_out - 1) + 1, size=mixed_count)]
