@@ -127,7 +127,7 @@ def test_block_lets_a_part_add_to_the_residual_in_steps_of_many_rows(monkeypatch
     """The block's choice, with stand-in parts: few rows -> norm and add go into the part's kernels (lazy norm, accumulate_into);
     many rows -> a materialised norm, and accumulate_into only if the part says it can add for that many rows."""
     from tinyllama_inference_engine_b200 import ops
-    from tinyllama_inference_engine_b200.parts.block import PreNormResidualBlock
+    from tinyllama_inference_engine_b200.parts import norm_then_part
 
     monkeypatch.setattr(ops, "fused_rows_limit", lambda dtype, device: 16)
     calls = []
@@ -155,13 +155,13 @@ def test_block_lets_a_part_add_to_the_residual_in_steps_of_many_rows(monkeypatch
             return None if accumulate_into is not None else "out"
 
     few, many = torch.zeros(8, 4), torch.zeros(200, 4)
-    assert PreNormResidualBlock._run(Norm(), Part(False), few, None, True, None) is None
+    assert norm_then_part(Norm(), Part(False), few, None, True, None) is None
     assert calls == [("norm", False, True), ("part", "lazy", True)]
     calls.clear()
-    assert PreNormResidualBlock._run(Norm(), Part(False), many, "pending", False, None) == "out"
+    assert norm_then_part(Norm(), Part(False), many, "pending", False, None) == "out"
     assert calls == [("norm", True, False), ("part", "normed", False)]
     calls.clear()
-    assert PreNormResidualBlock._run(Norm(), Part(True), many, "pending", False, None) is None
+    assert norm_then_part(Norm(), Part(True), many, "pending", False, None) is None
     assert calls == [("norm", True, False), ("part", "normed", True)]
 
 

@@ -19,8 +19,8 @@ from tinyllama_inference_engine_b200 import EngineConfig
 from tinyllama_inference_engine_b200.config import Architecture, register_architecture, unregister_architecture
 from tinyllama_inference_engine_b200.engine.batch import StepEntry
 from tinyllama_inference_engine_b200.engine.runner import ModelRunner
-from tinyllama_inference_engine_b200.parts import (CacheNeed, FeedForward, LayerSpec, Mixer, ModelSpec, OrderEntry, PartSpec, PositionEncoding, TensorSpec,
-                                                   register_part, unregister_part)
+from tinyllama_inference_engine_b200.parts import (Block, CacheNeed, FeedForward, LayerSpec, Mixer, ModelSpec, OrderEntry, PartSpec, PositionEncoding, TensorSpec,
+                                                   build_part, norm_then_part, part_class, register_part, unregister_part)
 from tinyllama_inference_engine_b200.weights import write_random_model
 
 
@@ -238,3 +238,121 @@ def test_a_part_with_state_that_vouches_for_itself_runs_in_the_graphs(toy_folder
     graphed, vouched, captured = run(DeviceDecayMixer, True)
     assert vouched and captured[0] >= 1 and captured[1] >= 1
     assert graphed == plain
+
+
+# --- a block kind of its own ----------------------------------------------------------------------------------------------
+class TwoFeedForwardBlock(Block):
+    """x + mixer(n1 x), then x + ff(n2 x), then x + ff2(n3 x): an arrangement the framework does not have, made of its parts.
+    ``norm_then_part`` gives it what the framework's own block gets from the small-step kernels (norm inside the first product,
+    residual add and the next norm's input inside the last) without the block knowing any of it."""
+
+    capturable = True
+    accepts_next_norm = True
+    _SLOTS = (("n1", "norm"), ("mix", "mixer"), ("n2", "norm"), ("ff", "feed_forward"), ("n3", "norm"), ("ff2", "feed_forward"))
+
+    @classmethod
+    def tensor_specs(cls, spec, prefix):
+        specs = []
+        for slot, category in cls._SLOTS:
+            specs += part_class(category, spec[slot]).tensor_specs(spec[slot], f"{prefix}.{slot}")
+        return specs
+
+    @classmethod
+    def cache_need(cls, spec):
+        return part_class("mixer", spec["mix"]).cache_need(spec["mix"])
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        for slot, category in self._SLOTS:
+            setattr(self, slot, build_part(category, spec[slot], f"{prefix}.{slot}", weights, runtime))
+
+    @property
+    def first_norm(self):
+        return self.n1
+
+    def forward(self, residual, pending, ctx, cache, next_norm=None):
+        from tinyllama_inference_engine_b200 import ops
+
+        fused = residual.shape[0] <= ops.fused_rows_limit(self.runtime.dtype, residual.device)
+        pending = norm_then_part(self.n1, self.mix, residual, pending, fused, self.n2, ctx, cache)
+        pending = norm_then_part(self.n2, self.ff, residual, pending, fused, self.n3, ctx)
+        pending = norm_then_part(self.n3, self.ff2, residual, pending, fused, next_norm, ctx)
+        return residual, pending
+
+
+@dataclass(frozen=True)
+class TwoFFConfig:
+    hidden_size: int = 128
+    vocab_size: int = 211
+    first_intermediate: int = 96
+    second_intermediate: int = 160
+    num_layers: int = 2
+    max_position_embeddings: int = 128
+    architectures: tuple = ("ToyTwoFFForCausalLM",)
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: (tuple(v) if k == "architectures" else v) for k, v in data.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return {**asdict(self), "architectures": list(self.architectures)}
+
+
+def build_two_ff_spec(c: TwoFFConfig) -> ModelSpec:
+    norm = PartSpec("rmsnorm", {"size": c.hidden_size, "eps": 1e-5})
+    attention = PartSpec("attention", {"hidden_size": c.hidden_size, "num_heads": 4, "num_kv_heads": 2, "head_dim": 32, "window": 0, "scale": None,
+                                       "position": PartSpec("rotary", {"rotary_dim": 32, "theta": 500.0})})
+    mlp = lambda inter: PartSpec("gated_mlp", {"hidden_size": c.hidden_size, "intermediate_size": inter, "activation": "silu"})  # noqa: E731
+    block = PartSpec("toy_two_ff", {"n1": norm, "mix": attention, "n2": norm, "ff": mlp(c.first_intermediate), "n3": norm, "ff2": mlp(c.second_intermediate)})
+    layers = tuple(LayerSpec(f"t.l{i}", block) for i in range(c.num_layers))
+    return ModelSpec("ToyTwoFFForCausalLM", c.hidden_size, c.vocab_size, c.max_position_embeddings,
+                     PartSpec("token_embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size, "name": "t.embed"}),
+                     layers, tuple(OrderEntry(i, cache=i) for i in range(c.num_layers)), PartSpec("rmsnorm", {"size": c.hidden_size, "eps": 1e-5, "name": "t.norm"}),
+                     PartSpec("linear_head", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size, "name": "t.head", "tied_to": None}))
+
+
+def _plain_two_ff(folder, tokens):
+    """The same arrangement from the plain functions (whole sequence, no cache)."""
+    import plain_llama
+
+    w = plain_llama.read_safetensors(folder / "model.safetensors")
+    c = TwoFFConfig()
+    n = len(tokens)
+    positions = torch.arange(n)
+    x = w["t.embed.weight"].float()[torch.tensor(tokens)]
+    for i in range(c.num_layers):
+        p = f"t.l{i}"
+        h = plain_llama.rms_norm(x, w[f"{p}.n1.weight"].float(), 1e-5)
+        q = plain_llama.rope(plain_llama.linear(w[f"{p}.mix.q_proj.weight"].float(), h).view(n, 4, 32), positions, 500.0)
+        k = plain_llama.rope(plain_llama.linear(w[f"{p}.mix.k_proj.weight"].float(), h).view(n, 2, 32), positions, 500.0)
+        v = plain_llama.linear(w[f"{p}.mix.v_proj.weight"].float(), h).view(n, 2, 32)
+        x = x + plain_llama.linear(w[f"{p}.mix.o_proj.weight"].float(), plain_llama.attention(q, k, v).reshape(n, 128))
+        for norm, ff in (("n2", "ff"), ("n3", "ff2")):
+            h = plain_llama.rms_norm(x, w[f"{p}.{norm}.weight"].float(), 1e-5)
+            gated = plain_llama.silu_multiply(plain_llama.linear(w[f"{p}.{ff}.gate_proj.weight"].float(), h), plain_llama.linear(w[f"{p}.{ff}.up_proj.weight"].float(), h))
+            x = x + plain_llama.linear(w[f"{p}.{ff}.down_proj.weight"].float(), gated)
+    return plain_llama.linear(w["t.head.weight"].float(), plain_llama.rms_norm(x, w["t.norm.weight"].float(), 1e-5))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,fraction", [("float32", 2e-5), ("bfloat16", 2.5e-2)])
+def test_a_block_kind_of_its_own_is_registered_and_gets_the_small_step_kernels(tmp_path, dtype, fraction):
+    register_part("block", "toy_two_ff", TwoFeedForwardBlock, replace=True)
+    register_architecture(Architecture("ToyTwoFFForCausalLM", TwoFFConfig, build_two_ff_spec), replace=True)
+    try:
+        folder = write_random_model(tmp_path / "two_ff", TwoFFConfig(), seed=11, storage_dtype="bfloat16")
+        rng = np.random.default_rng(3)
+        tokens = [int(t) for t in rng.integers(0, 211, size=70)]
+        want = _plain_two_ff(folder, tokens)
+        atol = fraction * float(want.abs().max())
+        runner = ModelRunner(folder, EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=256, max_requests=2, max_batch_tokens=64))
+        assert runner.model.capturable
+        got = [runner.step([StepEntry("r", tokens[:40], list(range(40)))]).cpu()]             # a prompt portion: the many-row kernels
+        got.append(runner.step([StepEntry("r", tokens[40:55], list(range(15)))]).cpu())       # 15 rows: the fused small-step kernels
+        for i in range(55, 70):                                                              # decoded one by one: prepared norms from product to product
+            got.append(runner.step([StepEntry("r", [tokens[i]], [0])]).cpu())
+        worst = float((torch.cat(got) - want).abs().max())
+        assert worst <= atol, (worst, atol)
+    finally:
+        unregister_architecture("ToyTwoFFForCausalLM")
+        unregister_part("block", "toy_two_ff")

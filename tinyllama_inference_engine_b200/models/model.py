@@ -64,7 +64,7 @@ class DecoderModel:
             block = self.blocks[entry.layer]
             if block.accepts_next_norm:
                 # the norm that reads this block's result: the next block's first one (if it names one), or the final norm
-                following = getattr(self.blocks[order[index + 1].layer], "mixer_norm", None) if index + 1 < len(order) else self.final_norm
+                following = self.blocks[order[index + 1].layer].first_norm if index + 1 < len(order) else self.final_norm
                 residual, pending = block.forward(residual, pending, ctx, cache, next_norm=following)
             else:
                 if isinstance(pending, ops.LazyNorm):

@@ -11,6 +11,7 @@ from .base import (
     Runtime,
     Workspace,
     build_part,
+    norm_then_part,
     part_class,
     register_part,
     unregister_part,
@@ -19,6 +20,6 @@ from .spec import LayerSpec, ModelSpec, OrderEntry, PartSpec, TensorSpec
 
 __all__ = [
     "Block", "CacheNeed", "FeedForward", "LayerCache", "LayerSpec", "Mixer", "ModelSpec", "Norm", "OrderEntry",
-    "Part", "PartSpec", "PositionEncoding", "Runtime", "TensorSpec", "Workspace", "build_part", "part_class",
+    "Part", "PartSpec", "PositionEncoding", "Runtime", "TensorSpec", "Workspace", "build_part", "norm_then_part", "part_class",
     "register_part", "unregister_part",
 ]

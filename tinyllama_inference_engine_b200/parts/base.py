@@ -194,6 +194,7 @@ class FeedForward(Part):
 class Block(Part):
     category = "block"
     accepts_next_norm = False      # forward(..., next_norm=<Norm>) : the norm that will read this block's result, if known
+    first_norm = None              # the norm that reads this block's input first, if it has one: what the block before is told as ``next_norm``
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
@@ -201,6 +202,42 @@ class Block(Part):
 
     def forward(self, residual, delta, ctx, cache: LayerCache):
         raise NotImplementedError
+
+
+def norm_then_part(norm, part, residual, pending, fused: bool, next_norm, *args):
+    """``part(norm(residual + pending))`` for a block of any kind, with what the small-step kernels can take over taken over.
+
+    A block that arranges its parts differently (two parts from one norm, a norm after the part, ...) calls this once per
+    (norm, part) pair and gets the decode fusions without knowing them: with few rows (``fused``: ``rows <=
+    ops.fused_rows_limit(...)``) a part that ``accepts_lazy_norm`` applies the norm inside its first product, one that
+    ``fuses_residual_add`` adds its output into ``residual`` itself, and one that ``prepares_next_norm`` leaves the input of
+    ``next_norm`` (the norm that will read the residual next, or None) ready.  A part that declares none of this is handed the
+    normalised tensor and its output is returned.
+
+    ``pending``: None, an output not yet added to the residual, or an ``ops.LazyNorm`` that the product before left prepared
+    (the residual is complete then).  ``args``: what the part's ``forward`` takes after ``x`` (``ctx``, and ``cache`` for a mixer).
+    Returns what is pending after the part: None (the residual is complete), the part's output, or the prepared lazy norm."""
+    from .. import ops
+
+    lazily = fused and part.accepts_lazy_norm and norm.supports_lazy   # a norm that says nothing of laziness is never asked for it
+    if isinstance(pending, ops.LazyNorm):
+        if lazily and pending.weight is norm.weight and pending.eps == norm.eps:
+            x = pending
+        else:
+            x = norm.forward(residual, None, lazy=True) if lazily else norm.forward(residual, None)
+    elif lazily:
+        x = norm.forward(residual, pending, lazy=True)
+    else:
+        x = norm.forward(residual, pending)
+    if not fused and part.fuses_residual_add and part.adds_to_residual(residual.shape[0]):
+        return part.forward(x, *args, accumulate_into=residual)   # many rows: the add happens in the last product's epilogue
+    if fused and part.fuses_residual_add:
+        if part.prepares_next_norm and next_norm is not None and next_norm.supports_lazy:
+            following = next_norm.forward(residual, None, lazy=True)   # of the residual as it will be when the part is done
+            part.forward(x, *args, accumulate_into=residual, prepare=following)
+            return following
+        return part.forward(x, *args, accumulate_into=residual)
+    return part.forward(x, *args)
 
 
 # --- registry of part classes -------------------------------------------------------------

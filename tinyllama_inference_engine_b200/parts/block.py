@@ -1,7 +1,7 @@
 """How the parts of one layer are arranged."""
 from __future__ import annotations
 
-from .base import Block, CacheNeed, LayerCache, build_part, part_class, register_part
+from .base import Block, CacheNeed, LayerCache, build_part, norm_then_part, part_class, register_part
 from .spec import PartSpec, TensorSpec
 
 
@@ -19,6 +19,7 @@ class PreNormResidualBlock(Block):
     _SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"))
 
     capturable = True
+
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
         specs: list[TensorSpec] = []
@@ -38,38 +39,17 @@ class PreNormResidualBlock(Block):
 
     accepts_next_norm = True
 
+    @property
+    def first_norm(self):
+        return self.mixer_norm
+
     def forward(self, residual, pending, ctx, cache: LayerCache, next_norm=None):
         from .. import ops
 
         fused = residual.shape[0] <= ops.fused_rows_limit(self.runtime.dtype, residual.device)
-        pending = self._run(self.mixer_norm, self.mixer, residual, pending, fused, self.feed_forward_norm, ctx, cache)
-        pending = self._run(self.feed_forward_norm, self.feed_forward, residual, pending, fused, next_norm, ctx)
+        pending = norm_then_part(self.mixer_norm, self.mixer, residual, pending, fused, self.feed_forward_norm, ctx, cache)
+        pending = norm_then_part(self.feed_forward_norm, self.feed_forward, residual, pending, fused, next_norm, ctx)
         return residual, pending
-
-    @staticmethod
-    def _run(norm, part, residual, pending, fused, next_norm, *args):
-        """norm -> part, letting the part take the norm and the residual add into its kernels where it can (few rows).
-
-        ``pending``: None, the output not yet added to the residual, or a lazy norm that the product before left prepared
-        (the residual is complete then).  Returns what is pending after the part."""
-        from .. import ops
-
-        if isinstance(pending, ops.LazyNorm):
-            usable = fused and part.accepts_lazy_norm and pending.weight is norm.weight and pending.eps == norm.eps
-            x = pending if usable else norm.forward(residual, None, lazy=fused and part.accepts_lazy_norm and norm.supports_lazy)
-        elif fused and part.accepts_lazy_norm and norm.supports_lazy:
-            x = norm.forward(residual, pending, lazy=True)
-        else:
-            x = norm.forward(residual, pending)
-        if not fused and part.fuses_residual_add and part.adds_to_residual(residual.shape[0]):
-            return part.forward(x, *args, accumulate_into=residual)   # many rows: the add happens in the last product's epilogue
-        if fused and part.fuses_residual_add:
-            if part.prepares_next_norm and next_norm is not None and next_norm.supports_lazy:
-                following = next_norm.forward(residual, None, lazy=True)   # of the residual as it will be when the part is done
-                part.forward(x, *args, accumulate_into=residual, prepare=following)
-                return following
-            return part.forward(x, *args, accumulate_into=residual)
-        return part.forward(x, *args)
 
 
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
