@@ -200,8 +200,11 @@ __global__ void __launch_bounds__(kThreadsTC, 2)
 
   // A work item is a pair of row tiles (the second may be absent): the host pairs a tile that sees many keys with one
   // that sees few, so that all CTAs carry about the same work and the grid ends together.
-  const int* item = tiles + (size_t)blockIdx.x * 4;
-  const int head = blockIdx.y;
+  // The heads of a work item are neighbours in the order CTAs are handed out (x runs fastest), and the items come heaviest first:
+  // with more CTAs than the SMs hold at once, every slot that comes free takes the heaviest work left, and the CTAs that run
+  // together read the same keys and values (the heads of a group) out of L2.
+  const int* item = tiles + (size_t)blockIdx.y * 4;
+  const int head = blockIdx.x;
   const int kvh = head / (q_heads / kv_heads);
   // S0 [0,64), S1 [64,128), O of the first row tile [128, 128 + D), of the second [128 + D, 128 + 2 D)
   // (head size 128: both row tiles use [128, 256), one after the other)
@@ -597,7 +600,7 @@ static int launch_attention_tc(const void* q, int q_row_stride, int tokens, cons
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid(n_tiles, q_heads);
+  dim3 grid(q_heads, n_tiles);
   return (int)launch_pdl(prefill_attention_tc_kernel<kD>, grid, dim3(kThreadsTC), (size_t)smem, stream, map_q, map_kv, tiles, seq_starts, first_positions,
                          block_table, table_stride, (__nv_bfloat16*)out, q_heads, kv_heads, page_size, window, scale, error_flag);
 }
@@ -610,7 +613,7 @@ TLIE_EXPORT int tlie_prefill_attention_tc(const void* q, int q_row_stride, int t
                                           int table_stride, void* out, int q_heads, int kv_heads, int head_dim, int page_size, int window, float scale,
                                           int* error_flag, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads > 65535 || page_size % kKeysTC != 0 || q_row_stride % 8 != 0 || error_flag == nullptr ||
+  if (kv_heads <= 0 || q_heads % kv_heads != 0 || n_tiles > 65535 || page_size % kKeysTC != 0 || q_row_stride % 8 != 0 || error_flag == nullptr ||
       (head_dim != 64 && head_dim != 128))
     return (int)cudaErrorInvalidValue;
   if (head_dim == 64)
