@@ -223,22 +223,40 @@ TLIE_EXPORT float tlie_uniform_from(long long seed, long long counter) {
 
 // After a decode step: the sampled tokens become the next step's inputs and every request
 // moves one position on.  Lets a run of decode steps stay on the device.
+// `mailbox` (optional): pinned host memory of count + 2 words, written by this kernel over the bus: the sampled tokens, the device
+// error word, and last (after a system-wide fence) the number of the step, which the host polls instead of asking the stream.
+// One block: the block barrier orders every token's store before the number's.
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
                                       int* __restrict__ positions, int* __restrict__ seq_lens,
-                                      int* __restrict__ first_positions, long long* __restrict__ counters, int count) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= count) return;
-  token_ids[i] = sampled[i];
-  positions[i] += 1;
-  seq_lens[i] += 1;
-  first_positions[i] += 1;
-  counters[i] += 1;
+                                      int* __restrict__ first_positions, long long* __restrict__ counters, int count,
+                                      volatile int* mailbox, const int* __restrict__ error_word, int* __restrict__ steps_done) {
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    const int token = sampled[i];
+    token_ids[i] = token;
+    positions[i] += 1;
+    seq_lens[i] += 1;
+    first_positions[i] += 1;
+    counters[i] += 1;
+    if (mailbox != nullptr) mailbox[i] = token;
+  }
+  if (mailbox == nullptr) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mailbox[count] = error_word != nullptr ? *error_word : 0;
+    const int number = *steps_done + 1;
+    *steps_done = number;
+    __threadfence_system();
+    mailbox[count + 1] = number;
+  }
 }
 
+// mailbox: null, or pinned host memory of count + 2 int32 (then steps_done: a device int32 that counts the steps; error_word may be null).
 TLIE_EXPORT int tlie_decode_advance(int* token_ids, const int* sampled, int* positions, int* seq_lens,
-                                    int* first_positions, long long* counters, int count, cudaStream_t stream) {
+                                    int* first_positions, long long* counters, int count, int* mailbox, const int* error_word,
+                                    int* steps_done, cudaStream_t stream) {
   if (count <= 0) return 0;
-  decode_advance_kernel<<<(count + 127) / 128, 128, 0, stream>>>(token_ids, sampled, positions, seq_lens,
-                                                                  first_positions, counters, count);
+  if (mailbox != nullptr && steps_done == nullptr) return (int)cudaErrorInvalidValue;
+  decode_advance_kernel<<<1, count <= 128 ? 128 : 256, 0, stream>>>(token_ids, sampled, positions, seq_lens, first_positions, counters, count, mailbox,
+                                                                    error_word, steps_done);
   return (int)cudaGetLastError();
 }

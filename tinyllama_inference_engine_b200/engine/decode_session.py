@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..errors import BatchError
+from ..errors import BatchError, KernelError
 from .batch import decode_context, decode_layout
 
 # A session runs its first steps kernel by kernel and is captured as a graph only when it is still in use after them:
@@ -24,8 +24,9 @@ EAGER_STEPS_BEFORE_CAPTURE = 2
 
 
 class DecodeSession:
-    def __init__(self, runner, count: int, use_graph: bool = True):
+    def __init__(self, runner, count: int, use_graph: bool = True, publish: bool = True):
         self.runner = runner
+        self.publish = publish   # False: steps that stay on the device (nothing is written to host memory; read_tokens() copies)
         self.cache = runner.cache
         self.request_ids: list = []
         self.count = count
@@ -41,8 +42,14 @@ class DecodeSession:
         view = lambda buffer, i: buffer[offsets[i] : offsets[i + 1]]  # noqa: E731
         self.h_tokens, self.h_positions = view(self._host, 0), view(self._host, 1)
         self._np = self._host.numpy()                       # the same pinned memory, for cheap host writes
-        self._sampled_host = torch.zeros(count, dtype=torch.int32).pin_memory()
-        self._error_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._d_tokens = self._device[:count]               # where the step's input ids lie on the device
+        # The step's result also arrives by itself: the last kernel of a step writes the tokens, the device error word and the
+        # step's number into this pinned memory over the bus, and read_tokens() polls the number instead of waiting for two
+        # copies and the stream (some 25 us of every step with the host in the loop).
+        self._mailbox = torch.zeros(count + 2, dtype=torch.int32).pin_memory()
+        self._mail = self._mailbox.numpy()
+        self._steps_done = torch.zeros(1, dtype=torch.int32, device=device)
+        self._steps_issued = 0
         self._error_word = ops.error_flag(device)            # what kernels of this device report without a host in the loop
         self._capacity = [0] * count                        # tokens each request's pages hold (least over the groups)
         self.h_tables = [view(self._host, 8 + g).view(count, width) for g in range(groups)]
@@ -122,20 +129,41 @@ class DecodeSession:
         self.logits = self.runner.model.forward(self.ctx, caches)
         ops.sample(self.logits, self.temperature, self.top_p, self.seeds, self.counters, self.sampled)
         c = self.ctx
-        ops.decode_advance(c.token_ids, self.sampled, c.positions, c.seq_lens, c.first_positions, self.counters)
+        if self.publish:
+            ops.decode_advance(c.token_ids, self.sampled, c.positions, c.seq_lens, c.first_positions, self.counters, self._mailbox, self._steps_done)
+        else:
+            ops.decode_advance(c.token_ids, self.sampled, c.positions, c.seq_lens, c.first_positions, self.counters)
 
     def set_tokens(self, tokens: list[int]) -> None:
         """Host tokens in: the step's input ids come from pinned host memory."""
         self._np[: self.count] = tokens
-        self._device[: self.count].copy_(self.h_tokens, non_blocking=True)
+        self._d_tokens.copy_(self.h_tokens, non_blocking=True)
+
+    def next_step_fits_its_pages(self) -> bool:
+        """Whether every request's next position lies in a page it already holds (then the next step reserves nothing)."""
+        capacity = self._capacity
+        for i, position in enumerate(self.positions):
+            if position >= capacity[i]:
+                return False
+        return not self._fresh
 
     def read_tokens(self) -> list[int]:
-        """Host tokens out: the tokens the last step sampled, through pinned host memory."""
-        self._sampled_host.copy_(self.sampled, non_blocking=True)
-        self._error_host.copy_(self._error_word, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        ops.raise_for_error_word(int(self._error_host[0]), self._error_word.device)
-        return self._sampled_host.tolist()
+        """Host tokens out: the tokens the last step sampled, as its last kernel wrote them into pinned host memory."""
+        if not self.publish:
+            tokens = self.sampled.cpu()
+            ops.check_device_errors(self.sampled.device)
+            return tokens.tolist()
+        mail, last, wanted = self._mail, self.count + 1, self._steps_issued
+        stream = torch.cuda.current_stream()
+        polls = 0
+        while mail[last] != wanted:
+            polls += 1
+            if polls % 4096 == 0 and stream.query() and mail[last] != wanted:
+                # the stream has nothing left to run and the number never came: a kernel of the step failed
+                stream.synchronize()
+                raise KernelError("a decode step ended without publishing its result")
+        ops.raise_for_error_word(int(mail[self.count]), self._error_word.device)
+        return mail[: self.count].tolist()
 
     def step(self) -> torch.Tensor:
         """One decode step for every request; returns the sampled tokens (device, int32).
@@ -176,6 +204,7 @@ class DecodeSession:
             self.graph.replay()
         else:
             self.graph.replay()
+        self._steps_issued += 1
         advance = self.cache.advance
         for i, request_id in enumerate(self.request_ids):
             self.positions[i] += 1

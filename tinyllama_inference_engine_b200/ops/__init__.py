@@ -356,11 +356,20 @@ def sample(logits, temperature, top_p, seeds, counters, out) -> None:
     )
 
 
-def decode_advance(token_ids, sampled, positions, seq_lens, first_positions, counters) -> None:
-    """token_ids = sampled; positions, seq_lens, first_positions and counters move on by one."""
+def decode_advance(token_ids, sampled, positions, seq_lens, first_positions, counters, mailbox=None, steps_done=None) -> None:
+    """token_ids = sampled; positions, seq_lens, first_positions and counters move on by one.
+
+    ``mailbox``: a pinned host int32 tensor of ``count + 2`` words that the kernel writes over the bus (the tokens, the device error
+    word, then the number of the step from the device counter ``steps_done``), so that the host can poll for the step's result."""
+    count = token_ids.shape[0]
+    box, flag, done = c_void_p(0), c_void_p(0), c_void_p(0)
+    if mailbox is not None:
+        if mailbox.dtype != torch.int32 or not mailbox.is_pinned() or mailbox.numel() < count + 2 or steps_done is None or steps_done.dtype != torch.int32:
+            raise KernelError("decode_advance: the mailbox is pinned host int32 of count + 2 words, with a device int32 step counter", code="invalid_shape")
+        box, flag, done = c_void_p(mailbox.data_ptr()), _ptr(error_flag(token_ids.device)), _ptr(steps_done)
     _check(
         core().tlie_decode_advance(_i32(token_ids, "token_ids"), _i32(sampled, "sampled"), _i32(positions, "positions"), _i32(seq_lens, "seq_lens"),
-                                   _i32(first_positions, "first_positions"), _ptr(counters), c_int(token_ids.shape[0]), _stream()),
+                                   _i32(first_positions, "first_positions"), _ptr(counters), c_int(count), box, flag, done, _stream()),
         "decode_advance",
     )
 
