@@ -125,6 +125,9 @@ class DecodeSession:
 
     # --- stepping ----------------------------------------------------------------------------
     def _body(self) -> None:
+        if self.publish:
+            # host in the loop: the step's input ids come from pinned host memory, by a copy that is part of the step (of its graph)
+            self._d_tokens.copy_(self.h_tokens, non_blocking=True)
         caches = self.cache.layer_caches(self.d_tables)
         self.logits = self.runner.model.forward(self.ctx, caches)
         ops.sample(self.logits, self.temperature, self.top_p, self.seeds, self.counters, self.sampled)
@@ -137,7 +140,8 @@ class DecodeSession:
     def set_tokens(self, tokens: list[int]) -> None:
         """Host tokens in: the step's input ids come from pinned host memory."""
         self._np[: self.count] = tokens
-        self._d_tokens.copy_(self.h_tokens, non_blocking=True)
+        if not self.publish:
+            self._d_tokens.copy_(self.h_tokens, non_blocking=True)
 
     def next_step_fits_its_pages(self) -> bool:
         """Whether every request's next position lies in a page it already holds (then the next step reserves nothing)."""
