@@ -30,17 +30,19 @@
 // Roles: warp 0 TMA producer, warp 1 issuer of the score products and tensor-memory owner, warp 2 issuer of the P . V products,
 // warp 3 idle, warps 4..7 softmax (128 threads).  The launch gives every thread 128 registers (two CTAs of 256 threads fill the
 // register file); the first four warps hand most of theirs back at once (setmaxnreg) and the softmax warps, whose threads hold a
-// row's 64 scores, take them: 200 each, with nothing spilled.  The two issuers are lone threads that share their schedulers with busy softmax warps, so
-// every instruction of theirs takes its time; one thread issuing both kinds of product had 2,100 of a tile's 2,500 cycles of
+// row's 64 scores, take them: 200 each, with nothing spilled.  The two issuers are lone threads that share their schedulers with
+// busy softmax warps, so every instruction of theirs takes its time; one thread issuing both kinds of product had 2,100 of a tile's 2,500 cycles of
 // work at head size 64 (2,670 of 2,830 at 128) and the softmax threads waited for their scores 930 (1,190) cycles of every tile.
 // Apart, the score issuer runs ahead as far as the two S buffers let it and a P . V product starts as soon as its P is there.
 // Every mbarrier wait is bounded; on a timeout the CTA raises `error_flag`, stops, lets copies land, frees its tensor
 // memory and returns.  Needs page_size % 64 == 0; other shapes use the mma.sync kernel.
-// Two CTAs share an SM, so that one's products run under the other's softmax.  Head size 64: three K / V stages, two P buffers,
-// 97 KB of shared memory and 256 columns of tensor memory (two score buffers, one running output per row tile).  Head size 128
-// is made to fit the same way: two stages, ONE P buffer (a tile's softmax writes it when the product of the tile before has
-// read it) and ONE running output of 128 columns that the second row tile takes over when the first has been read out:
-// 112 KB and 256 columns.  (One CTA per SM with everything doubled ran the 8,192-token prefill of the 8B shapes at 1.41 ms a layer.)
+// Two CTAs share an SM, so that one's products run under the other's softmax.  Head size 64: three K and three V stages, 65 KB of
+// shared memory and 256 columns of tensor memory (two score buffers, whose first halves take P, and one running output per row
+// tile).  Head size 128 is made to fit the same way: two stages and ONE running output of 128 columns that the second row tile
+// takes over when the first has been read out: 96 KB and 256 columns.  (One CTA per SM with everything doubled ran the
+// 8,192-token prefill of the 8B shapes at 1.41 ms a layer.)
+// With more work items than the SMs hold at once the host sends single row tiles, heaviest first (ops.fast.single_attention_tiles),
+// else pairs of a heavy and a light one (paired_attention_tiles); the kernel takes either.
 #include "tcgen05_utils.cuh"
 
 namespace tlie {
