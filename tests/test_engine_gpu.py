@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import plain_llama
+import tiny_configs
 import trace_tools
 from tinyllama_inference_engine_b200 import EngineConfig
 from tinyllama_inference_engine_b200.engine.api import Engine
@@ -128,6 +129,10 @@ def test_command_line_generates_on_the_gpu(model_folders, capsys):
     kernels = json.loads(capsys.readouterr().out)["kernels"]
     assert {"add_rmsnorm", "rope_store", "linear_qkv", "attention_decode_split_kv", "argmax"} <= set(kernels)
     assert all(k["median_us"] > 0 for k in kernels.values())
+    # a model of a config.json with seeded random weights, made on the spot: the same tokens as the folder written beforehand
+    config_file = model_folders["a"] / "config.json"
+    assert main(["generate", "-", text, "8", "--dtype", "float32", "--random-config", str(config_file), "--weights-seed", str(tiny_configs.ALL["a"][1])]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["generated_tokens"] == want
 
 
 def test_steps_launched_ahead_keep_the_engine_consistent(model_folders):

@@ -18,7 +18,9 @@ otherwise a list of token ids separated by commas or spaces; with ``--prompt-len
 stand in for it.  Options, before or after the positionals: ``--dtype bfloat16|float32``,
 ``--temperature``, ``--top-p``, ``--seed``, ``--batch``, ``--max-batch-tokens``,
 ``--page-size``, ``--num-pages`` (cache pages; by default what the request needs),
-``--device`` (a CUDA device; there is no CPU path and ``cpu`` is refused with an error), ``--weights-sha256`` (the digest the
+``--device`` (a CUDA device; there is no CPU path and ``cpu`` is refused with an error), ``--random-config FILE --weights-seed N``
+(the command runs on a model of that config.json with seeded random weights, written to MODEL_DIR, or to a temporary folder
+if MODEL_DIR is ``-``), ``--weights-sha256`` (the digest the
 folder's weights must have, as the reference pins its checkpoints: src/weight_store.cpp:150-190).  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
 (median and 95th percentile), like the reference's benchmarks/kernel_benchmarks.cu:127-325; with ``--probes`` it also measures what the
 kernels' designs rest on (tensor-core time per MMA shape, the cost of a barrier hand-off, a warp's arithmetic rate), with
@@ -291,6 +293,31 @@ _COMMANDS = {"generate": (_generate, (2, 3)), "reference": (_generate, (2, 3)), 
              "benchmark": (_benchmark, (4, 4)), "random-model": (_random_model, (2, 2)), "kernel-bench": (_kernel_bench, (3, 3))}
 
 
+def _random_folder(args):
+    """--random-config FILE: write the model folder (config.json and seeded random weights) the command then runs on.
+    Returns the temporary directory to remove afterwards, if MODEL_DIR was ``-``."""
+    import tempfile
+
+    from .config import architecture_for
+    from .weights import write_random_model
+
+    scratch = None
+    try:
+        data = json.loads(Path(args.random_config).read_text())
+        config = architecture_for(data).config_class.from_dict(data)
+        if args.model_dir == "-":
+            scratch = tempfile.TemporaryDirectory(prefix="tlie_random_model_")
+            args.model_dir = str(Path(scratch.name) / "model")
+        write_random_model(args.model_dir, config, args.weights_seed)
+    except (OSError, json.JSONDecodeError) as exc:
+        print(json.dumps(EngineError(f"unable to read {args.random_config}: {exc}", code="io").to_json()), file=sys.stderr)
+        raise SystemExit(1) from exc
+    except EngineError as exc:
+        print(json.dumps(exc.to_json()), file=sys.stderr)
+        raise SystemExit(1) from exc
+    return scratch
+
+
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(prog="tinyllama_b200", usage=USAGE, add_help=True)
     parser.add_argument("command", choices=sorted(_COMMANDS))
@@ -307,6 +334,9 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--prompt-len", type=int, default=0, help="use this many seeded random token ids as the prompt; the PROMPT argument is then left out")
     parser.add_argument("--prompt-seed", type=int, default=0)
     parser.add_argument("--device", default="cuda:0", help="the CUDA device to run on (there is no CPU path)")
+    parser.add_argument("--random-config", default="", metavar="FILE",
+                        help="run a model of this config.json with seeded random weights; MODEL_DIR is then the folder it is written to, or - for a temporary one")
+    parser.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights of --random-config")
     parser.add_argument("--weights-sha256", default="", help="the SHA-256 the model folder's weights must have; another digest is refused with checksum_mismatch")
     parser.add_argument("--probes", action="store_true", help="kernel-bench: also what an MMA of each shape, a barrier hand-off and a warp's arithmetic cost on this GPU")
     parser.add_argument("--attention-phases", type=int, default=0, metavar="TOKENS",
@@ -316,6 +346,9 @@ def main(argv: list[str] | None = None) -> int:
     except SystemExit as exc:
         return int(exc.code or 0) and 1
     handler, (low, high) = _COMMANDS[args.command]
+    scratch = None
+    if args.random_config and args.command != "random-model":
+        scratch = _random_folder(args)
     if args.prompt_len and args.command in ("generate", "reference", "logits"):
         args.rest.insert(0, "")   # the place of the PROMPT that --prompt-len stands in for
     try:
@@ -325,6 +358,9 @@ def main(argv: list[str] | None = None) -> int:
     except EngineError as exc:
         print(json.dumps(exc.to_json()), file=sys.stderr)
         return 1
+    finally:
+        if scratch is not None:
+            scratch.cleanup()
 
 
 if __name__ == "__main__":
