@@ -94,6 +94,9 @@ TLIE_EXPORT int tlie_decode_attention(const void* q, int q_row_stride, void* pag
   p.q_heads = q_heads;
   p.kv_heads = kv_heads;
   p.page_size = page_size;
+  p.page_shift = -1;
+  for (int shift = 0; shift < 31; ++shift)
+    if ((1 << shift) == page_size) p.page_shift = shift;
   p.window = window;
   p.scale = scale;
   p.splits = splits;

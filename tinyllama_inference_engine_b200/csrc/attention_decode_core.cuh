@@ -34,8 +34,28 @@ constexpr float kLog2e = 1.4426950408889634f;
 // lookups per tile, no division per row.
 __device__ __forceinline__ void load_tile(__nv_bfloat16* k_smem, __nv_bfloat16* v_smem, const __nv_bfloat16* pages,
                                           const int* table, int key0, int lo, int n_keys, int kvh, int kv_heads,
-                                          int page_size, int lane) {
+                                          int page_size, int page_shift, int lane) {
   const size_t plane = (size_t)kv_heads * page_size * kD;
+  // A warp runs a few hundred instructions per tile, and at large batches they, not memory, set the kernel's pace: a tile that
+  // lies wholly inside [lo, n_keys) (all but a request's first and last) takes the short way, with no row asked whether it counts.
+  if (key0 >= lo && key0 + kTileKeys <= n_keys) {
+    const __nv_bfloat16* half_base[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int k = key0 + 16 * h;
+      const int page_index = page_shift >= 0 ? k >> page_shift : k / page_size;   // pages of a power of two: no division
+      half_base[h] = pages + (size_t)table[page_index] * 2 * plane + ((size_t)kvh * page_size + (k - page_index * page_size)) * kD;
+    }
+#pragma unroll
+    for (int idx = lane; idx < kTileKeys * kChunks; idx += 32) {
+      const int row = idx / kChunks;
+      const int chunk = idx - row * kChunks;
+      const __nv_bfloat16* src = (row < 16 ? half_base[0] : half_base[1]) + (row & 15) * kD + chunk * 8;
+      cp_async_16(k_smem + row * kRow + chunk * 8, src, true);
+      cp_async_16(v_smem + row * kRow + chunk * 8, src + plane, true);
+    }
+    return;
+  }
   const __nv_bfloat16* half_base[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -76,6 +96,7 @@ struct DecodeAttnParams {
   float* partial_ml;
   int* tickets;
   int q_heads, kv_heads, page_size, window;
+  int page_shift;   // log2(page_size) if that is a whole number, else -1
   float scale;
   int splits, fuse_rope;
   const float* inv_freq;
@@ -136,7 +157,7 @@ __device__ __forceinline__ void decode_attn_prologue(const DecodeAttnParams& p, 
   for (int s = 0; s < kStages - 1; ++s) {
     if (it.next_load < it.tile_end) {
       __nv_bfloat16* ks = stage_base + (size_t)s * 2 * kTileElems;
-      load_tile(ks, ks + kTileElems, p.pages, it.table, it.next_load * kTileKeys, it.lo, it.n_keys, it.kvh, p.kv_heads, p.page_size, lane);
+      load_tile(ks, ks + kTileElems, p.pages, it.table, it.next_load * kTileKeys, it.lo, it.n_keys, it.kvh, p.kv_heads, p.page_size, p.page_shift, lane);
     }
     cp_async_commit();
     it.next_load += kWarps;
@@ -202,7 +223,7 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
       const int s = (stage + kStages - 1) % kStages;
       if (it.next_load < it.tile_end) {
         __nv_bfloat16* ks = stage_base + (size_t)s * 2 * kTileElems;
-        load_tile(ks, ks + kTileElems, p.pages, it.table, it.next_load * kTileKeys, it.lo, it.n_keys, it.kvh, p.kv_heads, p.page_size, lane);
+        load_tile(ks, ks + kTileElems, p.pages, it.table, it.next_load * kTileKeys, it.lo, it.n_keys, it.kvh, p.kv_heads, p.page_size, p.page_shift, lane);
       }
       cp_async_commit();
       it.next_load += kWarps;
@@ -258,17 +279,29 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
         mma_bf16(s_frag[jp * 2 + 1], qa[ks], b[2], b[3]);
       }
     }
-    // mask and online softmax (log2 domain)
+    // mask and online softmax (log2 domain); only a request's first and last tile hold keys that do not count
     const int key0 = tile * kTileKeys;
     float tile_max[2] = {-INFINITY, -INFINITY};
+    if (key0 >= it.lo && key0 + kTileKeys <= it.n_keys) {
 #pragma unroll
-    for (int j = 0; j < kTileKeys / 8; ++j) {
+      for (int j = 0; j < kTileKeys / 8; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + j * 8 + 2 * t + (e & 1);
-        const float v = (key >= it.lo && key < it.n_keys) ? s_frag[j][e] * sl2 : -INFINITY;
-        s_frag[j][e] = v;
-        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+        for (int e = 0; e < 4; ++e) {
+          const float v = s_frag[j][e] * sl2;
+          s_frag[j][e] = v;
+          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kTileKeys / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + j * 8 + 2 * t + (e & 1);
+          const float v = (key >= it.lo && key < it.n_keys) ? s_frag[j][e] * sl2 : -INFINITY;
+          s_frag[j][e] = v;
+          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+        }
       }
     }
     float rescale[2];
@@ -294,12 +327,14 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
       pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
       pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
     }
+    if (__any_sync(0xffffffffu, rescale[0] != 1.0f || rescale[1] != 1.0f)) {   // after a request's first tiles the maxima seldom move
 #pragma unroll
-    for (int i = 0; i < kD / 8; ++i) {
-      o[i][0] *= rescale[0];
-      o[i][1] *= rescale[0];
-      o[i][2] *= rescale[1];
-      o[i][3] *= rescale[1];
+      for (int i = 0; i < kD / 8; ++i) {
+        o[i][0] *= rescale[0];
+        o[i][1] *= rescale[0];
+        o[i][2] *= rescale[1];
+        o[i][3] *= rescale[1];
+      }
     }
     // O += P . V
 #pragma unroll
