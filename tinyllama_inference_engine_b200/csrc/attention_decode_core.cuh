@@ -169,6 +169,27 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
   const int g = lane >> 2, t = lane & 3;
   const int group = p.q_heads / p.kv_heads;
   __nv_bfloat16* stage_base = reinterpret_cast<__nv_bfloat16*>(smem_raw) + (size_t)warp * kStages * 2 * kTileElems;
+  // The warp whose tile holds the new token's position patches that tile with the new key and value (and stores them in the
+  // cache).  It asks for them here, together with q, so that both come back in one trip to L2 instead of one after the other.
+  constexpr int kNewPerLane = (kD / 2 + 31) / 32, kNewValuesPerLane = (kD + 31) / 32;
+  float k_new_first[kNewPerLane], k_new_second[kNewPerLane], v_new_value[kNewValuesPerLane];
+  const int new_tile = it.pos / kTileKeys;
+  const bool patches = it.patch_new && new_tile >= it.tile_begin + warp && new_tile < it.tile_end && (new_tile - it.tile_begin - warp) % kWarps == 0;
+  if (patches) {
+    const __nv_bfloat16* k_new = p.q + (size_t)it.seq * p.q_row_stride + (size_t)(p.q_heads + it.kvh) * kD;
+    const __nv_bfloat16* v_new = k_new + (size_t)p.kv_heads * kD;
+#pragma unroll
+    for (int i = 0; i < kNewPerLane; ++i) {
+      const int d = lane + 32 * i;
+      k_new_first[i] = d < kD / 2 ? ldcg_bf16(k_new + d) : 0.0f;
+      k_new_second[i] = d < kD / 2 ? ldcg_bf16(k_new + d + kD / 2) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < kNewValuesPerLane; ++i) {
+      const int d = lane + 32 * i;
+      v_new_value[i] = d < kD ? ldcg_bf16(v_new + d) : 0.0f;
+    }
+  }
   // Q fragments: rows = query heads of the group (row r valid if r < group), k = head dims
   unsigned qa[kD / 16][4];
   {
@@ -232,17 +253,15 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
     __syncwarp();
     __nv_bfloat16* k_smem = stage_base + (size_t)stage * 2 * kTileElems;
     __nv_bfloat16* v_smem = k_smem + kTileElems;
-    if (it.patch_new && tile == it.pos / kTileKeys) {
-      const __nv_bfloat16* k_new = p.q + (size_t)it.seq * p.q_row_stride + (size_t)(p.q_heads + it.kvh) * kD;
-      const __nv_bfloat16* v_new = k_new + (size_t)p.kv_heads * kD;
+    if (patches && tile == new_tile) {
       const size_t plane = (size_t)p.kv_heads * p.page_size * kD;
       __nv_bfloat16* k_dst = p.pages + (size_t)it.table[it.pos / p.page_size] * 2 * plane + ((size_t)it.kvh * p.page_size + (it.pos % p.page_size)) * kD;
       const int row = it.pos % kTileKeys;
 #pragma unroll
-      for (int i = 0; i < (kD / 2 + 31) / 32; ++i) {
+      for (int i = 0; i < kNewPerLane; ++i) {
         const int d = lane + 32 * i;
         if (d >= kD / 2) break;
-        float first = ldcg_bf16(k_new + d), second = ldcg_bf16(k_new + d + kD / 2);
+        float first = k_new_first[i], second = k_new_second[i];
         if (p.inv_freq != nullptr) {
           const float c = it.rotation[d], sn = it.rotation[kD / 2 + d];
           const float a = first * c - second * sn, b = second * c + first * sn;
@@ -255,8 +274,11 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
         k_dst[d] = kf;
         k_dst[d + kD / 2] = ks2;
       }
-      for (int d = lane; d < kD; d += 32) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(ldcg_bf16(v_new + d));
+#pragma unroll
+      for (int i = 0; i < kNewValuesPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= kD) break;
+        const __nv_bfloat16 v = __float2bfloat16_rn(v_new_value[i]);
         v_smem[row * kRow + d] = v;
         k_dst[plane + d] = v;
       }
