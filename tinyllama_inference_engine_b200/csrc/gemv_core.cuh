@@ -109,7 +109,10 @@ __device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* x
 // variant's epilogue.  acc[mt] is a warp's m16n8 accumulator (weight rows x activation rows).  A gated tile holds 8 gate
 // rows in the upper half of the accumulator's rows and the 8 up rows of the same outputs in the lower half.
 template <int MT, int XMODE, int EPI, int WARPS = kGemvWarps>
-__device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float (&acc)[MT][4], float* red, const float* row_scale, int n0) {
+// prior, prior_weight (ACCUM): the residual element this thread will add to and the next norm's weight for its column, asked for
+// before the k loop (gemv_epilogue_prefetch) so that the end of the tile does not wait for two trips to L2.
+__device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float (&acc)[MT][4], float* red, const float* row_scale, int n0, float prior = 0.0f,
+                                                  float prior_weight = 0.0f) {
   constexpr int kRedRow = MT * 8 + 1;
   constexpr int kTileRows = (EPI == EPI_GATED) ? 8 : 16;      // outputs of a tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,11 +149,11 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
     } else if (EPI == EPI_ACCUM) {
       float value = 0.0f;
       if (live) {
-        value = __ldcg(reinterpret_cast<const float*>(a.out) + o) + sum;
+        value = prior + sum;
         reinterpret_cast<float*>(a.out)[o] = value;
       }
       if (a.prepare_weight != nullptr) {   // the same for the whole block
-        if (live) a.prepare_x[o] = __float2bfloat16_rn(value * a.prepare_weight[n0 + r]);
+        if (live) a.prepare_x[o] = __float2bfloat16_rn(value * prior_weight);
         float squares = value * value;     // zero where nothing lives; the 16 columns of a row are 16 neighbouring lanes
 #pragma unroll
         for (int offset = 8; offset > 0; offset >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, offset);
@@ -219,6 +222,16 @@ struct GemvPhase {
       float acc[MT][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
+      // what the end of the tile will add to (the epilogue gives a thread at most one output: the block is at least as wide as the tile)
+      float prior = 0.0f, prior_weight = 0.0f;
+      if (EPI == EPI_ACCUM && threadIdx.x < kTileRows * MT * 8) {
+        static_assert(kTileRows * MT * 8 <= WARPS * 32, "one output per thread at most");
+        const int m = threadIdx.x / kTileRows, r = threadIdx.x - m * kTileRows;
+        if (m < a.M && n0 + r < n_rows) {
+          prior = __ldcg(reinterpret_cast<const float*>(a.out) + (size_t)m * n_rows + n0 + r);
+          if (a.prepare_weight != nullptr) prior_weight = __ldg(a.prepare_weight + n0 + r);
+        }
+      }
 
       for (int kb0 = warp; kb0 < blocks; kb0 += WARPS * UNROLL) {
         if (kb0 != warp || !issued) issue(a, n0, kb0);
@@ -261,7 +274,7 @@ struct GemvPhase {
       // old one, and the widest products took half as long again.)
       issued = tile_index + tile_step < tiles;
       if (issued) issue(a, (tile_index + tile_step) * kTileRows, warp);
-      gemv_reduce_store<MT, XMODE, EPI, WARPS>(a, acc, red, row_scale, n0);
+      gemv_reduce_store<MT, XMODE, EPI, WARPS>(a, acc, red, row_scale, n0, prior, prior_weight);
     }
   }
 };
