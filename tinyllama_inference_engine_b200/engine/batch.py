@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from itertools import chain
 
 import numpy as np
 import torch
@@ -89,36 +90,35 @@ class StepContext:
 
 
 def lay_out_step(entries: list[StepEntry], first_positions: list[int], slots: list[int], table_rows: list[list[list[int]]]) -> dict:
-    """The step as one flat list of int32 words and where its sections lie (host work only)."""
+    """The step as one flat array of int32 words and where its sections lie (host work only).
+
+    Sections that have a word per token are made with numpy (a 2,048-token portion costs 0.1 ms so, 0.3 ms as Python lists)."""
     q_lens = [len(e.tokens) for e in entries]
     num_tokens, num_seqs = sum(q_lens), len(entries)
-    token_ids: list[int] = []
-    positions: list[int] = []
-    token_seq: list[int] = []
-    seq_starts = [0]
-    want_rows: list[int] = []
-    for index, (entry, first) in enumerate(zip(entries, first_positions)):
-        start = seq_starts[-1]
-        token_ids += entry.tokens
-        positions += range(first, first + len(entry.tokens))
-        token_seq += [index] * len(entry.tokens)
-        want_rows += [start + w for w in entry.want]
-        seq_starts.append(start + len(entry.tokens))
+    lens = np.asarray(q_lens, dtype=np.int32)
+    starts = np.zeros(num_seqs + 1, dtype=np.int32)
+    np.cumsum(lens, out=starts[1:])
+    seq_starts = starts.tolist()
+    token_ids = np.fromiter(chain.from_iterable(e.tokens for e in entries), dtype=np.int32, count=num_tokens)
+    shift = np.asarray(first_positions, dtype=np.int32) - starts[:-1]           # position of a row = its index + its entry's shift
+    positions = np.arange(num_tokens, dtype=np.int32) + np.repeat(shift, lens)
+    token_seq = np.repeat(np.arange(num_seqs, dtype=np.int32), lens)
+    want_rows = [start + w for start, entry in zip(seq_starts, entries) for w in entry.want]
     seq_lens = [f + n for f, n in zip(first_positions, q_lens)]
     plans = [plan for plan in _STEP_PLANS.values() if plan.wanted(q_lens)]
-    sections = [token_ids, positions, token_seq, seq_starts, seq_lens, first_positions, slots, want_rows]
+    sections = [token_ids, positions, token_seq, starts, seq_lens, first_positions, slots, want_rows]
     sections += [plan.build(q_lens, first_positions, seq_starts) for plan in plans]
-    flat: list[int] = []
-    offsets = []
+    offsets, words = [], 0
     for section in sections:
-        offsets.append((len(flat), len(section)))
-        flat += section
+        offsets.append((words, len(section)))
+        words += len(section)
     table_offsets = []
     for rows in table_rows:
         width = len(rows[0]) if rows else 0
-        table_offsets.append((len(flat), num_seqs, width))
-        for row in rows:
-            flat += row
+        table_offsets.append((words, num_seqs, width))
+        sections.append(np.asarray(rows, dtype=np.int32).reshape(-1))
+        words += num_seqs * width
+    flat = np.concatenate([np.asarray(section, dtype=np.int32) for section in sections])
     return {"flat": flat, "offsets": offsets, "table_offsets": table_offsets, "plans": plans, "q_lens": q_lens, "seq_lens": seq_lens,
             "num_tokens": num_tokens, "num_seqs": num_seqs, "want_rows": want_rows}
 
@@ -132,7 +132,7 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
     layout = lay_out_step(entries, first_positions, slots, table_rows)
     flat, offsets, table_offsets, plans = layout["flat"], layout["offsets"], layout["table_offsets"], layout["plans"]
     if into is None:
-        host = torch.from_numpy(np.asarray(flat, dtype=np.int32))   # (torch.tensor of a list of 7,000 ints takes 0.46 ms, this 0.2)
+        host = torch.from_numpy(flat)
         if device.type == "cuda":
             host = host.pin_memory()
         buffer = host.to(device, non_blocking=True)
@@ -149,7 +149,7 @@ def pack_step(entries: list[StepEntry], first_positions: list[int], slots: list[
         first_positions=views[5], state_slots=views[6], want_rows=views[7] if want_rows else None,
         block_tables=tables, request_ids=[e.request_id for e in entries], host_q_lens=layout["q_lens"],
         host_first_positions=list(first_positions), host_state_slots=list(slots),
-        max_q_len=max(layout["q_lens"]), max_seq_len=max(layout["seq_lens"]), wants_every_row_in_order=want_rows == list(range(num_tokens)),
+        max_q_len=max(layout["q_lens"]), max_seq_len=max(layout["seq_lens"]), wants_every_row_in_order=len(want_rows) == num_tokens and want_rows == list(range(num_tokens)),
         plans={plan.name: views[8 + i].view(-1, plan.columns) for i, plan in enumerate(plans)},
     )
 
