@@ -565,6 +565,7 @@ __global__ void __launch_bounds__(kThreadsTC, 2)
 static bool make_map_2d(CUtensorMap* map, const void* base, long long rows, long long width, long long row_stride, int box_rows) {
   EncodeTiledFn fn = encode_tiled();
   if (fn == nullptr) return false;
+  if (rows > 0x7fffffffLL) return false;   // a copy's row is a 32-bit coordinate (a pool this large only exists for tiny heads)
   const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
   const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};

@@ -24,10 +24,15 @@
 
 namespace tlie {
 
-// BN: any multiple of 16 up to 256 (the N of one tcgen05.mma with M = 128).  Widths between 128 and 256 exist for products
-// whose tiles would otherwise fill one wave of CTAs and a sliver of a second one.
+// BN: any multiple of 16 up to 256 (the N of one tcgen05.mma with M = 128), or a multiple of 32 up to 512 that two such
+// instructions per 16 k fill, half each.  Widths between 128 and 256 exist for products whose tiles would otherwise fill one
+// wave of CTAs and a sliver of a second one; widths beyond 256 for products that fit ONE wave so (2,048 x 2,560 is 160
+// tiles of 256 columns, two waves on 148 SMs, and 128 tiles of 320): such a tile has all of tensor memory for its one
+// accumulator, so nothing of its epilogue runs under a next tile's MMAs, and the host asks for it only when every CTA has one tile.
 template <int BN, int EPI = 0>
 struct GemmShape {
+  static constexpr int kHalves = BN > 256 ? 2 : 1;   // MMAs per 16 k
+  static constexpr int kMmaN = BN / kHalves;
   static constexpr int kStageBytes = (kBM + BN) * kBK * 2;
   // staging boxes of the epilogue's bulk stores (EPI 3: 32-bit boxes for bulk reductions): one per warp at least, two where
   // they fit beside the ring
@@ -38,9 +43,11 @@ struct GemmShape {
   static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kBoxBytes <= kRoom) ? 2 : 1;
   static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kBoxBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
-  static constexpr int kAccStride = BN <= 128 ? 128 : 256;   // tensor memory is allocated in powers of two
-  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "the N of a tcgen05.mma with M = 128");
-  static_assert(2 * kAccStride <= 512, "two accumulators must fit the 512 columns of tensor memory");
+  static constexpr int kAccStride = BN <= 128 ? 128 : BN <= 256 ? 256 : 512;   // tensor memory is allocated in powers of two
+  static constexpr int kAccumulators = kAccStride <= 256 ? 2 : 1;
+  static_assert(kMmaN % 16 == 0 && kMmaN >= 16 && kMmaN <= 256, "the N of a tcgen05.mma with M = 128");
+  static_assert(kAccumulators * kAccStride <= 512, "the accumulators must fit the 512 columns of tensor memory");
+  static_assert(EPI != 2 || kHalves == 1, "the gated tile is one instruction wide");
   static_assert(kStages >= 2 && kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 };
 
@@ -68,7 +75,8 @@ __global__ void __launch_bounds__(kGemmThreads)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kTileN = EPI == 2 ? BN / 2 : BN;   // output columns of a tile
-  constexpr int kTmemCols = 2 * Shape::kAccStride;   // two accumulators
+  constexpr int kAccumulators = Shape::kAccumulators;
+  constexpr int kTmemCols = kAccumulators * Shape::kAccStride;
   const int m_blocks = (M + kBM - 1) / kBM;
   const int num_tiles = m_blocks * ((N + kTileN - 1) / kTileN);
   const int k_blocks = (K + kBK - 1) / kBK;
@@ -117,21 +125,23 @@ __global__ void __launch_bounds__(kGemmThreads)
             tma_load_2d(b_tile, &map_b, kb * kBK, n0, bar);                                  // gate rows
             tma_load_2d(b_tile + (BN / 2) * kBK * 2, &map_b, kb * kBK, N + n0, bar);        // up rows
           } else {
-            tma_load_2d(b_tile, &map_b, kb * kBK, n0, bar);
+#pragma unroll
+            for (int h = 0; h < Shape::kHalves; ++h)   // rows past N are filled with zeros
+              tma_load_2d(b_tile + h * Shape::kMmaN * kBK * 2, &map_b, kb * kBK, n0 + h * Shape::kMmaN, bar);
           }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {   // MMA issuer
-      constexpr uint32_t idesc = umma_instr_desc(kBM, BN);
+      constexpr uint32_t idesc = umma_instr_desc(kBM, Shape::kMmaN);
       RingPosition<kStages> ring;
       const uint32_t tiles_low = umma_desc_low(smem_u32(tiles)), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
       int local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const int acc = local & 1;
-        ok = mbar_wait(&accum_empty[acc], ((local >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained this accumulator
+        const int acc = local % kAccumulators;
+        ok = mbar_wait(&accum_empty[acc], ((local / kAccumulators) & 1) ^ 1, abort_flag);   // the epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride;
@@ -143,8 +153,11 @@ __global__ void __launch_bounds__(kGemmThreads)
           const uint32_t a_low = tiles_low + ring.stage * (Shape::kStageBytes >> 4), b_low = a_low + ((kBM * kBK * 2) >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
-            // 16 k = 32 bytes further inside the 128-byte swizzle span
-            umma_bf16(tmem_acc, a_low + k * ((kUmmaK * 2) >> 4), b_low + k * ((kUmmaK * 2) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            // 16 k = 32 bytes further inside the 128-byte swizzle span; the second half of a wide tile: kMmaN rows of B further, kMmaN columns on
+#pragma unroll
+            for (int h = 0; h < Shape::kHalves; ++h)
+              umma_bf16(tmem_acc + h * Shape::kMmaN, a_low + k * ((kUmmaK * 2) >> 4), b_low + h * ((Shape::kMmaN * kBK * 2) >> 4) + k * ((kUmmaK * 2) >> 4), idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_addr + 8 * ring.stage);   // the stage is free once these MMAs have read it
         }
@@ -156,9 +169,9 @@ __global__ void __launch_bounds__(kGemmThreads)
     const int sub = warp & 3;
     int local = 0, boxes = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-      const int acc = local & 1;
+      const int acc = local % kAccumulators;
       const int m0 = (tile % m_blocks) * kBM, n0 = (tile / m_blocks) * kTileN;
-      if (!mbar_wait(&accum_full[acc], (local >> 1) & 1, abort_flag)) break;
+      if (!mbar_wait(&accum_full[acc], (local / kAccumulators) & 1, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
@@ -193,7 +206,7 @@ template <int BN, int EPI>
 static int launch_gemm(const void* x, const void* w, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
   CUtensorMap map_a, map_b, map_out;
   // EPI 2: w has 2 N rows, fetched as two boxes of BN / 2 rows; N is the width of the output
-  if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, EPI == 2 ? BN / 2 : BN)) return (int)cudaErrorInvalidValue;
+  if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, EPI == 2 ? BN / 2 : GemmShape<BN, EPI>::kMmaN)) return (int)cudaErrorInvalidValue;
   if (EPI == 3 && !make_add_map(&map_out, out, M, N)) return (int)cudaErrorInvalidValue;
   const int staged = EPI == 3 || (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
   if (!staged) map_out = map_a;
@@ -218,13 +231,16 @@ using namespace tlie;
 // out[M, N] = x[M, K] . w[N, K]^T.  x and w bfloat16 row-major with 16-byte aligned bases and K % 8 == 0 (TMA strides);
 // out bfloat16 (out_f32 = 0), 32-bit (1), out_f32 = 2: w is [gate rows | up rows] of N rows each and out [M, N] = silu(gate) * up,
 // or out_f32 = 3: out is 32-bit (16-byte aligned, N % 4 == 0) and the product is added to it.
-// tile_n is 128, 160, 192 or 256.  `error_flag` (device int, zero) becomes 1 if a wait gave up.
+// tile_n is 128, 160, 192, 256 or 320.  `error_flag` (device int, zero) becomes 1 if a wait gave up.
 TLIE_EXPORT int tlie_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int tile_n, int* error_flag,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || error_flag == nullptr || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   if (out_f32 == 2) return launch_gemm<256, 2>(x, w, out, M, N, K, error_flag, stream);   // gated: N = rows of one half of w
   if (out_f32 == 3) return launch_gemm<256, 3>(x, w, out, M, N, K, error_flag, stream);   // out (32-bit) += the product
+  if (tile_n == 320) {
+    return out_f32 ? launch_gemm<320, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<320, 0>(x, w, out, M, N, K, error_flag, stream);
+  }
   if (tile_n == 256) {
     return out_f32 ? launch_gemm<256, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<256, 0>(x, w, out, M, N, K, error_flag, stream);
   }

@@ -280,6 +280,7 @@ def tcgen05_error_flag(device: torch.device) -> torch.Tensor:
 
 
 GEMM_TILE_WIDTHS = (256, 192, 160, 128)
+GEMM_WIDE_TILE = 320   # two MMAs wide, one accumulator: for products that fit one wave of CTAs so (one-SM tiles only)
 
 
 # Tiles of 256 rows on pairs of SMs (tcgen05 cta_group::2, gemm_tcgen05_pair.cu) bring a third less from L2 per flop.  Measured at
@@ -294,10 +295,14 @@ def gemm_tile_width(M: int, N: int, pair: bool = False) -> int:
     """The tile width whose waves of persistent CTAs (or pairs of them) cost least.
 
     A tile costs its width plus a fixed part about as large as 300 columns (measured: a 128 x 160 tile takes 0.8 of the time
-    of a 128 x 256 one), so the widest tile wins unless a narrower one saves a whole wave; the wider tile on a tie."""
+    of a 128 x 256 one), so the widest tile wins unless a narrower one saves a whole wave; the wider tile on a tie.  The wide
+    tile has no second accumulator to work on while its epilogue runs, so it is a candidate only where no CTA gets two."""
     workers = sm_count() // 2 if pair else sm_count()
     row_blocks = -(-M // (256 if pair else 128))
-    return min(GEMM_TILE_WIDTHS, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * (width + 300), -width))
+    widths = GEMM_TILE_WIDTHS
+    if not pair and row_blocks * -(-N // GEMM_WIDE_TILE) <= workers:
+        widths = (GEMM_WIDE_TILE,) + widths
+    return min(widths, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * (width + 300), -width))
 
 
 def gemm_tcgen05(x, weight, out, tile_n: int | None = None, pair: bool | None = None) -> None:
