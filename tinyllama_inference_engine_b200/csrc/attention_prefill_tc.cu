@@ -41,8 +41,9 @@
 // tile).  Head size 128 is made to fit the same way: two stages and ONE running output of 128 columns that the second row tile
 // takes over when the first has been read out: 96 KB and 256 columns.  (One CTA per SM with everything doubled ran the
 // 8,192-token prefill of the 8B shapes at 1.41 ms a layer.)
-// With more work items than the SMs hold at once the host sends single row tiles, heaviest first (ops.fast.single_attention_tiles),
-// else pairs of a heavy and a light one (paired_attention_tiles); the kernel takes either.
+// A work item is one row tile or two.  Steps send single row tiles, heaviest first (ops.fast.single_attention_tiles): a CTA is a
+// chain of dependent waits, so twice the CTAs with half the work each were faster at every length measured (one request of 512 to
+// 4,096 tokens: by 3 to 24 %) than pairs of a heavy and a light tile (paired_attention_tiles), which the kernel also takes.
 #include "tcgen05_utils.cuh"
 
 namespace tlie {
@@ -200,8 +201,7 @@ __global__ void __launch_bounds__(kThreadsTC, 2)
   volatile int* abort_flag = &sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // A work item is a pair of row tiles (the second may be absent): the host pairs a tile that sees many keys with one
-  // that sees few, so that all CTAs carry about the same work and the grid ends together.
+  // A work item is one row tile or a pair of them (the second absent: -1).
   // The heads of a work item are neighbours in the order CTAs are handed out (x runs fastest), and the items come heaviest first:
   // with more CTAs than the SMs hold at once, every slot that comes free takes the heaviest work left, and the CTAs that run
   // together read the same keys and values (the heads of a group) out of L2.

@@ -492,12 +492,14 @@ def _row_tiles_by_work(q_lens: list[int], first_positions: list[int], seq_starts
 
 
 def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int], first_entry: int = 0) -> list[int]:
-    """Work items of the tensor-memory attention kernel: (entry, first row, entry or -1, first row) per item.
+    """Work items of two row tiles for the tensor-memory attention kernel: (entry, first row, entry or -1, first row) per item.
 
     A run of ATTENTION_TC_TILE_ROWS rows late in a long request sees many keys, an early one few.  Pairing the heaviest
     tile with the lightest, the second heaviest with the second lightest, and so on, gives every CTA about the same
-    number of key tiles, so a grid that the SMs hold at once finishes together instead of waiting for the last heavy tiles.
-    """
+    number of key tiles.  The kernel takes such items, but steps do not send them: a CTA is a chain of dependent waits,
+    so twice the CTAs with half the work each are faster at every length (one request of 512 tokens at 32 heads of 64:
+    15.6 us in pairs, 11.9 us as single tiles; 1,024: 25.7 / 21.1; 2,048: 42.5 / 41.2; 4,096: 139 / 129; head size 128, 2,048:
+    60.9 / 54.1).  Kept for the kernel's tests and its cycle counters."""
     singles = _row_tiles_by_work(q_lens, first_positions, seq_starts, first_entry)
     flat: list[int] = []
     low, high = 0, len(singles) - 1
@@ -514,9 +516,8 @@ def paired_attention_tiles(q_lens: list[int], first_positions: list[int], seq_st
 
 
 def single_attention_tiles(q_lens: list[int], first_positions: list[int], seq_starts: list[int], first_entry: int = 0) -> list[int]:
-    """The same row tiles one to a work item, heaviest first: for grids of several waves, where the CTAs are handed out in this order
-    and every slot that comes free takes the heaviest tile left (equal pairs would run in whole waves: 1,024 CTAs of 8,192 tokens at
-    32 heads take four rounds on 296 slots where the work is 3.5)."""
+    """Work items of the tensor-memory attention kernel, a row tile each, heaviest first: (entry, first row, -1, 0) per item.  The CTAs
+    are handed out in this order, so every slot that comes free takes the heaviest tile left."""
     flat: list[int] = []
     for _, index, row in _row_tiles_by_work(q_lens, first_positions, seq_starts, first_entry):
         flat += [index, row, -1, 0]
@@ -532,9 +533,7 @@ def _register_step_plans() -> None:
 
     not_decode = lambda q_lens: max(q_lens) > 1  # noqa: E731
     register_step_plan(StepPlan("attention_tiles", 2, lambda q, f, s: attention_tiles(q, f, s, leading_single_rows(q)), not_decode), replace=True)
-    register_step_plan(StepPlan("attention_tiles_tc", 4, lambda q, f, s: paired_attention_tiles(q, f, s, leading_single_rows(q)), not_decode), replace=True)
-    register_step_plan(StepPlan("attention_tiles_tc_single", 4, lambda q, f, s: single_attention_tiles(q, f, s, leading_single_rows(q)),
-                                lambda q_lens: sum(-(-n // ATTENTION_TC_TILE_ROWS) for n in q_lens) > 8), replace=True)
+    register_step_plan(StepPlan("attention_tiles_tc", 4, lambda q, f, s: single_attention_tiles(q, f, s, leading_single_rows(q)), not_decode), replace=True)
     register_step_plan(StepPlan("attention_tiles_lead", 2, lambda q, f, s: attention_tiles(q, f, s, 0, leading_single_rows(q)),
                                 lambda q_lens: max(q_lens) > 1 and leading_single_rows(q_lens) > 0), replace=True)
 
@@ -599,11 +598,8 @@ def paged_attention_bf16(qkv, pages, positions, token_seq, block_table, out, q_h
             prefill_attention(qkv, pages, batch.plan("attention_tiles_lead"), batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads,
                               head_dim, page_size, window, scale)
     tc_tiles = batch.plan("attention_tiles_tc")
-    singles = batch.plan("attention_tiles_tc_single")
-    if tc_tiles is not None and singles is not None and tc_tiles.shape[0] * q_heads > 2 * sm_count():
-        tc_tiles = singles   # more pairs than the SMs hold at once (two CTAs each): single row tiles, heaviest first, fill the slots as they come free
     if (use_tc_attention and tc_tiles is not None and head_dim in TC_ATTENTION_HEAD_DIMS and page_size % 64 == 0 and pages.is_contiguous()
-            and batch.num_tokens - lead >= TC_ATTENTION_MIN_ROWS_PER_TILE * (1 if tc_tiles is singles else 2) * tc_tiles.shape[0]):
+            and batch.num_tokens - lead >= TC_ATTENTION_MIN_ROWS_PER_TILE * tc_tiles.shape[0]):
         prefill_attention_tc(qkv, pages, tc_tiles, batch.seq_starts, batch.first_positions, block_table, out, q_heads, kv_heads, head_dim, page_size, window, scale)
         return True
     tiles = batch.plan("attention_tiles")
