@@ -106,9 +106,9 @@ class ModelRunner:
             seen.add(entry.request_id)
             if not entry.tokens:
                 raise BatchError(f"request {entry.request_id!r} brings no tokens")
-            for token in entry.tokens:
-                if not 0 <= token < vocab:
-                    raise BatchError(f"token {token} of request {entry.request_id!r} is outside the vocabulary of {vocab}")
+            if min(entry.tokens) < 0 or max(entry.tokens) >= vocab:
+                token = next(token for token in entry.tokens if not 0 <= token < vocab)
+                raise BatchError(f"token {token} of request {entry.request_id!r} is outside the vocabulary of {vocab}")
             for place in entry.want:
                 if not 0 <= place < len(entry.tokens):
                     raise BatchError(f"request {entry.request_id!r} wants place {place} among {len(entry.tokens)} tokens")
