@@ -72,7 +72,7 @@ TLIE_EXPORT int tlie_decode_attention(const void* q, int q_row_stride, void* pag
                                       int fuse_rope, const float* inv_freq, int write_cache, cudaStream_t stream) {
   if (requests <= 0) return 0;
   if (kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || splits < 1 || splits > 32 || scratch == nullptr ||
-      (long long)requests * kv_heads > kMaxTickets || (fuse_rope && inv_freq != nullptr && kD % 32 != 0))
+      (long long)requests * kv_heads > kMaxTickets || (fuse_rope && inv_freq != nullptr && kD % 32 != 0) || !(scale > 0.0f))   // the maximum is taken before the scale
     return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
@@ -141,7 +141,7 @@ TLIE_EXPORT int tlie_decode_attention_static(const void* q, int q_row_stride, vo
   if (requests <= 0) return 0;
   // every shape rule of tlie_decode_attention is applied here first, so that nothing at all is enqueued for a refused shape
   if (kv_heads <= 0 || q_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || splits < 1 || splits > 32 ||
-      (fuse_rope && inv_freq != nullptr && kD % 32 != 0))
+      (fuse_rope && inv_freq != nullptr && kD % 32 != 0) || !(scale > 0.0f))
     return (int)cudaErrorInvalidValue;
   if ((long long)requests * q_heads * splits > kStaticMaxSlots || (long long)requests * kv_heads > kMaxTickets)
     return (int)cudaErrorInvalidValue;   // beyond the built-in scratch: nothing is launched

@@ -46,6 +46,27 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* k_smem, __nv_bfloat16* 
       const int page_index = page_shift >= 0 ? k >> page_shift : k / page_size;   // pages of a power of two: no division
       half_base[h] = pages + (size_t)table[page_index] * 2 * plane + ((size_t)kvh * page_size + (k - page_index * page_size)) * kD;
     }
+    if constexpr (32 % kChunks == 0) {
+      // A lane's chunks lie a fixed distance apart, in the page and in the buffer: two source addresses per half of the tile and
+      // one destination each for K and V, everything else is an immediate offset (one instruction per 16 bytes, where the general
+      // loop below works out two 64-bit addresses for every chunk).
+      constexpr int kRowsPerPass = 32 / kChunks;   // rows that one pass of the warp covers: 4 at head size 64, 2 at 128
+      const int r = lane / kChunks, c = lane % kChunks;
+      const unsigned k_dst = (unsigned)__cvta_generic_to_shared(k_smem + r * kRow + c * 8);
+      const unsigned v_dst = (unsigned)__cvta_generic_to_shared(v_smem + r * kRow + c * 8);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const __nv_bfloat16* k_src = half_base[h] + r * kD + c * 8;
+        const __nv_bfloat16* v_src = k_src + plane;
+#pragma unroll
+        for (int i = 0; i < 16 / kRowsPerPass; ++i) {
+          constexpr int kRowBytes = kRow * (int)sizeof(__nv_bfloat16);
+          cp_async_16_to(k_dst + (h * 16 + i * kRowsPerPass) * kRowBytes, k_src + i * kRowsPerPass * kD);
+          cp_async_16_to(v_dst + (h * 16 + i * kRowsPerPass) * kRowBytes, v_src + i * kRowsPerPass * kD);
+        }
+      }
+      return;
+    }
 #pragma unroll
     for (int idx = lane; idx < kTileKeys * kChunks; idx += 32) {
       const int row = idx / kChunks;
@@ -236,6 +257,7 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.0f, 0.0f};
   const float sl2 = p.scale * kLog2e;
+  const bool upper_rows = group > 8;
 
   int stage = 0;
   for (int tile = it.tile_begin + warp; tile < it.tile_end; tile += kWarps) {
@@ -301,37 +323,34 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
         mma_bf16(s_frag[jp * 2 + 1], qa[ks], b[2], b[3]);
       }
     }
-    // mask and online softmax (log2 domain); only a request's first and last tile hold keys that do not count
+    // mask and online softmax (log2 domain); only a request's first and last tile hold keys that do not count.  The scores stay
+    // as the product left them: the scale goes into the exponent's multiply-add (it is positive, so the maximum can be taken first).
+    // Rows 8..15 of the tile exist only for groups of more than eight query heads: otherwise nothing is worked out for them.
     const int key0 = tile * kTileKeys;
     float tile_max[2] = {-INFINITY, -INFINITY};
-    if (key0 >= it.lo && key0 + kTileKeys <= it.n_keys) {
-#pragma unroll
-      for (int j = 0; j < kTileKeys / 8; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float v = s_frag[j][e] * sl2;
-          s_frag[j][e] = v;
-          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
-        }
-      }
-    } else {
+    if (!(key0 >= it.lo && key0 + kTileKeys <= it.n_keys)) {
 #pragma unroll
       for (int j = 0; j < kTileKeys / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int key = key0 + j * 8 + 2 * t + (e & 1);
-          const float v = (key >= it.lo && key < it.n_keys) ? s_frag[j][e] * sl2 : -INFINITY;
-          s_frag[j][e] = v;
-          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+          if (!(key >= it.lo && key < it.n_keys)) s_frag[j][e] = -INFINITY;
         }
       }
     }
-    float rescale[2];
+#pragma unroll
+    for (int j = 0; j < kTileKeys / 8; ++j) tile_max[0] = fmaxf(tile_max[0], fmaxf(s_frag[j][0], s_frag[j][1]));
+    if (upper_rows) {
+#pragma unroll
+      for (int j = 0; j < kTileKeys / 8; ++j) tile_max[1] = fmaxf(tile_max[1], fmaxf(s_frag[j][2], s_frag[j][3]));
+    }
+    float rescale[2] = {1.0f, 1.0f};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
+      if (r == 1 && !upper_rows) break;
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-      const float new_max = fmaxf(row_max[r], tile_max[r]);
+      const float new_max = fmaxf(row_max[r], tile_max[r] * sl2);
       // a tile holds at least one valid key (tiles start at or after it.lo's tile and before it.n_keys), so new_max is finite
       rescale[r] = exp2f(row_max[r] - new_max);
       row_max[r] = new_max;
@@ -340,14 +359,20 @@ __device__ __forceinline__ void decode_attn_main(const DecodeAttnParams& p, Deco
     unsigned pa[kTileKeys / 16][4];
 #pragma unroll
     for (int j = 0; j < kTileKeys / 8; ++j) {
-      const float p0 = exp2_approx(s_frag[j][0] - row_max[0]);
-      const float p1 = exp2_approx(s_frag[j][1] - row_max[0]);
-      const float p2 = exp2_approx(s_frag[j][2] - row_max[1]);
-      const float p3 = exp2_approx(s_frag[j][3] - row_max[1]);
+      const float p0 = exp2_approx(fmaf(s_frag[j][0], sl2, -row_max[0]));
+      const float p1 = exp2_approx(fmaf(s_frag[j][1], sl2, -row_max[0]));
       row_sum[0] += p0 + p1;
-      row_sum[1] += p2 + p3;
       pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
-      pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      pa[j >> 1][(j & 1) * 2 + 1] = 0u;
+    }
+    if (upper_rows) {
+#pragma unroll
+      for (int j = 0; j < kTileKeys / 8; ++j) {
+        const float p2 = exp2_approx(fmaf(s_frag[j][2], sl2, -row_max[1]));
+        const float p3 = exp2_approx(fmaf(s_frag[j][3], sl2, -row_max[1]));
+        row_sum[1] += p2 + p3;
+        pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
     }
     if (__any_sync(0xffffffffu, rescale[0] != 1.0f || rescale[1] != 1.0f)) {   // after a request's first tiles the maxima seldom move
 #pragma unroll

@@ -10,6 +10,11 @@ __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool v
   const int bytes = valid ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled, nothing is read
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(gmem), "r"(bytes));
 }
+// The same copy by its shared-memory address, nothing zero-filled: with addresses that differ by constants a run of these is one
+// instruction each.
+__device__ __forceinline__ void cp_async_16_to(unsigned smem_addr, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
