@@ -103,14 +103,15 @@ def test_gemm_tile_width_prefers_full_waves():
     320-wide tiles, or narrower tiles where that is no single wave either."""
     from tinyllama_inference_engine_b200.ops import fast
 
-    assert fast.gemm_tile_width(2048, 2560) == 320      # 160 tiles of 256 would be two waves; 128 tiles of 320 are one
+    assert fast.gemm_tile_width(2048, 2560) == 288      # 160 tiles of 256 would be two waves; 144 tiles of 288 are one
+    assert fast.gemm_tile_width(2048, 2816) == 320      # 160 tiles of 288 are two waves; 144 tiles of 320 are one
     assert fast.gemm_tile_width(4096, 2560) == 256      # 256 tiles of 320 are no single wave, so the wide tile is no candidate
     assert fast.gemm_tile_width(2048, 2560, pair=True) in fast.GEMM_TILE_WIDTHS   # the wide tile is a one-SM tile
     assert fast.gemm_tile_width(2048, 2048) == 256      # 128 tiles: one wave
     assert fast.gemm_tile_width(256, 2048) == 128       # few row blocks: narrow tiles keep more CTAs busy
     for rows in (128, 300, 5000):
         for cols in (64, 1000, 32000):
-            assert fast.gemm_tile_width(rows, cols) in fast.GEMM_TILE_WIDTHS + (fast.GEMM_WIDE_TILE,)
+            assert fast.gemm_tile_width(rows, cols) in fast.GEMM_TILE_WIDTHS + fast.GEMM_WIDE_TILES
 
 
 def test_decode_attention_parts_fit_one_wave():

@@ -503,7 +503,7 @@ def test_decode_attention_with_rotation_and_cache_write(ops, q_heads, kv_heads, 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (2048, 2560, 2048), (300, 200, 136), (2048, 2048, 5632), (129, 1000, 2048), (1000, 131, 80),
                                    (4200, 2500, 72)])
-@pytest.mark.parametrize("tile_n,pair", [(width, pair) for width in (128, 160, 192, 256) for pair in (False, True)] + [(320, False)])   # the wide tile is a one-SM tile
+@pytest.mark.parametrize("tile_n,pair", [(width, pair) for width in (128, 160, 192, 256) for pair in (False, True)] + [(288, False), (320, False)])   # the wide tiles are one-SM tiles
 def test_gemm_tcgen05(ops, M, N, K, tile_n, pair):
     """The tcgen05 / TMA / tensor-memory product against a 32-bit product of the same bfloat16 values, tails included (the last
     shape gives every CTA several tiles at every width, the one-accumulator wide tile too)."""

@@ -27,7 +27,7 @@ namespace tlie {
 // BN: any multiple of 16 up to 256 (the N of one tcgen05.mma with M = 128), or a multiple of 32 up to 512 that two such
 // instructions per 16 k fill, half each.  Widths between 128 and 256 exist for products whose tiles would otherwise fill one
 // wave of CTAs and a sliver of a second one; widths beyond 256 for products that fit ONE wave so (2,048 x 2,560 is 160
-// tiles of 256 columns, two waves on 148 SMs, and 128 tiles of 320): such a tile has all of tensor memory for its one
+// tiles of 256 columns, two waves on 148 SMs, and 144 tiles of 288): such a tile has all of tensor memory for its one
 // accumulator, so nothing of its epilogue runs under a next tile's MMAs, and the host asks for it only when every CTA has one tile.
 template <int BN, int EPI = 0>
 struct GemmShape {
@@ -231,7 +231,7 @@ using namespace tlie;
 // out[M, N] = x[M, K] . w[N, K]^T.  x and w bfloat16 row-major with 16-byte aligned bases and K % 8 == 0 (TMA strides);
 // out bfloat16 (out_f32 = 0), 32-bit (1), out_f32 = 2: w is [gate rows | up rows] of N rows each and out [M, N] = silu(gate) * up,
 // or out_f32 = 3: out is 32-bit (16-byte aligned, N % 4 == 0) and the product is added to it.
-// tile_n is 128, 160, 192, 256 or 320.  `error_flag` (device int, zero) becomes 1 if a wait gave up.
+// tile_n is 128, 160, 192, 256, 288 or 320.  `error_flag` (device int, zero) becomes 1 if a wait gave up.
 TLIE_EXPORT int tlie_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int tile_n, int* error_flag,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -241,6 +241,10 @@ TLIE_EXPORT int tlie_gemm_tcgen05(const void* x, const void* w, void* out, int M
   if (tile_n == 320) {
     return out_f32 ? launch_gemm<320, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<320, 0>(x, w, out, M, N, K, error_flag, stream);
   }
+  if (tile_n == 288) {
+    return out_f32 ? launch_gemm<288, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<288, 0>(x, w, out, M, N, K, error_flag, stream);
+  }
+
   if (tile_n == 256) {
     return out_f32 ? launch_gemm<256, 1>(x, w, out, M, N, K, error_flag, stream) : launch_gemm<256, 0>(x, w, out, M, N, K, error_flag, stream);
   }

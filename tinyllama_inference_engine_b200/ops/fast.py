@@ -280,7 +280,7 @@ def tcgen05_error_flag(device: torch.device) -> torch.Tensor:
 
 
 GEMM_TILE_WIDTHS = (256, 192, 160, 128)
-GEMM_WIDE_TILE = 320   # two MMAs wide, one accumulator: for products that fit one wave of CTAs so (one-SM tiles only)
+GEMM_WIDE_TILES = (288, 320)   # two MMAs wide, one accumulator: for products that fit one wave of CTAs so (one-SM tiles only)
 
 
 # Tiles of 256 rows on pairs of SMs (tcgen05 cta_group::2, gemm_tcgen05_pair.cu) bring a third less from L2 per flop.  Measured at
@@ -300,8 +300,8 @@ def gemm_tile_width(M: int, N: int, pair: bool = False) -> int:
     workers = sm_count() // 2 if pair else sm_count()
     row_blocks = -(-M // (256 if pair else 128))
     widths = GEMM_TILE_WIDTHS
-    if not pair and row_blocks * -(-N // GEMM_WIDE_TILE) <= workers:
-        widths = (GEMM_WIDE_TILE,) + widths
+    if not pair:
+        widths = tuple(width for width in GEMM_WIDE_TILES if row_blocks * -(-N // width) <= workers) + widths
     return min(widths, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * (width + 300), -width))
 
 
