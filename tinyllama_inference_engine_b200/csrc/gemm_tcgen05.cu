@@ -48,6 +48,7 @@ struct GemmShape {
   static_assert(kMmaN % 16 == 0 && kMmaN >= 16 && kMmaN <= 256, "the N of a tcgen05.mma with M = 128");
   static_assert(kAccumulators * kAccStride <= 512, "the accumulators must fit the 512 columns of tensor memory");
   static_assert(EPI != 2 || kHalves == 1, "the gated tile is one instruction wide");
+  static_assert(BN % kStoreCols == 0, "the epilogue hands the tile over in boxes of kStoreCols columns");
   static_assert(kStages >= 2 && kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 };
 
