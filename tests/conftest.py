@@ -23,3 +23,16 @@ def model_folders(tmp_path_factory):
 
     base = tmp_path_factory.mktemp("models")
     return {key: write_random_model(base / key, config, seed) for key, (config, seed) in ALL.items()}
+
+
+@pytest.fixture(params=["library", "own"], ids=["mid-size products by the library", "own products from 128 rows"])
+def product_thresholds(request, monkeypatch):
+    """Steps of 128 to 2,047 rows send their products to the library (it is faster there); the second run of a test that uses this
+    fixture lowers the thresholds, so that the engine's own tensor-core products (plain, gated, adding into the residual) are
+    checked through the engine at the test's small sizes too."""
+    if request.param == "own":
+        from tinyllama_inference_engine_b200.ops import fast
+
+        monkeypatch.setattr(fast, "TCGEN05_MIN_ROWS", 128)
+        monkeypatch.setattr(fast, "TCGEN05_GATED_MIN_ROWS", 128)
+    return request.param

@@ -87,14 +87,17 @@ def test_step_refuses_bad_batches(model_folders, monkeypatch):
         small.runtime.workspace.get("anything", 9, 4, torch.float32)
 
 
-def test_plain_products_with_few_tiles_and_a_long_k_go_to_the_library():
+def test_products_below_2048_rows_go_to_the_library(monkeypatch):
     from tinyllama_inference_engine_b200.ops import fast
 
-    assert fast.tcgen05_takes(2048, 2048, 5632) and fast.tcgen05_takes(2048, 2560, 2048) and fast.tcgen05_takes(1280, 2048, 5632)
+    assert fast.tcgen05_takes(2048, 2048, 5632) and fast.tcgen05_takes(2048, 2560, 2048) and fast.tcgen05_takes(8192, 4096, 14336)
+    assert not fast.tcgen05_takes(1536, 2048, 5632) and not fast.tcgen05_takes(512, 2048, 2048)   # the library is ahead at these sizes
+    assert not fast.tcgen05_takes(64, 32000, 2048)
+    # the tile rule behind the row threshold: tiles for fewer than half of the SMs and a long K go to the library whatever the rows
+    monkeypatch.setattr(fast, "TCGEN05_MIN_ROWS", 128)
     assert not fast.tcgen05_takes(512, 2048, 5632)      # 32 tiles for 148 SMs, 88 k blocks each
     assert not fast.tcgen05_takes(1024, 2048, 5632)     # 64 tiles
-    assert fast.tcgen05_takes(512, 2048, 2048)          # few tiles, short K: level with the library and cheaper to launch
-    assert not fast.tcgen05_takes(64, 32000, 2048)      # below the kernel's smallest row count
+    assert fast.tcgen05_takes(512, 2048, 2048)          # few tiles, short K
     assert fast.tcgen05_takes(128, 32000, 8192)         # one row block, 125 tiles
 
 

@@ -23,7 +23,7 @@ from tinyllama_inference_engine_b200 import EngineConfig
 from tinyllama_inference_engine_b200.engine.runner import ModelRunner
 from tinyllama_inference_engine_b200.weights import write_random_model
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("product_thresholds")]
 
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}   # of the largest |logit|, as everywhere in these tests
 

@@ -9,7 +9,7 @@ import trace_tools
 from tinyllama_inference_engine_b200 import EngineConfig
 from tinyllama_inference_engine_b200.engine.runner import ModelRunner
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("product_thresholds")]
 
 # largest |difference| allowed, as a fraction of the largest |logit| of the request set
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}

@@ -248,7 +248,17 @@ def gemm_skinny(x, weight, out, *, epilogue: str = "store", prepared=None, prepa
 
 
 # --- tensor-core product for many rows (tcgen05, TMA, tensor memory) -------------------------------------
-TCGEN05_MIN_ROWS = 128     # from this many rows on the engine's own tcgen05 kernel runs instead of the library's product
+# From how many rows on the engine's own tcgen05 kernels run instead of the library's product (and, for the fused forms, the small
+# kernel after it).  Measured with CUDA events in a replayed graph, weights from HBM, at 1.1B and 7B widths, 128 to 2,048 rows:
+#   * the plain product is level with the library's from 2,048 rows on (qkv of 2,048 rows at 1.1B widths 19.4 against 20.7 us)
+#     and behind it below: by a tenth where there are tiles for every SM (7B widths, 1,024 rows: 83 against 74 us), by half where
+#     there are not (1.1B widths, 512 rows: 13.2 against 7.8 us; a CTA runs all of K for its tile, the library also splits K);
+#   * the product that adds into the 32-bit residual is level with product + add kernel from 2,048 rows on and behind below
+#     (7B widths, down-proj of 1,536 rows: 159 against 122 us);
+#   * the gated product on pairs of SMs is ahead of product + activation kernel from 1,024 rows on (7B widths: 130 against
+#     160 us; 1.1B widths: 46.7 against 45.5) and behind below (768 rows: 116 against 111, 36.4 against 33.6).
+TCGEN05_MIN_ROWS = 2048
+TCGEN05_GATED_MIN_ROWS = 1024
 use_tcgen05 = True
 
 
@@ -256,15 +266,13 @@ TCGEN05_SOURCES = ["gemm_tcgen05.cu", "gemm_tcgen05_pair.cu"]
 
 
 def tcgen05_takes(M: int, N: int, K: int) -> bool:
-    """Whether a plain product runs on this engine's tcgen05 kernel (else on the library's).
+    """Whether a plain product runs on this engine's tcgen05 kernel (else on the library's): from TCGEN05_MIN_ROWS rows on, and
+    not with tiles for fewer than half of the SMs and a long K.
 
-    The kernel gives a CTA whole 128 x 256 tiles, all of K each.  With tiles for fewer than half of the SMs and a long K the
-    library's product, which also splits K, is ahead by a factor: measured at 512 rows on the 1.1B shapes, down (K = 5,632)
-    32 against 16 us.  With a short K the two are within 10 % of each other and this kernel is the cheaper one to launch, which
-    is what counts for short prompt portions (their steps wait for the host, not for the GPU).  (Sharing a tile's k blocks
-    among CTAs was tried in this kernel: the owner of a tile collects the others' partial accumulators at the very end of its
-    share, eight trips to the L2 per partial tile with nothing left to hide them behind, and that cost more than even shares
-    saved.)"""
+    The kernel gives a CTA whole 128 x 256 tiles, all of K each; the library's product also splits K (measured at 512 rows on
+    the 1.1B shapes, down (K = 5,632): 32 against 16 us).  (Sharing a tile's k blocks among CTAs was tried in this kernel: the
+    owner of a tile collects the others' partial accumulators at the very end of its share, eight trips to the L2 per partial
+    tile with nothing left to hide them behind, and that cost more than even shares saved.)"""
     if M < TCGEN05_MIN_ROWS:
         return False
     return -(-M // 128) * -(-N // 256) >= sm_count() // 2 or K < 4096
