@@ -523,8 +523,9 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n, pair):
         assert float(error.max()) <= tol * scale, (float(error.max()), scale, int(error.argmax()) // N, int(error.argmax()) % N)
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (2048, 2048, 5632), (300, 200, 136), (1000, 132, 80), (129, 1000, 2048)])
-def test_gemm_tcgen05_accumulate(ops, M, N, K):
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (2048, 2048, 5632), (300, 200, 136), (1000, 132, 80), (129, 1000, 2048), (2100, 4100, 72)])
+def test_gemm_tcgen05_accumulate(ops, M, N, K, pair):
     """residual += product in the product's epilogue (bulk tensor reductions, each element once): twice in a row, tails included."""
     from tinyllama_inference_engine_b200.ops import fast
 
@@ -538,7 +539,7 @@ def test_gemm_tcgen05_accumulate(ops, M, N, K):
     view = guard[:M]
     view.copy_(residual)
     for times in (1, 2):
-        fast.gemm_tcgen05_accumulate(x.cuda(), w.cuda(), view)
+        fast.gemm_tcgen05_accumulate(x.cuda(), w.cuda(), view, pair=pair)
         torch.cuda.synchronize()
         assert int(fast.tcgen05_error_flag(view.device)) == 0, "a bounded wait inside the kernel gave up"
         want = start + times * product

@@ -59,26 +59,30 @@ __device__ __forceinline__ void arrive_at_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & kLeaderWindow) : "memory");
 }
 
-template <int BN>
+template <int BN, int EPI = 0>
 struct PairShape {
   static constexpr int kStageBytes = (kBM + BN / 2) * kBK * 2;   // per CTA: its rows of x and its half of the rows of w
-  static constexpr int kStages = (220 * 1024 / kStageBytes) < 8 ? (220 * 1024 / kStageBytes) : 8;
-  // staging boxes of the epilogue's bulk stores: two per warp where they fit beside the ring, else one
-  static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kStoreBoxBytes + 1280 <= 227 * 1024) ? 2 : 1;
-  static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kStoreBoxBytes;
+  // staging boxes of the epilogue's bulk stores (EPI 3: 32-bit boxes for bulk reductions): two per warp where they fit beside the
+  // ring, else one
+  static constexpr int kBoxBytes = EPI == 3 ? kAddBoxBytes : kStoreBoxBytes;
+  static constexpr int kRing = 220 * 1024 - (EPI == 3 ? kStoreWarps * 2 * kAddBoxBytes : 0);   // the reductions' boxes come out of the ring's room
+  static constexpr int kStages = (kRing / kStageBytes) < 8 ? (kRing / kStageBytes) : 8;
+  static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kBoxBytes + 1280 <= 227 * 1024) ? 2 : 1;
+  static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kBoxBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /* alignment slack */ + 256 /* barriers */;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
   static constexpr int kAccStride = BN <= 128 ? 128 : 256;       // tensor memory is allocated in powers of two
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "each CTA holds BN / 2 rows of w, in groups of 8");
 };
 
-// EPI as in gemm_tcgen05.cu: 0 bfloat16 out, 1 32-bit out, 2 (BN = 256) w = [gate rows | up rows] and out = silu(gate) * up.
+// EPI as in gemm_tcgen05.cu: 0 bfloat16 out, 1 32-bit out, 2 (BN = 256) w = [gate rows | up rows] and out = silu(gate) * up,
+// 3 the tile is added into the 32-bit `out` by bulk tensor reductions.
 template <int BN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_out, int staged, void* __restrict__ out, int M, int N, int K,
                      int* __restrict__ error_flag) {
-  using Shape = PairShape<BN>;
+  using Shape = PairShape<BN, EPI>;
   constexpr int kStages = Shape::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles need 1024-byte alignment
@@ -185,7 +189,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
-      if (EPI != 1 && staged) {
+      if (EPI == 3) {
+        add_tile_staged<BN, Shape::kStoreBuffers>(tmem_acc, m0 + sub * 32, n0, M, N, &map_out, staging + sub * Shape::kStoreBuffers * kAddBoxBytes, lane, boxes);
+      } else if (EPI != 1 && staged) {
         store_tile_staged<BN, EPI, Shape::kStoreBuffers>(tmem_acc, m0 + sub * 32, n0, M, N, &map_out,
                                                          staging + sub * Shape::kStoreBuffers * kStoreBoxBytes, lane, boxes);
       } else {
@@ -216,11 +222,12 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   CUtensorMap map_a, map_b, map_out;
   // each CTA fetches boxes of 128 rows of x and BN / 2 rows of w (gated: w has 2 N rows, one CTA takes gate rows, the other up rows)
   if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, BN / 2)) return (int)cudaErrorInvalidValue;
-  const int staged = (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
+  if (EPI == 3 && !make_add_map(&map_out, out, M, N)) return (int)cudaErrorInvalidValue;
+  const int staged = EPI == 3 || (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
   if (!staged) map_out = map_a;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairShape<BN>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairShape<BN, EPI>::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -228,7 +235,7 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   const int num_tiles = ((N + kTileN - 1) / kTileN) * ((M + 2 * kBM - 1) / (2 * kBM));
   const int sm_count = device_sm_count();
   const int pairs = num_tiles < sm_count / 2 ? num_tiles : sm_count / 2;
-  return (int)launch_pdl(gemm_pair_kernel<BN, EPI>, dim3(2 * pairs), dim3(kGemmThreads), PairShape<BN>::kSmemBytes, stream, map_a, map_b, map_out, staged, out,
+  return (int)launch_pdl(gemm_pair_kernel<BN, EPI>, dim3(2 * pairs), dim3(kGemmThreads), PairShape<BN, EPI>::kSmemBytes, stream, map_a, map_b, map_out, staged, out,
                          M, N, K, error_flag);
 }
 
@@ -242,6 +249,7 @@ TLIE_EXPORT int tlie_gemm_tcgen05_pair(const void* x, const void* w, void* out, 
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || error_flag == nullptr || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   if (out_f32 == 2) return launch_pair<256, 2>(x, w, out, M, N, K, error_flag, stream);   // gated: N = rows of one half of w
+  if (out_f32 == 3) return launch_pair<256, 3>(x, w, out, M, N, K, error_flag, stream);   // out (32-bit, 16-byte aligned, N % 4 == 0) += the product
   if (tile_n == 256) return out_f32 ? launch_pair<256, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<256, 0>(x, w, out, M, N, K, error_flag, stream);
   if (tile_n == 192) return out_f32 ? launch_pair<192, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<192, 0>(x, w, out, M, N, K, error_flag, stream);
   if (tile_n == 160) return out_f32 ? launch_pair<160, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<160, 0>(x, w, out, M, N, K, error_flag, stream);

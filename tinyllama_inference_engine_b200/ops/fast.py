@@ -291,11 +291,18 @@ GEMM_TILE_WIDTHS = (256, 192, 160, 128)
 GEMM_WIDE_TILES = (288, 320)   # two MMAs wide, one accumulator: for products that fit one wave of CTAs so (one-SM tiles only)
 
 
-# Tiles of 256 rows on pairs of SMs (tcgen05 cta_group::2, gemm_tcgen05_pair.cu) bring a third less from L2 per flop.  Measured at
-# 2,048 rows they are level with the one-SM tiles for the plain products (the wider tile fits the waves of small products
-# worse) and a little ahead for the gated one, which is what they are used for.
+# Tiles of 256 rows on pairs of SMs (tcgen05 cta_group::2, gemm_tcgen05_pair.cu) bring a third less from L2 per flop.  That pays
+# where a product is several waves of tiles, so that what the SMs can pull from L2 sets the pace: measured at 2,048 rows and
+# K = 4,096, N = 12,288: 139 us on pairs, 153 on single SMs (the library: 142); N = 4,096, K = 11,008: 129, 163 (144); 8,192 rows,
+# N = 6,144: 278, 317 (278).  A product of one wave or so is better off with one-SM tiles of the width that fits the wave
+# (2,048 x 2,560 x 2,048: 19.4 us in one wave of 288-wide tiles, 24.3 on pairs).  The gated product runs on pairs from 1,024 rows.
 PAIR_MIN_ROWS = 1024
 use_sm_pairs = True
+
+
+def pair_tiles_pay(M: int, N: int) -> bool:
+    """Whether a plain or accumulating product of this shape runs on pairs of SMs: one and a half waves of one-SM tiles or more."""
+    return use_sm_pairs and M >= PAIR_MIN_ROWS and -(-M // 128) * -(-N // 256) >= (3 * sm_count()) // 2
 
 
 @functools.lru_cache(maxsize=4096)
@@ -323,9 +330,9 @@ def gemm_tcgen05(x, weight, out, tile_n: int | None = None, pair: bool | None = 
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or K % 8 != 0 or not x.is_contiguous():
         raise KernelError("gemm_tcgen05 takes contiguous bfloat16 operands with K % 8 == 0", code="invalid_shape")
     if pair is None:
-        pair = False
+        pair = tile_n is None and pair_tiles_pay(M, N)
     if tile_n is None:
-        tile_n = gemm_tile_width(M, N, pair)
+        tile_n = 256 if pair else gemm_tile_width(M, N, pair)   # pairs: the widest tile brings least from L2 per flop
     library = tcgen05_library()
     entry = library.tlie_gemm_tcgen05_pair if pair else library.tlie_gemm_tcgen05
     ops._check(
@@ -344,17 +351,25 @@ def can_accumulate(rows: int, weight) -> bool:
     return (use_tcgen05 and use_accumulate_epilogue and weight.dtype == torch.bfloat16 and N % 4 == 0 and K % 8 == 0 and tcgen05_takes(rows, N, K))
 
 
-def gemm_tcgen05_accumulate(x, weight, residual) -> None:
-    """residual[M, N] (32-bit) += x[M, K] . weight[N, K]^T: the product's tiles are added by bulk tensor reductions, each element once."""
+def gemm_tcgen05_accumulate(x, weight, residual, pair: bool | None = None) -> None:
+    """residual[M, N] (32-bit) += x[M, K] . weight[N, K]^T: the product's tiles are added by bulk tensor reductions, each element once.
+
+    ``pair``: on pairs of SMs (default: from PAIR_MIN_ROWS rows on; these tiles are 256 wide either way, and the pairs were ahead
+    at every shape measured: down-proj of 2,048 rows at 1.1B widths 38.4 -> 35.3 us, at 7B widths 146 -> 133, at 8B widths and
+    8,192 rows 749 -> 668)."""
     ops = _ops()
     M, K = x.shape
     N = weight.shape[0]
     if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or residual.dtype != torch.float32 or residual.shape != (M, N) or K % 8 != 0 or N % 4 != 0
             or not x.is_contiguous() or not residual.is_contiguous()):
         raise KernelError("gemm_tcgen05_accumulate takes contiguous bfloat16 operands (K % 8 == 0) and a contiguous 32-bit residual [M, N] with N % 4 == 0", code="invalid_shape")
+    if pair is None:
+        pair = use_sm_pairs and M >= PAIR_MIN_ROWS
+    library = tcgen05_library()
+    entry = library.tlie_gemm_tcgen05_pair if pair else library.tlie_gemm_tcgen05
     ops._check(
-        tcgen05_library().tlie_gemm_tcgen05(ops._ptr(x), ops._ptr(weight), ops._ptr(residual), c_int(M), c_int(N), c_int(K), c_int(3), c_int(256),
-                                            ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
+        entry(ops._ptr(x), ops._ptr(weight), ops._ptr(residual), c_int(M), c_int(N), c_int(K), c_int(3), c_int(256),
+              ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
         "gemm_tcgen05_accumulate",
     )
 
