@@ -630,6 +630,17 @@ def test_hardware_probes_report_what_the_designs_rest_on():
     assert 400 < alone < 1200 and shared > 1.4 * alone                                       # the exponential unit is what two warps wait for
 
 
+def test_product_comparison_runs_every_form(ops):
+    """The committed comparison of the engine's products with the library's (kernel-bench --products) runs all forms at a small shape."""
+    from tinyllama_inference_engine_b200.ops.probes import product_comparison
+
+    report = product_comparison(256, 256, 512, 384, "cuda:0", launches=3)
+    assert set(report) == {"qkv", "o", "gate_up", "down"}
+    for line in report.values():
+        assert line["own, one SM"] > 0 and line["own, SM pairs"] > 0 and any(key.startswith("library") and value > 0 for key, value in line.items())
+        assert line["own_runs"] is False   # 256 rows: the library's
+
+
 @pytest.mark.parametrize("M", [1, 8, 16])
 def test_products_of_very_long_rows_stay_in_the_fused_kernel(ops, M):
     """K = 14,336 (the down projection of the 8B shapes): eight staged rows of x would not fit the kernel's shared memory, but with no

@@ -24,7 +24,8 @@ if MODEL_DIR is ``-``), ``--weights-sha256`` (the digest the
 folder's weights must have, as the reference pins its checkpoints: src/weight_store.cpp:150-190).  ``kernel-bench`` times every kernel family at the model's own shapes with CUDA events
 (median and 95th percentile), like the reference's benchmarks/kernel_benchmarks.cu:127-325; with ``--probes`` it also measures what the
 kernels' designs rest on (tensor-core time per MMA shape, the cost of a barrier hand-off, a warp's arithmetic rate), with
-``--attention-phases TOKENS`` where a key tile's cycles go in the tensor-memory prompt attention.
+``--attention-phases TOKENS`` where a key tile's cycles go in the tensor-memory prompt attention, with ``--products ROWS[,ROWS...]`` the
+layer's four products at those row counts on the engine's own tcgen05 kernels (one SM, SM pairs) and on the library's.
 """
 from __future__ import annotations
 
@@ -274,6 +275,10 @@ def _kernel_bench(args) -> int:
         from .ops.probes import attention_phase_cycles
 
         record["attention_phases"] = attention_phase_cycles(args.attention_phases, QH, KVH, D, dev)
+    if args.products:
+        from .ops.probes import product_comparison
+
+        record["products"] = {str(r): product_comparison(r, H, I, (QH + 2 * KVH) * D, dev) for r in args.products}
     print(json.dumps(record))
     return 0
 
@@ -339,6 +344,8 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights of --random-config")
     parser.add_argument("--weights-sha256", default="", help="the SHA-256 the model folder's weights must have; another digest is refused with checksum_mismatch")
     parser.add_argument("--probes", action="store_true", help="kernel-bench: also what an MMA of each shape, a barrier hand-off and a warp's arithmetic cost on this GPU")
+    parser.add_argument("--products", type=lambda text: [int(v) for v in text.split(",")], default=[], metavar="ROWS[,ROWS...]",
+                        help="kernel-bench: also the layer's four products at these row counts (128 or more), the engine's own tcgen05 kernels against the library's")
     parser.add_argument("--attention-phases", type=int, default=0, metavar="TOKENS",
                         help="kernel-bench: also where a key tile's cycles go in the tensor-memory prompt attention, for one request of TOKENS tokens (seven builds of the kernel)")
     try:

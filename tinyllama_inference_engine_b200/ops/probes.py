@@ -101,3 +101,61 @@ def attention_phase_cycles(tokens: int, q_heads: int, kv_heads: int, head_dim: i
             elif slot < len(phases):
                 report[role]["phases"][phases[slot]] = round(stamps[base + slot] / tiles_run)
     return report
+
+
+def product_comparison(rows: int, hidden: int, intermediate: int, qkv_width: int, device: torch.device | str = "cuda:0", launches: int = 12) -> dict:
+    """The four products of a layer for a step of ``rows`` rows (128 or more), bfloat16: the engine's own tcgen05 kernels (tiles on one
+    SM, tiles on pairs of SMs; plain, adding into the 32-bit residual, gated) against the library's product plus the small kernel
+    the fused form saves.  Microseconds per launch inside a replayed CUDA graph, every launch with another copy of the weights so
+    that they come from HBM.  ``own_runs`` says which form a step of this size gets (ops.fast thresholds)."""
+    from .. import ops
+    from . import fast
+
+    device = torch.device(device)
+
+    def timed(call) -> float:
+        for index in range(3):
+            call(index)
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for index in range(launches):
+                call(index)
+        graph.replay()
+        torch.cuda.synchronize(device)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize(device)
+        return round(start.elapsed_time(end) / launches * 1e3, 1)
+
+    report = {}
+    for name, N, K, kind in (("qkv", qkv_width, hidden, "plain"), ("o", hidden, hidden, "add"), ("gate_up", 2 * intermediate, hidden, "gated"),
+                             ("down", hidden, intermediate, "add")):
+        copies = max(2, int(300e6 / (N * K * 2)))
+        x = torch.randn(rows, K, device=device).bfloat16()
+        weights = [(torch.randn(N, K, device=device) * 0.05).bfloat16() for _ in range(copies)]
+        out = torch.empty(rows, N, device=device, dtype=torch.bfloat16)
+        line = {"N": N, "K": K}
+        if kind == "plain":
+            line["library"] = timed(lambda i: torch.mm(x, weights[i % copies].t(), out=out))
+            line["own, one SM"] = timed(lambda i: fast.gemm_tcgen05(x, weights[i % copies], out, pair=False))
+            line["own, SM pairs"] = timed(lambda i: fast.gemm_tcgen05(x, weights[i % copies], out, tile_n=256, pair=True))
+            line["own_runs"] = fast.tcgen05_takes(rows, N, K) and ("SM pairs" if fast.pair_tiles_pay(rows, N) else "one SM")
+        elif kind == "add":
+            residual = torch.zeros(rows, N, device=device)
+            line["library + add kernel"] = timed(lambda i: (torch.mm(x, weights[i % copies].t(), out=out), ops.add_(residual, out)))
+            line["own, one SM"] = timed(lambda i: fast.gemm_tcgen05_accumulate(x, weights[i % copies], residual, pair=False))
+            line["own, SM pairs"] = timed(lambda i: fast.gemm_tcgen05_accumulate(x, weights[i % copies], residual, pair=True))
+            line["own_runs"] = fast.can_accumulate(rows, weights[0]) and ("SM pairs" if rows >= fast.PAIR_MIN_ROWS else "one SM")
+        else:
+            half = torch.empty(rows, N // 2, device=device, dtype=torch.bfloat16)
+            line["library + activation kernel"] = timed(lambda i: (torch.mm(x, weights[i % copies].t(), out=out), ops.silu_mul(out, half)))
+            line["own, one SM"] = timed(lambda i: fast.gemm_tcgen05_gated(x, weights[i % copies], half, pair=False))
+            line["own, SM pairs"] = timed(lambda i: fast.gemm_tcgen05_gated(x, weights[i % copies], half, pair=True))
+            line["own_runs"] = rows >= fast.TCGEN05_GATED_MIN_ROWS and ("SM pairs" if rows >= fast.PAIR_MIN_ROWS else "one SM")
+        report[name] = line
+        del weights
+    ops.check_device_errors(device)
+    return report
