@@ -109,7 +109,13 @@ def test_gemm_tile_width_prefers_full_waves():
     assert fast.gemm_tile_width(2048, 2560) == 288      # 160 tiles of 256 would be two waves; 144 tiles of 288 are one
     assert fast.gemm_tile_width(2048, 2816) == 320      # 160 tiles of 288 are two waves; 144 tiles of 320 are one
     assert fast.gemm_tile_width(4096, 2560) == 256      # 256 tiles of 320 are no single wave, so the wide tile is no candidate
-    assert fast.gemm_tile_width(2048, 2560, pair=True) in fast.GEMM_TILE_WIDTHS   # the wide tile is a one-SM tile
+    assert not fast.pair_tiles_pay(2048, 2560)          # one wave on single SMs: it stays there
+    # pairs of SMs: where waves of tiles make L2 the limit, or where a wide tile of theirs makes one wave of two
+    assert fast.pair_tiles_pay(2048, 12288) and fast.gemm_tile_width(2048, 12288, pair=True) == 256
+    assert fast.pair_tiles_pay(2048, 4096) and fast.gemm_tile_width(2048, 4096, pair=True) == 480       # 72 tiles for 74 pairs
+    assert fast.gemm_tile_width(2048, 4096, pair=True, adding=True) == 480 and fast.gemm_tile_width(2048, 2048, pair=True, adding=True) == 256
+    assert fast.gemm_tile_width(4096, 4096, pair=True, adding=True) == 256                             # no single wave: two accumulators
+    assert not fast.pair_tiles_pay(512, 12288)          # below the pairs' row count
     assert fast.gemm_tile_width(2048, 2048) == 256      # 128 tiles: one wave
     assert fast.gemm_tile_width(256, 2048) == 128       # few row blocks: narrow tiles keep more CTAs busy
     for rows in (128, 300, 5000):

@@ -503,7 +503,7 @@ def test_decode_attention_with_rotation_and_cache_write(ops, q_heads, kv_heads, 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (2048, 2560, 2048), (300, 200, 136), (2048, 2048, 5632), (129, 1000, 2048), (1000, 131, 80),
                                    (4200, 2500, 72)])
-@pytest.mark.parametrize("tile_n,pair", [(width, pair) for width in (128, 160, 192, 256) for pair in (False, True)] + [(288, False), (320, False)])   # the wide tiles are one-SM tiles
+@pytest.mark.parametrize("tile_n,pair", [(width, pair) for width in (128, 160, 192, 256) for pair in (False, True)] + [(288, False), (320, False), (288, True), (384, True), (480, True)])   # the wide tiles: two for single SMs, three for pairs
 def test_gemm_tcgen05(ops, M, N, K, tile_n, pair):
     """The tcgen05 / TMA / tensor-memory product against a 32-bit product of the same bfloat16 values, tails included (the last
     shape gives every CTA several tiles at every width, the one-accumulator wide tile too)."""
@@ -523,9 +523,9 @@ def test_gemm_tcgen05(ops, M, N, K, tile_n, pair):
         assert float(error.max()) <= tol * scale, (float(error.max()), scale, int(error.argmax()) // N, int(error.argmax()) % N)
 
 
-@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("pair,tile_n", [(False, 256), (True, 256), (True, 384), (True, 480)])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (2048, 2048, 5632), (300, 200, 136), (1000, 132, 80), (129, 1000, 2048), (2100, 4100, 72)])
-def test_gemm_tcgen05_accumulate(ops, M, N, K, pair):
+def test_gemm_tcgen05_accumulate(ops, M, N, K, pair, tile_n):
     """residual += product in the product's epilogue (bulk tensor reductions, each element once): twice in a row, tails included."""
     from tinyllama_inference_engine_b200.ops import fast
 
@@ -539,7 +539,7 @@ def test_gemm_tcgen05_accumulate(ops, M, N, K, pair):
     view = guard[:M]
     view.copy_(residual)
     for times in (1, 2):
-        fast.gemm_tcgen05_accumulate(x.cuda(), w.cuda(), view, pair=pair)
+        fast.gemm_tcgen05_accumulate(x.cuda(), w.cuda(), view, pair=pair, tile_n=tile_n)
         torch.cuda.synchronize()
         assert int(fast.tcgen05_error_flag(view.device)) == 0, "a bounded wait inside the kernel gave up"
         want = start + times * product

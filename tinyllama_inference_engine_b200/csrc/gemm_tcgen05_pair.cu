@@ -59,20 +59,31 @@ __device__ __forceinline__ void arrive_at_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & kLeaderWindow) : "memory");
 }
 
+// BN up to 256 is the N of one MMA; beyond that (up to 512, a multiple of 32) two MMAs per 16 k fill the tile, half each, and the one
+// accumulator takes all of tensor memory: for products whose 256-wide tiles would be a wave and a half or two of the pairs and that
+// fit ONE wave so (2,048 x 4,096: 128 tiles of 256 columns on 74 pairs, or 72 tiles of 480).  The host asks for such a width only
+// when no pair gets a second tile, since nothing of a tile's epilogue could run under the next tile's MMAs.
 template <int BN, int EPI = 0>
 struct PairShape {
+  static constexpr int kHalves = BN > 256 ? 2 : 1;   // MMAs per 16 k
+  static constexpr int kMmaN = BN / kHalves;
   static constexpr int kStageBytes = (kBM + BN / 2) * kBK * 2;   // per CTA: its rows of x and its half of the rows of w
   // staging boxes of the epilogue's bulk stores (EPI 3: 32-bit boxes for bulk reductions): two per warp where they fit beside the
   // ring, else one
   static constexpr int kBoxBytes = EPI == 3 ? kAddBoxBytes : kStoreBoxBytes;
-  static constexpr int kRing = 220 * 1024 - (EPI == 3 ? kStoreWarps * 2 * kAddBoxBytes : 0);   // the reductions' boxes come out of the ring's room
+  // room for the ring: what is left beside alignment slack, barriers and the boxes (two per warp for the reductions, else one at least)
+  static constexpr int kRing = 227 * 1024 - 1280 - kStoreWarps * (EPI == 3 ? 2 : 1) * kBoxBytes;
   static constexpr int kStages = (kRing / kStageBytes) < 8 ? (kRing / kStageBytes) : 8;
   static constexpr int kStoreBuffers = (kStages * kStageBytes + kStoreWarps * 2 * kBoxBytes + 1280 <= 227 * 1024) ? 2 : 1;
   static constexpr int kStoreBytes = kStoreWarps * kStoreBuffers * kBoxBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /* alignment slack */ + 256 /* barriers */;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
-  static constexpr int kAccStride = BN <= 128 ? 128 : 256;       // tensor memory is allocated in powers of two
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "each CTA holds BN / 2 rows of w, in groups of 8");
+  static constexpr int kAccStride = BN <= 128 ? 128 : BN <= 256 ? 256 : 512;       // tensor memory is allocated in powers of two
+  static constexpr int kAccumulators = kAccStride <= 256 ? 2 : 1;
+  static_assert(kMmaN % 16 == 0 && kMmaN >= 32 && kMmaN <= 256, "N of an MMA is a multiple of 16, and each CTA holds half of its rows of w, in groups of 8");
+  static_assert(BN % kStoreCols == 0, "the epilogue hands the tile over in boxes of kStoreCols columns");
+  static_assert(EPI != 2 || kHalves == 1, "the gated tile is one instruction wide");
+  static_assert(kStages >= 2, "a ring needs two stages");
 };
 
 // EPI as in gemm_tcgen05.cu: 0 bfloat16 out, 1 32-bit out, 2 (BN = 256) w = [gate rows | up rows] and out = silu(gate) * up,
@@ -98,7 +109,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
   const int rank = (int)cluster_rank();
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   constexpr int kTileN = EPI == 2 ? BN / 2 : BN;   // output columns of a tile
-  constexpr int kTmemCols = 2 * Shape::kAccStride;   // two accumulators
+  constexpr int kAccumulators = Shape::kAccumulators;
+  constexpr int kTmemCols = kAccumulators * Shape::kAccStride;
   const int m_blocks = (M + 2 * kBM - 1) / (2 * kBM);
   const int num_tiles = m_blocks * ((N + kTileN - 1) / kTileN);
   const int k_blocks = (K + kBK - 1) / kBK;
@@ -137,8 +149,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
         const int m0 = (tile % m_blocks) * 2 * kBM + rank * kBM, n0 = (tile / m_blocks) * kTileN;
-        // this CTA's half of the tile's rows of w: rank 0 the first BN / 2 (the gate rows if gated), rank 1 the rest (the up rows)
-        const int w_row = EPI == 2 ? rank * N + n0 : n0 + rank * (BN / 2);
+        // this CTA's half of the rows of w of every MMA of the tile: rank 0 the first kMmaN / 2 (the gate rows if gated), rank 1 the rest (the up rows)
+        const int w_row = EPI == 2 ? rank * N + n0 : n0 + rank * (Shape::kMmaN / 2);
         for (int kb = 0; kb < k_blocks; ++kb, ring.advance()) {
           ok = mbar_wait(empty_addr + 8 * ring.stage, ring.phase ^ 1, abort_flag);
           if (!ok) break;
@@ -146,20 +158,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
           const uint32_t bar = full_addr + 8 * ring.stage;
           if (rank == 0) mbar_expect_tx(bar, 2 * Shape::kStageBytes);   // this CTA's bytes and the peer's
           tma_load_2d_pair(a_tile, &map_a, kb * kBK, m0, bar);
-          tma_load_2d_pair(b_tile, &map_b, kb * kBK, w_row, bar);
+#pragma unroll
+          for (int h = 0; h < Shape::kHalves; ++h)   // rows past N are filled with zeros
+            tma_load_2d_pair(b_tile + h * (Shape::kMmaN / 2) * kBK * 2, &map_b, kb * kBK, w_row + h * Shape::kMmaN, bar);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {   // MMA issuer of the pair
-      constexpr uint32_t idesc = umma_instr_desc(2 * kBM, BN);
+      constexpr uint32_t idesc = umma_instr_desc(2 * kBM, Shape::kMmaN);
       RingPosition<kStages> ring;
       const uint32_t tiles_low = umma_desc_low(smem_u32(tiles)), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
       int local = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++local) {
-        const int acc = local & 1;
-        ok = mbar_wait(&accum_empty[acc], ((local >> 1) & 1) ^ 1, abort_flag);   // both epilogues have drained this accumulator
+        const int acc = local % kAccumulators;
+        ok = mbar_wait(&accum_empty[acc], ((local / kAccumulators) & 1) ^ 1, abort_flag);   // both epilogues have drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride;
@@ -171,7 +185,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
           const uint32_t a_low = tiles_low + ring.stage * (Shape::kStageBytes >> 4), b_low = a_low + ((kBM * kBK * 2) >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
-            umma_bf16_pair(tmem_acc, a_low + k * ((kUmmaK * 2) >> 4), b_low + k * ((kUmmaK * 2) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            // the second half of a wide tile: this CTA's kMmaN / 2 rows of w further, kMmaN columns on
+#pragma unroll
+            for (int h = 0; h < Shape::kHalves; ++h)
+              umma_bf16_pair(tmem_acc + h * Shape::kMmaN, a_low + k * ((kUmmaK * 2) >> 4), b_low + h * (((Shape::kMmaN / 2) * kBK * 2) >> 4) + k * ((kUmmaK * 2) >> 4), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(empty_addr + 8 * ring.stage);   // the stage is free in both CTAs once these MMAs have read it
         }
@@ -183,9 +201,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads)
     const int sub = warp & 3;
     int local = 0, boxes = 0;
     for (int tile = pair; tile < num_tiles; tile += pairs, ++local) {
-      const int acc = local & 1;
+      const int acc = local % kAccumulators;
       const int m0 = (tile % m_blocks) * 2 * kBM + rank * kBM, n0 = (tile / m_blocks) * kTileN;
-      if (!mbar_wait(&accum_full[acc], (local >> 1) & 1, abort_flag)) break;
+      if (!mbar_wait(&accum_full[acc], (local / kAccumulators) & 1, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t tmem_acc = tmem_base + acc * Shape::kAccStride + ((uint32_t)(sub * 32) << 16);
       const int row = m0 + sub * 32 + lane;
@@ -221,7 +239,7 @@ template <int BN, int EPI>
 static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
   CUtensorMap map_a, map_b, map_out;
   // each CTA fetches boxes of 128 rows of x and BN / 2 rows of w (gated: w has 2 N rows, one CTA takes gate rows, the other up rows)
-  if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, BN / 2)) return (int)cudaErrorInvalidValue;
+  if (!make_map(&map_a, x, M, K, kBM) || !make_map(&map_b, w, EPI == 2 ? 2 * N : N, K, PairShape<BN, EPI>::kMmaN / 2)) return (int)cudaErrorInvalidValue;
   if (EPI == 3 && !make_add_map(&map_out, out, M, N)) return (int)cudaErrorInvalidValue;
   const int staged = EPI == 3 || (EPI != 1 && make_store_map(&map_out, out, M, N)) ? 1 : 0;   // else rows are stored straight from registers
   if (!staged) map_out = map_a;
@@ -243,13 +261,21 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
 
 using namespace tlie;
 
-// As tlie_gemm_tcgen05 (gemm_tcgen05.cu), on pairs of SMs; tile_n is 128, 160, 192 or 256.
+// As tlie_gemm_tcgen05 (gemm_tcgen05.cu), on pairs of SMs; tile_n is 128, 160, 192, 256, or 288, 384 or 480 (two MMAs wide, one accumulator);
+// adding into a 32-bit out (out_f32 = 3): 256, 384 or 480.
 TLIE_EXPORT int tlie_gemm_tcgen05_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int tile_n, int* error_flag,
                                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || error_flag == nullptr || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   if (out_f32 == 2) return launch_pair<256, 2>(x, w, out, M, N, K, error_flag, stream);   // gated: N = rows of one half of w
-  if (out_f32 == 3) return launch_pair<256, 3>(x, w, out, M, N, K, error_flag, stream);   // out (32-bit, 16-byte aligned, N % 4 == 0) += the product
+  if (out_f32 == 3) {   // out (32-bit, 16-byte aligned, N % 4 == 0) += the product
+    if (tile_n == 480) return launch_pair<480, 3>(x, w, out, M, N, K, error_flag, stream);
+    if (tile_n == 384) return launch_pair<384, 3>(x, w, out, M, N, K, error_flag, stream);
+    return launch_pair<256, 3>(x, w, out, M, N, K, error_flag, stream);
+  }
+  if (tile_n == 480) return out_f32 ? launch_pair<480, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<480, 0>(x, w, out, M, N, K, error_flag, stream);
+  if (tile_n == 384) return out_f32 ? launch_pair<384, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<384, 0>(x, w, out, M, N, K, error_flag, stream);
+  if (tile_n == 288) return out_f32 ? launch_pair<288, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<288, 0>(x, w, out, M, N, K, error_flag, stream);
   if (tile_n == 256) return out_f32 ? launch_pair<256, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<256, 0>(x, w, out, M, N, K, error_flag, stream);
   if (tile_n == 192) return out_f32 ? launch_pair<192, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<192, 0>(x, w, out, M, N, K, error_flag, stream);
   if (tile_n == 160) return out_f32 ? launch_pair<160, 1>(x, w, out, M, N, K, error_flag, stream) : launch_pair<160, 0>(x, w, out, M, N, K, error_flag, stream);

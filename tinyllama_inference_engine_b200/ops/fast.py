@@ -294,30 +294,50 @@ GEMM_WIDE_TILES = (288, 320)   # two MMAs wide, one accumulator: for products th
 # Tiles of 256 rows on pairs of SMs (tcgen05 cta_group::2, gemm_tcgen05_pair.cu) bring a third less from L2 per flop.  That pays
 # where a product is several waves of tiles, so that what the SMs can pull from L2 sets the pace: measured at 2,048 rows and
 # K = 4,096, N = 12,288: 139 us on pairs, 153 on single SMs (the library: 142); N = 4,096, K = 11,008: 129, 163 (144); 8,192 rows,
-# N = 6,144: 278, 317 (278).  A product of one wave or so is better off with one-SM tiles of the width that fits the wave
-# (2,048 x 2,560 x 2,048: 19.4 us in one wave of 288-wide tiles, 24.3 on pairs).  The gated product runs on pairs from 1,024 rows.
+# N = 6,144: 278, 317 (278).  The pairs have wide tiles of their own (two MMAs wide, one accumulator) for products that fit one
+# wave of the pairs so: 2,048 x 4,096 is 128 tiles of 256 columns for 74 pairs, or 72 tiles of 480 (K = 11,008, adding into the
+# residual: 132 -> 123.5 us; 2,048 x 3,072 x 3,072 with 384-wide tiles: 42.7 -> 36.6 us).  The gated product runs on pairs from
+# 1,024 rows.
 PAIR_MIN_ROWS = 1024
+PAIR_TILE_WIDTHS = (256,)          # narrower tiles on pairs were behind the 256-wide ones wherever they were measured
+PAIR_WIDE_TILES = (288, 384, 480)
+PAIR_ADDING_WIDE_TILES = (384, 480)
+PAIR_TILE_GAIN = 0.9               # a tile on a pair of SMs against two tiles of the same width on single SMs, where L2 sets the pace
 use_sm_pairs = True
 
 
-def pair_tiles_pay(M: int, N: int) -> bool:
-    """Whether a plain or accumulating product of this shape runs on pairs of SMs: one and a half waves of one-SM tiles or more."""
-    return use_sm_pairs and M >= PAIR_MIN_ROWS and -(-M // 128) * -(-N // 256) >= (3 * sm_count()) // 2
-
-
-@functools.lru_cache(maxsize=4096)
-def gemm_tile_width(M: int, N: int, pair: bool = False) -> int:
-    """The tile width whose waves of persistent CTAs (or pairs of them) cost least.
+def _cheapest_tiles(M: int, N: int, pair: bool, adding: bool) -> tuple[int, int, int]:
+    """(tile width, cost, waves) of the cheapest way to tile an M x N product on single SMs or on pairs: cost = waves x (width + 300).
 
     A tile costs its width plus a fixed part about as large as 300 columns (measured: a 128 x 160 tile takes 0.8 of the time
-    of a 128 x 256 one), so the widest tile wins unless a narrower one saves a whole wave; the wider tile on a tie.  The wide
+    of a 128 x 256 one), so the widest tile wins unless a narrower one saves a whole wave; the wider tile on a tie.  A wide
     tile has no second accumulator to work on while its epilogue runs, so it is a candidate only where no CTA gets two."""
     workers = sm_count() // 2 if pair else sm_count()
     row_blocks = -(-M // (256 if pair else 128))
-    widths = GEMM_TILE_WIDTHS
-    if not pair:
-        widths = tuple(width for width in GEMM_WIDE_TILES if row_blocks * -(-N // width) <= workers) + widths
-    return min(widths, key=lambda width: (-(-(row_blocks * -(-N // width)) // workers) * (width + 300), -width))
+    if pair:
+        widths, wide = PAIR_TILE_WIDTHS, (PAIR_ADDING_WIDE_TILES if adding else PAIR_WIDE_TILES)
+    else:
+        widths, wide = ((256,), ()) if adding else (GEMM_TILE_WIDTHS, GEMM_WIDE_TILES)
+    candidates = tuple(width for width in wide if row_blocks * -(-N // width) <= workers) + widths
+    waves = lambda width: -(-(row_blocks * -(-N // width)) // workers)  # noqa: E731
+    best = min(candidates, key=lambda width: (waves(width) * (width + 300), -width))
+    return best, waves(best) * (best + 300), waves(best)
+
+
+@functools.lru_cache(maxsize=4096)
+def gemm_tile_width(M: int, N: int, pair: bool = False, adding: bool = False) -> int:
+    """The tile width whose waves of persistent CTAs (or pairs of them) cost least; ``adding``: for the product that adds into the residual."""
+    return _cheapest_tiles(M, N, pair, adding)[0]
+
+
+@functools.lru_cache(maxsize=4096)
+def pair_tiles_pay(M: int, N: int) -> bool:
+    """Whether a plain product of this shape runs on pairs of SMs: where their cheapest tiling (with what a pair gains on two single
+    SMs, if it is waves of tiles) costs less than the cheapest one-SM tiling; a product that one wave of one-SM tiles holds stays there."""
+    if not use_sm_pairs or M < PAIR_MIN_ROWS:
+        return False
+    _, pair_cost, pair_waves = _cheapest_tiles(M, N, True, False)
+    return (PAIR_TILE_GAIN if pair_waves > 1 else 1.0) * pair_cost < _cheapest_tiles(M, N, False, False)[1]
 
 
 def gemm_tcgen05(x, weight, out, tile_n: int | None = None, pair: bool | None = None) -> None:
@@ -332,7 +352,7 @@ def gemm_tcgen05(x, weight, out, tile_n: int | None = None, pair: bool | None = 
     if pair is None:
         pair = tile_n is None and pair_tiles_pay(M, N)
     if tile_n is None:
-        tile_n = 256 if pair else gemm_tile_width(M, N, pair)   # pairs: the widest tile brings least from L2 per flop
+        tile_n = gemm_tile_width(M, N, pair)
     library = tcgen05_library()
     entry = library.tlie_gemm_tcgen05_pair if pair else library.tlie_gemm_tcgen05
     ops._check(
@@ -351,7 +371,7 @@ def can_accumulate(rows: int, weight) -> bool:
     return (use_tcgen05 and use_accumulate_epilogue and weight.dtype == torch.bfloat16 and N % 4 == 0 and K % 8 == 0 and tcgen05_takes(rows, N, K))
 
 
-def gemm_tcgen05_accumulate(x, weight, residual, pair: bool | None = None) -> None:
+def gemm_tcgen05_accumulate(x, weight, residual, pair: bool | None = None, tile_n: int | None = None) -> None:
     """residual[M, N] (32-bit) += x[M, K] . weight[N, K]^T: the product's tiles are added by bulk tensor reductions, each element once.
 
     ``pair``: on pairs of SMs (default: from PAIR_MIN_ROWS rows on; these tiles are 256 wide either way, and the pairs were ahead
@@ -365,10 +385,12 @@ def gemm_tcgen05_accumulate(x, weight, residual, pair: bool | None = None) -> No
         raise KernelError("gemm_tcgen05_accumulate takes contiguous bfloat16 operands (K % 8 == 0) and a contiguous 32-bit residual [M, N] with N % 4 == 0", code="invalid_shape")
     if pair is None:
         pair = use_sm_pairs and M >= PAIR_MIN_ROWS
+    if tile_n is None:
+        tile_n = gemm_tile_width(M, N, pair, adding=True)
     library = tcgen05_library()
     entry = library.tlie_gemm_tcgen05_pair if pair else library.tlie_gemm_tcgen05
     ops._check(
-        entry(ops._ptr(x), ops._ptr(weight), ops._ptr(residual), c_int(M), c_int(N), c_int(K), c_int(3), c_int(256),
+        entry(ops._ptr(x), ops._ptr(weight), ops._ptr(residual), c_int(M), c_int(N), c_int(K), c_int(3), c_int(tile_n),
               ops._ptr(tcgen05_error_flag(x.device)), ops._stream()),
         "gemm_tcgen05_accumulate",
     )
