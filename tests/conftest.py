@@ -25,14 +25,15 @@ def model_folders(tmp_path_factory):
     return {key: write_random_model(base / key, config, seed) for key, (config, seed) in ALL.items()}
 
 
-@pytest.fixture(params=["library", "own"], ids=["mid-size products by the library", "own products from 128 rows"])
+@pytest.fixture(params=["library", "own"], ids=["small products by the library", "own products from 128 rows"])
 def product_thresholds(request, monkeypatch):
-    """Steps of 128 to 2,047 rows send their products to the library (it is faster there); the second run of a test that uses this
-    fixture lowers the thresholds, so that the engine's own tensor-core products (plain, gated, adding into the residual) are
-    checked through the engine at the test's small sizes too."""
+    """Small products, and those whose tiles would leave SMs idle, go to the library (it is faster there); the second run of a test
+    that uses this fixture takes the conditions away, so that the engine's own tensor-core products (plain, gated, adding into the
+    residual) are checked through the engine at the test's small sizes too."""
     if request.param == "own":
         from tinyllama_inference_engine_b200.ops import fast
 
-        monkeypatch.setattr(fast, "TCGEN05_MIN_ROWS", 128)
-        monkeypatch.setattr(fast, "TCGEN05_GATED_MIN_ROWS", 128)
+        for name, value in (("TCGEN05_MIN_ROWS", 128), ("TCGEN05_GATED_MIN_ROWS", 128), ("OWN_PRODUCT_MIN_EFFICIENCY", 0.0), ("OWN_PRODUCT_MIN_FLOP", 0.0),
+                            ("OWN_ADDING_MIN_FLOP", 0.0)):
+            monkeypatch.setattr(fast, name, value)
     return request.param

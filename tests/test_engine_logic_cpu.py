@@ -87,18 +87,20 @@ def test_step_refuses_bad_batches(model_folders, monkeypatch):
         small.runtime.workspace.get("anything", 9, 4, torch.float32)
 
 
-def test_products_below_2048_rows_go_to_the_library(monkeypatch):
+def test_own_products_run_where_their_tiles_fill_the_waves():
     from tinyllama_inference_engine_b200.ops import fast
 
-    assert fast.tcgen05_takes(2048, 2048, 5632) and fast.tcgen05_takes(2048, 2560, 2048) and fast.tcgen05_takes(8192, 4096, 14336)
-    assert not fast.tcgen05_takes(1536, 2048, 5632) and not fast.tcgen05_takes(512, 2048, 2048)   # the library is ahead at these sizes
-    assert not fast.tcgen05_takes(64, 32000, 2048)
-    # the tile rule behind the row threshold: tiles for fewer than half of the SMs and a long K go to the library whatever the rows
-    monkeypatch.setattr(fast, "TCGEN05_MIN_ROWS", 128)
-    assert not fast.tcgen05_takes(512, 2048, 5632)      # 32 tiles for 148 SMs, 88 k blocks each
-    assert not fast.tcgen05_takes(1024, 2048, 5632)     # 64 tiles
-    assert fast.tcgen05_takes(512, 2048, 2048)          # few tiles, short K
-    assert fast.tcgen05_takes(128, 32000, 8192)         # one row block, 125 tiles
+    # 1.1B widths: the step of 2,048 rows, not the smaller ones
+    assert fast.tcgen05_takes(2048, 2560, 2048) and fast.tcgen05_takes(2048, 2048, 2048, adding=True) and fast.tcgen05_takes(2048, 2048, 5632, adding=True)
+    assert not fast.tcgen05_takes(1536, 2560, 2048) and not fast.tcgen05_takes(1024, 2560, 2048)   # small products: the library's start and end are shorter
+    assert not fast.tcgen05_takes(1536, 2048, 5632, adding=True)        # 48 tiles for 74 pairs
+    assert fast.tcgen05_takes(1792, 2048, 5632, adding=True)            # 56 tiles
+    assert fast.tcgen05_takes(8192, 2560, 2048)
+    # 7B / 8B widths: from 1,024 rows on
+    assert fast.tcgen05_takes(1024, 12288, 4096) and fast.tcgen05_takes(1024, 4096, 4096, adding=True) and fast.tcgen05_takes(1536, 4096, 11008, adding=True)
+    assert fast.tcgen05_takes(1280, 4096, 11008, adding=True)           # 55 tiles of 384 columns for 74 pairs
+    assert fast.tcgen05_takes(8192, 4096, 14336, adding=True) and fast.tcgen05_takes(8192, 6144, 4096)
+    assert not fast.tcgen05_takes(512, 12288, 4096) and not fast.tcgen05_takes(64, 32000, 2048)   # below the smallest row count
 
 
 def test_gemm_tile_width_prefers_full_waves():

@@ -248,34 +248,42 @@ def gemm_skinny(x, weight, out, *, epilogue: str = "store", prepared=None, prepa
 
 
 # --- tensor-core product for many rows (tcgen05, TMA, tensor memory) -------------------------------------
-# From how many rows on the engine's own tcgen05 kernels run instead of the library's product (and, for the fused forms, the small
-# kernel after it).  Measured with CUDA events in a replayed graph, weights from HBM, at 1.1B and 7B widths, 128 to 2,048 rows:
-#   * the plain product is level with the library's from 2,048 rows on (qkv of 2,048 rows at 1.1B widths 19.4 against 20.7 us)
-#     and behind it below: by a tenth where there are tiles for every SM (7B widths, 1,024 rows: 83 against 74 us), by half where
-#     there are not (1.1B widths, 512 rows: 13.2 against 7.8 us; a CTA runs all of K for its tile, the library also splits K);
-#   * the product that adds into the 32-bit residual is level with product + add kernel from 2,048 rows on and behind below
-#     (7B widths, down-proj of 1,536 rows: 159 against 122 us);
+# Where the engine's own tcgen05 kernels run instead of the library's product (and, for the fused forms, the small kernel after
+# it).  Measured with CUDA events in a replayed graph, weights from HBM, at 1.1B, 7B and 8B widths, 128 to 8,192 rows
+# (`kernel-bench --products`): the engine's kernels are level with or ahead of the library wherever their tiles are wide and keep the
+# SMs busy over whole waves and the product is large enough for its start and end not to count, and behind elsewhere, since a CTA
+# runs all of K for its tile where the library also splits K:
+#   * 1.1B widths, 2,048 rows: qkv 19.9 us (one wave of 288-wide tiles) against 19.0, o (adding) 17.5 against 22.0 for product + add
+#     kernel; 1,024 rows: qkv 14.7 against 10.9 (half the work, the same start and end), o 16.5 against 14.1 (32 tiles for 74 pairs);
+#   * 7B widths, 1,024 rows: o 28.1 against 33.8, down 67.3 against 71.2, qkv level; 8B widths, 1,024 rows: qkv 44.8 against 37.4 (96
+#     tiles for 74 pairs: two waves, the second a third full);
 #   * the gated product on pairs of SMs is ahead of product + activation kernel from 1,024 rows on (7B widths: 130 against
 #     160 us; 1.1B widths: 46.7 against 45.5) and behind below (768 rows: 116 against 111, 36.4 against 33.6).
-TCGEN05_MIN_ROWS = 2048
+TCGEN05_MIN_ROWS = 1024            # below this the library was ahead at every width
 TCGEN05_GATED_MIN_ROWS = 1024
+OWN_PRODUCT_MIN_EFFICIENCY = 0.75  # what the product's tiling costs against 256-wide tiles on every SM with no wave left partly empty (0.76: ahead, 0.73: behind)
+OWN_PRODUCT_MIN_FLOP = 20e9        # a smaller product is mostly its start and end, where the library is ahead
+OWN_ADDING_MIN_FLOP = 10e9         # the adding product also saves the add kernel
 use_tcgen05 = True
 
 
 TCGEN05_SOURCES = ["gemm_tcgen05.cu", "gemm_tcgen05_pair.cu"]
 
 
-def tcgen05_takes(M: int, N: int, K: int) -> bool:
-    """Whether a plain product runs on this engine's tcgen05 kernel (else on the library's): from TCGEN05_MIN_ROWS rows on, and
-    not with tiles for fewer than half of the SMs and a long K.
+def tcgen05_takes(M: int, N: int, K: int, adding: bool = False) -> bool:
+    """Whether a plain product (``adding``: one that adds into the residual) runs on this engine's tcgen05 kernels (else on the
+    library's): from TCGEN05_MIN_ROWS rows on, where the tiling it would get is an efficient one (waves that are full, tiles that
+    are not narrow: the cost model of ``_cheapest_tiles`` against its own ideal) and the product is not a small one.
 
-    The kernel gives a CTA whole 128 x 256 tiles, all of K each; the library's product also splits K (measured at 512 rows on
-    the 1.1B shapes, down (K = 5,632): 32 against 16 us).  (Sharing a tile's k blocks among CTAs was tried in this kernel: the
+    (Sharing a tile's k blocks among CTAs, which would fill the SMs for small products too, was tried in the one-SM kernel: the
     owner of a tile collects the others' partial accumulators at the very end of its share, eight trips to the L2 per partial
     tile with nothing left to hide them behind, and that cost more than even shares saved.)"""
     if M < TCGEN05_MIN_ROWS:
         return False
-    return -(-M // 128) * -(-N // 256) >= sm_count() // 2 or K < 4096
+    pair = (use_sm_pairs and M >= PAIR_MIN_ROWS) if adding else pair_tiles_pay(M, N)
+    _, cost, _ = _cheapest_tiles(M, N, pair, adding)
+    ideal = -(-M // (256 if pair else 128)) * N / (sm_count() // 2 if pair else sm_count()) * (256 + 300) / 256
+    return ideal / cost >= OWN_PRODUCT_MIN_EFFICIENCY and 2.0 * M * N * K >= (OWN_ADDING_MIN_FLOP if adding else OWN_PRODUCT_MIN_FLOP)
 
 
 def tcgen05_library():
@@ -368,7 +376,7 @@ use_accumulate_epilogue = True   # o-proj and down-proj of prompt portions add i
 def can_accumulate(rows: int, weight) -> bool:
     """Whether ``gemm_tcgen05_accumulate`` takes residual += x . weight^T for this many rows."""
     N, K = weight.shape
-    return (use_tcgen05 and use_accumulate_epilogue and weight.dtype == torch.bfloat16 and N % 4 == 0 and K % 8 == 0 and tcgen05_takes(rows, N, K))
+    return (use_tcgen05 and use_accumulate_epilogue and weight.dtype == torch.bfloat16 and N % 4 == 0 and K % 8 == 0 and tcgen05_takes(rows, N, K, adding=True))
 
 
 def gemm_tcgen05_accumulate(x, weight, residual, pair: bool | None = None, tile_n: int | None = None) -> None:

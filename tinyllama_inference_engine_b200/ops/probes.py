@@ -107,7 +107,8 @@ def product_comparison(rows: int, hidden: int, intermediate: int, qkv_width: int
     """The four products of a layer for a step of ``rows`` rows (128 or more), bfloat16: the engine's own tcgen05 kernels (tiles on one
     SM, tiles on pairs of SMs; plain, adding into the 32-bit residual, gated) against the library's product plus the small kernel
     the fused form saves.  Microseconds per launch inside a replayed CUDA graph, every launch with another copy of the weights so
-    that they come from HBM.  ``own_runs`` says which form a step of this size gets (ops.fast thresholds)."""
+    that they come from HBM.  Each form runs with the tile width the engine would pick for it; ``own_runs`` says which form a step of
+    this size gets (ops.fast.tcgen05_takes, pair_tiles_pay)."""
     from .. import ops
     from . import fast
 
@@ -141,14 +142,14 @@ def product_comparison(rows: int, hidden: int, intermediate: int, qkv_width: int
         if kind == "plain":
             line["library"] = timed(lambda i: torch.mm(x, weights[i % copies].t(), out=out))
             line["own, one SM"] = timed(lambda i: fast.gemm_tcgen05(x, weights[i % copies], out, pair=False))
-            line["own, SM pairs"] = timed(lambda i: fast.gemm_tcgen05(x, weights[i % copies], out, tile_n=256, pair=True))
+            line["own, SM pairs"] = timed(lambda i: fast.gemm_tcgen05(x, weights[i % copies], out, pair=True))
             line["own_runs"] = fast.tcgen05_takes(rows, N, K) and ("SM pairs" if fast.pair_tiles_pay(rows, N) else "one SM")
         elif kind == "add":
             residual = torch.zeros(rows, N, device=device)
             line["library + add kernel"] = timed(lambda i: (torch.mm(x, weights[i % copies].t(), out=out), ops.add_(residual, out)))
             line["own, one SM"] = timed(lambda i: fast.gemm_tcgen05_accumulate(x, weights[i % copies], residual, pair=False))
             line["own, SM pairs"] = timed(lambda i: fast.gemm_tcgen05_accumulate(x, weights[i % copies], residual, pair=True))
-            line["own_runs"] = fast.can_accumulate(rows, weights[0]) and ("SM pairs" if rows >= fast.PAIR_MIN_ROWS else "one SM")
+            line["own_runs"] = fast.can_accumulate(rows, weights[0]) and ("SM pairs" if fast.use_sm_pairs and rows >= fast.PAIR_MIN_ROWS else "one SM")
         else:
             half = torch.empty(rows, N // 2, device=device, dtype=torch.bfloat16)
             line["library + activation kernel"] = timed(lambda i: (torch.mm(x, weights[i % copies].t(), out=out), ops.silu_mul(out, half)))
