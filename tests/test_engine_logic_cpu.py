@@ -101,6 +101,8 @@ def test_own_products_run_where_their_tiles_fill_the_waves():
     assert fast.tcgen05_takes(1280, 4096, 11008, adding=True)           # 55 tiles of 384 columns for 74 pairs
     assert fast.tcgen05_takes(8192, 4096, 14336, adding=True) and fast.tcgen05_takes(8192, 6144, 4096)
     assert not fast.tcgen05_takes(512, 12288, 4096) and not fast.tcgen05_takes(64, 32000, 2048)   # below the smallest row count
+    # the gated product: from 1,024 rows, and from 512 where it is a large one
+    assert fast.gated_takes(1024, 11264, 2048) and not fast.gated_takes(896, 11264, 2048) and fast.gated_takes(512, 22016, 4096) and not fast.gated_takes(384, 28672, 4096)
 
 
 def test_gemm_tile_width_prefers_full_waves():

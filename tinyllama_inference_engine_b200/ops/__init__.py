@@ -266,7 +266,7 @@ def linear_gated(x, weight, out) -> None:
     """out = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel."""
     if fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True):
         fast.gemv_fused(x, weight, out, epilogue="gated")
-    elif fast.use_tcgen05 and x.shape[0] >= fast.TCGEN05_GATED_MIN_ROWS and weight.shape[1] % 8 == 0 and x.is_contiguous():
+    elif fast.use_tcgen05 and fast.gated_takes(x.shape[0], weight.shape[0], weight.shape[1]) and weight.shape[1] % 8 == 0 and x.is_contiguous():
         fast.gemm_tcgen05_gated(x, weight, out)
     elif fast.use_skinny and fast.skinny_fits(x.shape[0], weight, x) and out.is_contiguous() and out.dtype == torch.bfloat16:
         fast.gemm_skinny(x, weight, out, epilogue="gated")

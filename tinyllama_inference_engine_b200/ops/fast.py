@@ -258,9 +258,11 @@ def gemm_skinny(x, weight, out, *, epilogue: str = "store", prepared=None, prepa
 #   * 7B widths, 1,024 rows: o 28.1 against 33.8, down 67.3 against 71.2, qkv level; 8B widths, 1,024 rows: qkv 44.8 against 37.4 (96
 #     tiles for 74 pairs: two waves, the second a third full);
 #   * the gated product on pairs of SMs is ahead of product + activation kernel from 1,024 rows on (7B widths: 130 against
-#     160 us; 1.1B widths: 46.7 against 45.5) and behind below (768 rows: 116 against 111, 36.4 against 33.6).
+#     160 us; 1.1B widths: 46.7 against 45.5); below that it is ahead where the product is a large one (7B widths, 768 rows: 104
+#     against 112 us; 8B widths, 512 rows: 100 against 112) and behind where it is not (1.1B widths, 768 rows: 36.4 against 34.5).
 TCGEN05_MIN_ROWS = 1024            # below this the library was ahead at every width
 TCGEN05_GATED_MIN_ROWS = 1024
+TCGEN05_GATED_LARGE = (512, 80e9)  # the gated product also from this many rows on where it is this many flop or more
 OWN_PRODUCT_MIN_EFFICIENCY = 0.75  # what the product's tiling costs against 256-wide tiles on every SM with no wave left partly empty (0.76: ahead, 0.73: behind)
 OWN_PRODUCT_MIN_FLOP = 20e9        # a smaller product is mostly its start and end, where the library is ahead
 OWN_ADDING_MIN_FLOP = 10e9         # the adding product also saves the add kernel
@@ -284,6 +286,11 @@ def tcgen05_takes(M: int, N: int, K: int, adding: bool = False) -> bool:
     _, cost, _ = _cheapest_tiles(M, N, pair, adding)
     ideal = -(-M // (256 if pair else 128)) * N / (sm_count() // 2 if pair else sm_count()) * (256 + 300) / 256
     return ideal / cost >= OWN_PRODUCT_MIN_EFFICIENCY and 2.0 * M * N * K >= (OWN_ADDING_MIN_FLOP if adding else OWN_PRODUCT_MIN_FLOP)
+
+
+def gated_takes(M: int, N: int, K: int) -> bool:
+    """Whether the gated product ([gate rows | up rows]: N rows of w in all) of a step of M rows runs on this engine's tcgen05 kernel."""
+    return M >= TCGEN05_GATED_MIN_ROWS or (M >= TCGEN05_GATED_LARGE[0] and 2.0 * M * N * K >= TCGEN05_GATED_LARGE[1])
 
 
 def tcgen05_library():
@@ -411,8 +418,8 @@ def gemm_tcgen05_gated(x, weight, out, pair: bool | None = None) -> None:
     inter = weight.shape[0] // 2
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or K % 8 != 0 or not x.is_contiguous() or out.shape != (M, inter):
         raise KernelError("gemm_tcgen05_gated takes contiguous bfloat16 operands with K % 8 == 0 and out [M, rows / 2]", code="invalid_shape")
-    if pair is None:
-        pair = use_sm_pairs and M >= PAIR_MIN_ROWS
+    if pair is None:   # below the pairs' usual row count: where the rows are whole 256-row tiles (640 rows at 7B widths: 102 us on pairs, 96 on single SMs)
+        pair = use_sm_pairs and (M >= PAIR_MIN_ROWS or (M >= 512 and M % 256 == 0))
     library = tcgen05_library()
     entry = library.tlie_gemm_tcgen05_pair if pair else library.tlie_gemm_tcgen05
     ops._check(

@@ -155,7 +155,7 @@ def product_comparison(rows: int, hidden: int, intermediate: int, qkv_width: int
             line["library + activation kernel"] = timed(lambda i: (torch.mm(x, weights[i % copies].t(), out=out), ops.silu_mul(out, half)))
             line["own, one SM"] = timed(lambda i: fast.gemm_tcgen05_gated(x, weights[i % copies], half, pair=False))
             line["own, SM pairs"] = timed(lambda i: fast.gemm_tcgen05_gated(x, weights[i % copies], half, pair=True))
-            line["own_runs"] = rows >= fast.TCGEN05_GATED_MIN_ROWS and ("SM pairs" if rows >= fast.PAIR_MIN_ROWS else "one SM")
+            line["own_runs"] = fast.gated_takes(rows, N, K) and ("SM pairs" if fast.use_sm_pairs and (rows >= fast.PAIR_MIN_ROWS or (rows >= 512 and rows % 256 == 0)) else "one SM")
         report[name] = line
         del weights
     ops.check_device_errors(device)
