@@ -473,6 +473,7 @@ def test_gemm_skinny(ops, M, N, K):
 
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,page_size,window,rotate", [
     (32, 4, 64, 64, 0, True), (8, 8, 128, 64, 0, True), (6, 2, 32, 32, 0, True), (8, 2, 64, 16, 100, True), (4, 2, 64, 16, 0, False), (12, 3, 96, 16, 0, True),
+    (24, 2, 64, 16, 0, True),   # groups of twelve: the tile's upper rows are in use, four of them empty
 ])
 @pytest.mark.parametrize("splits", [1, 5])
 def test_decode_attention_with_rotation_and_cache_write(ops, q_heads, kv_heads, head_dim, page_size, window, rotate, splits):
