@@ -34,6 +34,6 @@ def product_thresholds(request, monkeypatch):
         from tinyllama_inference_engine_b200.ops import fast
 
         for name, value in (("TCGEN05_MIN_ROWS", 128), ("TCGEN05_GATED_MIN_ROWS", 128), ("OWN_PRODUCT_MIN_EFFICIENCY", 0.0), ("OWN_PRODUCT_MIN_FLOP", 0.0),
-                            ("OWN_ADDING_MIN_FLOP", 0.0)):
+                            ("OWN_ADDING_MIN_FLOP", 0.0), ("PAIR_MIN_ROWS", 256)):   # pairs of SMs from 256 rows: their kernels too
             monkeypatch.setattr(fast, name, value)
     return request.param
