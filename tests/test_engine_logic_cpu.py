@@ -193,3 +193,35 @@ def test_the_engine_refuses_weights_with_another_digest(model_folders):
     with pytest.raises(EngineError) as caught:
         ModelRunner(folder, EngineConfig(dtype="float32", page_size=16, max_cache_tokens=64, device="cpu", weights_sha256="f" * 64))
     assert caught.value.code == "checksum_mismatch"
+
+
+def test_a_packed_step_holds_what_its_entries_say():
+    """The packer's flat buffer, section by section, against plain loops: decoding requests beside prompt portions, wanted places,
+    block tables of two page groups, a registered work list; written fresh and into a buffer of fixed address."""
+    from tinyllama_inference_engine_b200.engine.batch import StepEntry, StepPlan, pack_step, register_step_plan, unregister_step_plan
+
+    entries = [StepEntry("d0", [7], [0]), StepEntry("d1", [9], []), StepEntry("p0", [3, 1, 4, 1, 5], [4, 0]), StepEntry("p1", [2, 6], [1])]
+    firsts, slots = [40, 3, 0, 17], [5, 0, 2, 9]
+    tables = [[[1, 2, -1], [3, -1, -1], [4, 5, 6], [7, -1, -1]], [[8, -1, -1], [9, -1, -1], [10, 11, -1], [12, 13, -1]]]
+    register_step_plan(StepPlan("test_lengths_twice", 2, lambda q, f, s: [n for n in q for _ in range(2)], lambda q: True))
+    try:
+        host = torch.zeros(256, dtype=torch.int32)
+        device = torch.zeros(256, dtype=torch.int32)
+        for into in (None, (host, device)):
+            ctx = pack_step(entries, firsts, slots, tables, torch.device("cpu"), into=into)
+            assert ctx.num_tokens == 9 and ctx.num_seqs == 4 and ctx.max_q_len == 5 and ctx.max_seq_len == 41 and not ctx.decode_only
+            assert ctx.token_ids.tolist() == [7, 9, 3, 1, 4, 1, 5, 2, 6]
+            assert ctx.positions.tolist() == [40, 3, 0, 1, 2, 3, 4, 17, 18]
+            assert ctx.token_seq.tolist() == [0, 1, 2, 2, 2, 2, 2, 3, 3]
+            assert ctx.seq_starts.tolist() == [0, 1, 2, 7, 9] and ctx.seq_lens.tolist() == [41, 4, 5, 19]
+            assert ctx.first_positions.tolist() == firsts and ctx.state_slots.tolist() == slots
+            assert ctx.want_rows.tolist() == [0, 6, 2, 8] and not ctx.wants_every_row_in_order
+            assert [t.tolist() for t in ctx.block_tables] == tables
+            assert ctx.plan("test_lengths_twice").tolist() == [[1, 1], [1, 1], [5, 5], [2, 2]] and ctx.plan("nobody registered this") is None
+            assert ctx.host_q_lens == [1, 1, 5, 2] and ctx.request_ids == ["d0", "d1", "p0", "p1"]
+        whole = pack_step([StepEntry("w", [1, 2, 3], [0, 1, 2])], [0], [0], [[[0]]], torch.device("cpu"))
+        assert whole.wants_every_row_in_order and whole.want_rows.tolist() == [0, 1, 2]
+        nothing_wanted = pack_step([StepEntry("w", [1, 2, 3], [])], [5], [0], [[[0]]], torch.device("cpu"))
+        assert nothing_wanted.want_rows is None and nothing_wanted.positions.tolist() == [5, 6, 7]
+    finally:
+        unregister_step_plan("test_lengths_twice")
